@@ -1,0 +1,355 @@
+/*
+ * kuiops.h -- C ABI of the B200 (sm_100a) kuiops operator library.
+ *
+ * The reference project (panther03/kuiLLM) has no fixed C ABI: every kernel
+ * instantiation is extracted to a host launcher `<Module>_<name>(dims..., ptrs...)`
+ * whose prototype sits in a generated `_decl.h` (kuipy/toolchain.py:171-182,
+ * kuipy/compile.py:98-112) and is called from a per-family pybind wrapper
+ * template (kuiops/<op>/wrapper_<op>.cu.j2).  This header fixes those launcher
+ * calls as one stable set of `extern "C"` entry points.  Each declaration cites
+ * the reference launcher call it replaces; the argument order of the reference
+ * is kept (dims first, then pointers), followed by the additions every entry
+ * point shares: caller-owned workspace where a kernel needs scratch, and the
+ * CUDA stream.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  All pointers are device pointers unless a
+ *     parameter is documented as a host array (shape vectors, pointer tables).
+ *   - Every entry point returns KUIOPS_OK (0) or a negative KUIOPS_E* code.
+ *     Contract violations are detected on the host and nothing is launched.
+ *   - Nothing here allocates, frees or synchronises.  Work is enqueued on
+ *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *   - Tensors are dense row-major unless a leading dimension is given.
+ *   - `status` parameters are optional device int32 words.  A kernel that meets
+ *     an out-of-range index skips that access and stores a non-zero code there.
+ *   - The library is re-entrant.  The only process-wide state is the driver
+ *     entry point used to encode TMA descriptors, resolved once under a mutex.
+ */
+#ifndef KUIOPS_H_
+#define KUIOPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KUIOPS_ABI_VERSION 1
+
+/* ---- return codes ------------------------------------------------------- */
+#define KUIOPS_OK             0
+#define KUIOPS_EINVAL        (-1)  /* a shape/stride/dtype contract does not hold     */
+#define KUIOPS_EUNSUPPORTED  (-2)  /* legal request outside what the kernels cover     */
+#define KUIOPS_EWORKSPACE    (-3)  /* workspace missing or smaller than *_workspace_bytes */
+#define KUIOPS_ELAUNCH       (-4)  /* the CUDA runtime refused the launch              */
+#define KUIOPS_EDRIVER       (-5)  /* TMA descriptor encoding failed                   */
+#define KUIOPS_ELIMIT        (-6)  /* size beyond a stated fixed maximum               */
+
+/* ---- element types ------------------------------------------------------ */
+#define KUIOPS_F32   0
+#define KUIOPS_BF16  1
+#define KUIOPS_F16   2
+
+typedef void* kuiops_stream_t;
+
+#if defined(__GNUC__)
+#define KUIOPS_API __attribute__((visibility("default")))
+#else
+#define KUIOPS_API
+#endif
+
+KUIOPS_API int         kuiops_abi_version(void);
+KUIOPS_API const char* kuiops_strerror(int code);
+/* Diagnostics for the tensor-core kernels, whose pipeline waits are bounded: copies the
+ * device-side error word to *host_out (0 = no wait ever ran out; otherwise the code of the
+ * wait that gave up) and optionally clears it.  Synchronises the device. */
+KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
+/* Number of kernels this library has enqueued since load (all threads). */
+KUIOPS_API uint64_t    kuiops_launch_count(void);
+
+/* ======================================================================== */
+/* GEMM family                                                              */
+/* ======================================================================== */
+
+/* General entry every GEMM-shaped op lowers to.
+ *   C[b] = alpha * A[b] x B[b] + beta * Cin[b]          (b = 0..batch-1)
+ * A is [M,K] with leading dimension lda.  B is [K,N] with leading dimension ldb
+ * when trans_b == 0, or is stored as [N,K] (the `weight.t()` view of a Linear
+ * layer) with leading dimension ldb when trans_b == 1.  Cin may be NULL (beta is
+ * then ignored); ldcin == 0 means Cin is a length-N row vector broadcast over
+ * rows (the fused bias of addmm).  Inputs are `dtype`; C is `out_dtype`
+ * (same as dtype, or KUIOPS_F32).  Accumulation is always fp32.
+ * bf16/f16 operands whose pointers are 16-byte aligned and whose leading
+ * dimensions are multiples of 8 run on the tcgen05 tensor-core kernels; M <= 64
+ * uses the weight-streaming split-K kernel with its in-kernel reduction.
+ * Everything else (fp32, odd strides) runs on the SIMT kernel.
+ * `workspace` must hold kuiops_gemm_workspace_bytes(...) bytes, and its first
+ * KUIOPS_GEMM_COUNTER_BYTES bytes must be zero the first time it is used; the
+ * kernels leave them zero.  Replaces the launchers at wrapper_mm.cu.j2:15-19,
+ * wrapper_addmm.cu.j2:18-24 and wrapper_bmm.cu.j2:16-20. */
+#define KUIOPS_GEMM_COUNTER_BYTES 16384
+KUIOPS_API size_t kuiops_gemm_workspace_bytes(int dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
+KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
+                uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, int64_t stride_a,
+                const void* B, int64_t ldb, int64_t stride_b, int trans_b,
+                const void* Cin, int64_t ldcin, int64_t stride_cin,
+                float alpha, float beta,
+                void* C, int64_t ldc, int64_t stride_c,
+                void* workspace, size_t workspace_bytes,
+                kuiops_stream_t stream);
+
+/* aten.mm: C[M,N] = A[M,K] x B[K,N], all dense row-major.
+ * Reference launcher: (u32 M, u32 N, u32 K, in* A, in* B, out* C), kuiops/mm/wrapper_mm.cu.j2:15-19.
+ * The reference's bf16 kernel writes fp32 and the Python side casts
+ * (kuipy/kuiops.py:428,467-468); here C has the input dtype. */
+KUIOPS_API int kuiops_mm_f32 (uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, void* C,
+                   void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_mm_bf16(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, void* C,
+                   void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_mm_f16 (uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, void* C,
+                   void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* aten.addmm with a full [M,N] C: C := beta*C + alpha*(A x B), in place on C
+ * (the caller passes a clone of the bias matrix, as the reference wrapper does).
+ * Reference launcher: (u32 M, u32 K, u32 N, et alpha, et beta, A, B, C) -- note
+ * the M,K,N order -- kuiops/addmm/wrapper_addmm.cu.j2:18-24. */
+KUIOPS_API int kuiops_addmm_f32 (uint32_t M, uint32_t K, uint32_t N, float alpha, float beta,
+                      const void* A, const void* B, void* C,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_addmm_bf16(uint32_t M, uint32_t K, uint32_t N, float alpha, float beta,
+                      const void* A, const void* B, void* C,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_addmm_f16 (uint32_t M, uint32_t K, uint32_t N, float alpha, float beta,
+                      const void* A, const void* B, void* C,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* aten.bmm: C[b] = A[b] x B[b].  Reference launcher: (u32 B, u32 M, u32 K, u32 N, A, B, C),
+ * kuiops/bmm/wrapper_bmm.cu.j2:16-20. */
+KUIOPS_API int kuiops_bmm_f32 (uint32_t batch, uint32_t M, uint32_t K, uint32_t N,
+                    const void* A, const void* B, void* C,
+                    void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_bmm_bf16(uint32_t batch, uint32_t M, uint32_t K, uint32_t N,
+                    const void* A, const void* B, void* C,
+                    void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_bmm_f16 (uint32_t batch, uint32_t M, uint32_t K, uint32_t N,
+                    const void* A, const void* B, void* C,
+                    void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* ======================================================================== */
+/* Scaled dot-product attention                                             */
+/* ======================================================================== */
+
+/* out = softmax(scale * Q K^T [+ bias] [causal mask]) V and the natural-log
+ * row log-sum-exp.  Q is (n, h, l, e), K is (n, h_kv, s, e), V is (n, h_kv, s, ev),
+ * out is (n, h, l, ev), lse (optional, fp32) is (n, h, l).  h must be a multiple
+ * of h_kv (grouped-query attention: query head i reads KV head i / (h / h_kv)).
+ * Strides are in elements for dims (batch, head, row); the innermost dim is
+ * contiguous.  `bias` (optional, same dtype, dense (n, h, l, s)) is added to the
+ * scaled scores as aten does.  With is_causal, query row i sees keys
+ * j <= i + (s - l) (bottom-right aligned, so decode with l == 1 sees the whole
+ * cache).  Reference launcher: (u32 n,h,l,s,e,ev, Q,K,V,bias, scale) returning
+ * kernel-allocated out/lse, kuiops/sdpa/wrapper_sdpa.cu.j2:21-27; extended with
+ * h_kv, is_causal, strides and caller-owned outputs.
+ * bf16/f16 with e == ev == 128, no bias and l >= 64 run on the tcgen05 flash
+ * kernel; short-query calls (l <= 8, decode) run on the split-KV kernel, which
+ * needs kuiops_sdpa_workspace_bytes(...) of workspace; the rest use the generic
+ * SIMT kernel. */
+KUIOPS_API size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
+                                   uint32_t l, uint32_t s, uint32_t e, uint32_t ev);
+KUIOPS_API int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
+                uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                const void* bias, float scale, int is_causal,
+                void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl,
+                float* lse,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* ======================================================================== */
+/* Streaming reductions                                                     */
+/* ======================================================================== */
+
+/* Row softmax of an [m, n] row-major matrix over n.  Y may equal X (the
+ * reference kernel is in place on the caller's clone).
+ * Reference launcher: (u32 m, u32 n, T* X), kuiops/softmax/wrapper_softmax.cu.j2:14-16. */
+KUIOPS_API int kuiops_softmax_f32 (uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
+KUIOPS_API int kuiops_softmax_bf16(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
+KUIOPS_API int kuiops_softmax_f16 (uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
+
+/* Last-axis mean with keepdim: out[i] = sum_j in[i,j] / n, fp32 accumulation.
+ * Reference launcher: (size_t m, size_t n, in*, out*), kuiops/mean/wrapper_mean.cu.j2:28-31. */
+KUIOPS_API int kuiops_mean_f32 (uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t stream);
+KUIOPS_API int kuiops_mean_bf16(uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t stream);
+KUIOPS_API int kuiops_mean_f16 (uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t stream);
+
+/* Whole-tensor folds to one device scalar (aten.all / aten.any over bool bytes,
+ * aten.max over int64 / fp32).  Reference: Kuiops.HReducePoly.Exact.reduce,
+ * kuiops/reduce/Kuiops.HReducePoly.Exact.fsti:26-46 (which mallocs the result
+ * and copies it to the host, .fst:1029-1036; here the scalar stays on the
+ * device at `out`).  workspace: KUIOPS_REDUCE_WORKSPACE_BYTES, first 8 bytes
+ * zero on first use and left zero. */
+#define KUIOPS_REDUCE_ALL 0
+#define KUIOPS_REDUCE_ANY 1
+#define KUIOPS_REDUCE_MAX 2
+#define KUIOPS_REDUCE_WORKSPACE_BYTES 16384
+KUIOPS_API int kuiops_reduce_u8 (int op, uint64_t n, const void* in, void* out,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_reduce_i64(int op, uint64_t n, const void* in, void* out,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+KUIOPS_API int kuiops_reduce_f32(int op, uint64_t n, const void* in, void* out,
+                      void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* aten.topk over the last axis of an [m, n] fp32 matrix, largest first.
+ * values is [m, k] fp32, indices [m, k] int64.  Equal values are ordered by
+ * ascending index, and NaN sorts above +inf (torch's ordering).  k <= 2048.
+ * No reference kernel exists (kuiops/topk/ is empty); signature from KERNELS.md:58. */
+KUIOPS_API int kuiops_topk_f32(uint32_t m, uint32_t n, uint32_t k, const void* X,
+                    void* values, int64_t* indices, kuiops_stream_t stream);
+
+/* ======================================================================== */
+/* Indexed data movement (payload moves: any element size 1, 2, 4, 8 bytes) */
+/* ======================================================================== */
+#define KUIOPS_MAX_RANK 8
+
+/* aten.gather: out[x] = inp[x with x[dim] := idx[x]], out has idx's shape.
+ * Contract (Kuiops.Common.fsti:34-38, Kuiops.Gather.fsti:31-33): equal ranks,
+ * idx_shape[d] <= inp_shape[d] for every d != dim, n == numel(idx) > 0 and every
+ * index value in [0, inp_shape[dim]).  The reference demands idx_shape <=
+ * inp_shape on `dim` too (kuipy/kuiops.py:736); that extra limit is kept in the
+ * Python gate, not here.  The int64 index is read directly (the reference
+ * narrows it to u32 with a strided copy first, include/kuiops.h:28-36).
+ * inp_shape / idx_shape are host arrays of `rank` entries.
+ * Reference launcher: (u32 inp dims.., u32 idx dims.., T* inp, u32* idx, T* out, u32 n),
+ * kuiops/gather/wrapper_gather.cu.j2:26-32. */
+KUIOPS_API int kuiops_gather(uint32_t elem_bytes, uint32_t rank, uint32_t dim,
+                  const uint64_t* inp_shape, const uint64_t* idx_shape,
+                  const void* inp, const int64_t* idx, void* out, uint64_t n,
+                  int32_t* status, kuiops_stream_t stream);
+
+/* aten.scatter.src: out = self; out[i with i[dim] := idx[i]] = src[i] for every
+ * cell i of src (src and idx share one shape <= self's shape pointwise).
+ * If self_ != out the library first copies self_ into out (the reference wrapper
+ * clones on the host side, wrapper_scatter.cu.j2:25).  Duplicate targets are a
+ * contract violation the kernel cannot see (Kuiops.Scatter.fsti:36-41): one of
+ * the writers wins, as in PyTorch.
+ * Reference launcher: (u32 self dims.., u32 src dims.., T* src, u32* idx, T* out, u32 n),
+ * kuiops/scatter/wrapper_scatter.cu.j2:30-36. */
+KUIOPS_API int kuiops_scatter(uint32_t elem_bytes, uint32_t rank, uint32_t dim,
+                   const uint64_t* self_shape, const uint64_t* src_shape,
+                   const void* self_, const void* src, const int64_t* idx, void* out, uint64_t n,
+                   int32_t* status, kuiops_stream_t stream);
+
+/* aten.cat of two tensors that agree off `dim`.
+ * Reference launcher: (u32 a dims.., u32 b_dim, T* A, T* B, T* out, u32 n),
+ * kuiops/cat/wrapper_cat.cu.j2:28-34; n must equal numel(out). */
+KUIOPS_API int kuiops_cat(uint32_t elem_bytes, uint32_t rank, uint32_t dim,
+               const uint64_t* a_shape, uint64_t b_dim,
+               const void* A, const void* B, void* out, uint64_t n,
+               kuiops_stream_t stream);
+
+/* N-ary cat: `count` tensors whose shapes equal `shape` except along `dim`,
+ * where tensor t has dim_sizes[t] entries.  ptrs and dim_sizes are host arrays.
+ * No reference counterpart (the reference kernel is binary only,
+ * kuipy/kuiops.py:822). */
+KUIOPS_API int kuiops_cat_n(uint32_t elem_bytes, uint32_t rank, uint32_t dim, uint32_t count,
+                 const uint64_t* shape, const uint64_t* dim_sizes,
+                 const void* const* ptrs, void* out, kuiops_stream_t stream);
+
+/* aten.index.Tensor with `n_idx` int64 index tensors applied to the adjacent
+ * dims [first_dim, first_dim + n_idx) of a dense `self`.  The index tensors are
+ * already broadcast to one shape idx_shape[idx_rank]; idx_strides holds
+ * n_idx * idx_rank element strides (0 on broadcast dims).  Output shape is
+ * self_shape[:first_dim] + idx_shape + self_shape[first_dim + n_idx:].
+ * Negative indices wrap once; out-of-range ones are skipped and flagged.
+ * idx_ptrs is a host array of device pointers.  No reference kernel exists
+ * (kuiops/index/ is empty); signature from KERNELS.md:67. */
+KUIOPS_API int kuiops_index(uint32_t elem_bytes, uint32_t self_rank, const uint64_t* self_shape,
+                 uint32_t first_dim, uint32_t n_idx, const int64_t* const* idx_ptrs,
+                 uint32_t idx_rank, const uint64_t* idx_shape, const int64_t* idx_strides,
+                 const void* self_, void* out, int32_t* status, kuiops_stream_t stream);
+
+/* aten.isin(elements int64[n], test_elements int64[m]) -> bool bytes [n].
+ * No reference kernel exists (kuiops/isin/ is empty); signature from KERNELS.md:56-57. */
+KUIOPS_API int kuiops_isin_i64(uint64_t n, const int64_t* elements, uint64_t m, const int64_t* test_elements,
+                    int invert, void* out, kuiops_stream_t stream);
+
+/* ======================================================================== */
+/* Elementwise maps                                                         */
+/* ======================================================================== */
+/* The reference bakes the lambda and its constants into each instantiation
+ * (kuipy/kuiops.py:292-296); here `op` selects it and `c0`, `c1` carry the
+ * constants.  Y may equal X (the reference kernels are in place on a clone).
+ * Reference launchers, kuiops/elementwise/wrapper_elementwise.cu.j2:20-42:
+ *   map(len, T*), map2(len, T*, T*), map_nip(len, Tin*, Tout*), map3(len, u8*, T*, T*, T*). */
+#define KUIOPS_MAP_SILU     0
+#define KUIOPS_MAP_NEG      1
+#define KUIOPS_MAP_RSQRT    2
+#define KUIOPS_MAP_COS      3
+#define KUIOPS_MAP_SIN      4
+#define KUIOPS_MAP_POW      5   /* x ** c0                    */
+#define KUIOPS_MAP_SQUARE   6   /* x * x  (the x**2 special case, kuiops.py:270-273) */
+#define KUIOPS_MAP_ADD      7   /* x + c1 * (y | c0)          */
+#define KUIOPS_MAP_MUL      8   /* x * (y | c0)               */
+#define KUIOPS_MAP_SUB      9   /* x - c1 * (y | c0)          */
+#define KUIOPS_MAP_DIV     10   /* x / (y | c0)               */
+#define KUIOPS_MAP_BNOT    11   /* bool bytes                 */
+#define KUIOPS_MAP_BAND    12
+#define KUIOPS_MAP_BOR     13
+#define KUIOPS_MAP_EQ      14   /* x == c0 -> bool byte       */
+#define KUIOPS_MAP_LE      15
+#define KUIOPS_MAP_LT      16
+#define KUIOPS_MAP_GELU    17   /* tanh-free erf GELU, for the GPT-2-shaped config */
+/* Unary map, or binary with a scalar constant: Y[i] = op(X[i], c0, c1). */
+KUIOPS_API int kuiops_map (int dtype, int op, uint64_t len, const void* X, void* Y, double c0, double c1,
+                kuiops_stream_t stream);
+/* Binary same-shape map: Y[i] = op(X[i], B[i]); c1 is the `alpha` of add/sub. */
+KUIOPS_API int kuiops_map2(int dtype, int op, uint64_t len, const void* X, const void* B, void* Y, double c1,
+                kuiops_stream_t stream);
+/* Bool-byte maps (bitwise_not / and / or).  B is ignored for BNOT. */
+KUIOPS_API int kuiops_map_u8(int op, uint64_t len, const void* X, const void* B, void* Y,
+                  kuiops_stream_t stream);
+/* Scalar comparisons, float in -> bool byte out. */
+KUIOPS_API int kuiops_map_nip(int dtype, int op, uint64_t len, const void* X, void* Y, double c0,
+                   kuiops_stream_t stream);
+/* where(cond, a, b) with payload elements of elem_bytes. */
+KUIOPS_API int kuiops_map3(uint32_t elem_bytes, uint64_t len, const void* cond, const void* A, const void* B,
+                void* Y, kuiops_stream_t stream);
+
+/* ======================================================================== */
+/* Fused decoder-layer helpers (compositions of the maps above that the      */
+/* dispatcher sees as pow/mean/add/rsqrt/mul, silu/mul, mul/cat/neg/add)     */
+/* ======================================================================== */
+
+/* y = (x [+ residual]) * rsqrt(mean((x [+ residual])^2) + eps) * weight, rows of
+ * length n.  When residual != NULL, the sum is also written to residual_out
+ * (may alias residual).  fp32 statistics. */
+KUIOPS_API int kuiops_rmsnorm(int dtype, uint64_t m, uint32_t n, const void* x, const void* residual,
+                   const void* weight, float eps, void* y, void* residual_out,
+                   kuiops_stream_t stream);
+/* y[i, j] = silu(gu[i, j]) * gu[i, n + j] for a fused [m, 2n] gate|up matrix. */
+KUIOPS_API int kuiops_swiglu(int dtype, uint64_t m, uint32_t n, const void* gate_up, void* y,
+                  kuiops_stream_t stream);
+/* Rotary embedding (rotate-half form) applied in place to q (rows, hq, d) and
+ * k (rows, hk, d) slices of a packed qkv row of `row_stride` elements; positions
+ * is int64 [rows]; theta is the base.  Also appends the rotated k and the raw v
+ * of each row to a (batch, hk, cap, d) cache at slot positions[row] when
+ * k_cache != NULL; rows_per_seq consecutive rows belong to one sequence. */
+KUIOPS_API int kuiops_rope_qkv(int dtype, uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d,
+                    void* qkv, int64_t row_stride, const int64_t* positions, float theta,
+                    void* k_cache, void* v_cache, uint64_t cache_cap, uint32_t rows_per_seq,
+                    kuiops_stream_t stream);
+/* out[r, :] = table[ids[r], :] (aten.embedding), row length `width` elements. */
+KUIOPS_API int kuiops_embedding(uint32_t elem_bytes, uint64_t rows, uint64_t width, uint64_t vocab,
+                     const void* table, const int64_t* ids, void* out, int32_t* status,
+                     kuiops_stream_t stream);
+/* Row arg-max of an [m, n] matrix (greedy sampling); ties -> lowest index. */
+KUIOPS_API int kuiops_argmax(int dtype, uint64_t m, uint64_t n, const void* X, int64_t* out,
+                  kuiops_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KUIOPS_H_ */

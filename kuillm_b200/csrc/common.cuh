@@ -1,0 +1,104 @@
+// Shared device/host helpers for the kuiops sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <atomic>
+#include "../../include/kuiops.h"
+
+namespace kuiops {
+
+constexpr int kNumSMs = 148;           // B200: 2 dies x 74 SMs
+constexpr int kWarp = 32;
+
+extern std::atomic<uint64_t> g_launches;
+
+inline int check_launch() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaPeekAtLastError() == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+}
+
+inline cudaStream_t as_stream(kuiops_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct ElemTraits<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+// 16-byte vector of T, the unit of every coalesced HBM access here.
+template <typename T> struct alignas(16) Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16(const T* p) {
+  return *reinterpret_cast<const Vec16<T>*>(p);
+}
+// Streaming load: data read exactly once, keep it out of L1.
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16_stream(const T* p) {
+  Vec16<T> r;
+  int4 raw = __ldcs(reinterpret_cast<const int4*>(p));
+  *reinterpret_cast<int4*>(&r) = raw;
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void st16(T* p, const Vec16<T>& v) {
+  *reinterpret_cast<Vec16<T>*>(p) = v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide reductions over <= 32 warps; `red` is a 32-float shared scratch.
+// Every thread returns the full result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Grid size for grid-stride streaming kernels: whole multiples of the SM count.
+inline unsigned stream_grid(uint64_t work_items, unsigned per_block, unsigned max_waves = 8) {
+  uint64_t blocks = (work_items + per_block - 1) / per_block;
+  uint64_t cap = uint64_t(kNumSMs) * max_waves;
+  if (blocks >= cap) return unsigned(cap);
+  if (blocks > unsigned(kNumSMs)) blocks = ((blocks + kNumSMs - 1) / kNumSMs) * kNumSMs;
+  return unsigned(blocks ? blocks : 1);
+}
+
+}  // namespace kuiops

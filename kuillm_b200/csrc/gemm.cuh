@@ -1,0 +1,25 @@
+// Argument block shared by the GEMM kernels.
+#pragma once
+#include "common.cuh"
+
+namespace kuiops {
+
+struct GemmArgs {
+  int dtype, out_dtype;
+  uint32_t batch, M, N, K;
+  const void* A; int64_t lda, stride_a;
+  const void* B; int64_t ldb, stride_b; int trans_b;
+  const void* Cin; int64_t ldcin, stride_cin;
+  float alpha, beta;
+  void* C; int64_t ldc, stride_c;
+};
+
+// SIMT kernel: any dtype / shape / stride.
+int gemm_simt(const GemmArgs& a, cudaStream_t st);
+// tcgen05 kernel: bf16 / f16, 16-byte aligned operands.  Returns KUIOPS_EUNSUPPORTED when the
+// operands do not meet the TMA alignment rules so the caller can fall back to gemm_simt.
+bool gemm_tc_eligible(const GemmArgs& a);
+size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
+int gemm_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+
+}  // namespace kuiops

@@ -1,0 +1,90 @@
+// C-ABI entry points of the GEMM family and the library-wide helpers.
+#include "gemm.cuh"
+#include "tc_ptx.cuh"
+
+namespace kuiops {
+std::atomic<uint64_t> g_launches{0};
+}
+using namespace kuiops;
+
+extern "C" {
+
+int kuiops_abi_version(void) { return KUIOPS_ABI_VERSION; }
+
+uint64_t kuiops_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* kuiops_strerror(int code) {
+  switch (code) {
+    case KUIOPS_OK: return "ok";
+    case KUIOPS_EINVAL: return "kuiops: a shape, stride or dtype contract does not hold";
+    case KUIOPS_EUNSUPPORTED: return "kuiops: request outside what the kernels cover";
+    case KUIOPS_EWORKSPACE: return "kuiops: workspace missing or too small";
+    case KUIOPS_ELAUNCH: return "kuiops: CUDA launch failed";
+    case KUIOPS_EDRIVER: return "kuiops: TMA descriptor encoding failed";
+    case KUIOPS_ELIMIT: return "kuiops: size beyond a fixed maximum";
+  }
+  return "kuiops: unknown error";
+}
+
+int kuiops_debug_tc_error(unsigned int* host_out, int reset) {
+  unsigned int* dev = tc_error_word_device();
+  if (!dev || !host_out) return KUIOPS_EINVAL;
+  if (cudaMemcpy(host_out, dev, sizeof(unsigned int), cudaMemcpyDeviceToHost) != cudaSuccess) return KUIOPS_ELAUNCH;
+  if (reset && *host_out) {
+    unsigned int zero = 0;
+    if (cudaMemcpy(dev, &zero, sizeof(zero), cudaMemcpyHostToDevice) != cudaSuccess) return KUIOPS_ELAUNCH;
+  }
+  return KUIOPS_OK;
+}
+
+size_t kuiops_gemm_workspace_bytes(int dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K) {
+  if (dtype == KUIOPS_F32) return KUIOPS_GEMM_COUNTER_BYTES;
+  return gemm_tc_workspace_bytes(batch, M, N, K);
+}
+
+int kuiops_gemm(int dtype, int out_dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, int64_t stride_a,
+                const void* B, int64_t ldb, int64_t stride_b, int trans_b,
+                const void* Cin, int64_t ldcin, int64_t stride_cin,
+                float alpha, float beta,
+                void* C, int64_t ldc, int64_t stride_c,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
+  if (dtype != KUIOPS_F32 && dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EINVAL;
+  if (out_dtype != dtype && out_dtype != KUIOPS_F32) return KUIOPS_EINVAL;
+  if (batch == 0 || M == 0 || N == 0 || K == 0) return KUIOPS_EINVAL;
+  if (!A || !B || !C) return KUIOPS_EINVAL;
+  if (lda < int64_t(K) || ldc < int64_t(N)) return KUIOPS_EINVAL;
+  if (ldb < int64_t(trans_b ? K : N)) return KUIOPS_EINVAL;
+  if (Cin && ldcin != 0 && ldcin < int64_t(N)) return KUIOPS_EINVAL;
+  GemmArgs a;
+  a.dtype = dtype; a.out_dtype = out_dtype; a.batch = batch; a.M = M; a.N = N; a.K = K;
+  a.A = A; a.lda = lda; a.stride_a = stride_a;
+  a.B = B; a.ldb = ldb; a.stride_b = stride_b; a.trans_b = trans_b ? 1 : 0;
+  a.Cin = Cin; a.ldcin = ldcin; a.stride_cin = stride_cin;
+  a.alpha = alpha; a.beta = Cin ? beta : 0.f;
+  a.C = C; a.ldc = ldc; a.stride_c = stride_c;
+  cudaStream_t st = as_stream(stream);
+  if (gemm_tc_eligible(a)) return gemm_tc(a, workspace, workspace_bytes, st);
+  return gemm_simt(a, st);
+}
+
+#define KUIOPS_GEMM_ENTRIES(SUFFIX, DT)                                                                             \
+  int kuiops_mm_##SUFFIX(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, void* C, void* ws,       \
+                         size_t wsb, kuiops_stream_t s) {                                                           \
+    return kuiops_gemm(DT, DT, 1, M, N, K, A, K, 0, B, N, 0, 0, nullptr, 0, 0, 1.f, 0.f, C, N, 0, ws, wsb, s);      \
+  }                                                                                                                 \
+  int kuiops_addmm_##SUFFIX(uint32_t M, uint32_t K, uint32_t N, float alpha, float beta, const void* A,             \
+                            const void* B, void* C, void* ws, size_t wsb, kuiops_stream_t s) {                      \
+    return kuiops_gemm(DT, DT, 1, M, N, K, A, K, 0, B, N, 0, 0, C, N, 0, alpha, beta, C, N, 0, ws, wsb, s);         \
+  }                                                                                                                 \
+  int kuiops_bmm_##SUFFIX(uint32_t batch, uint32_t M, uint32_t K, uint32_t N, const void* A, const void* B,         \
+                          void* C, void* ws, size_t wsb, kuiops_stream_t s) {                                       \
+    return kuiops_gemm(DT, DT, batch, M, N, K, A, K, int64_t(M) * K, B, N, int64_t(K) * N, 0, nullptr, 0, 0, 1.f,   \
+                       0.f, C, N, int64_t(M) * N, ws, wsb, s);                                                      \
+  }
+
+KUIOPS_GEMM_ENTRIES(f32, KUIOPS_F32)
+KUIOPS_GEMM_ENTRIES(bf16, KUIOPS_BF16)
+KUIOPS_GEMM_ENTRIES(f16, KUIOPS_F16)
+
+}  // extern "C"

@@ -1,0 +1,436 @@
+// tcgen05 GEMM for bf16 / f16 operands with fp32 accumulation in tensor memory.
+//
+// One kernel template serves two operand placements.  The 128 TMEM lanes carry the "P" operand
+// and the BN TMEM columns the "Q" operand:
+//   * normal  (M > 128): P = A rows (m), Q = B columns (n); persistent CTAs walk 128 x BN tiles
+//     with two accumulator stages so the epilogue of a tile overlaps the MMAs of the next.
+//   * swapped (M <= 128, decode shapes): P = B columns (n, the weight rows that have to be
+//     streamed from HBM), Q = A rows (m, padded to 16..128).  K is split over several CTAs per
+//     tile so that every SM streams weights; the fp32 partials meet in the workspace and the
+//     CTA that draws the last ticket of a tile reduces them in split order and runs the
+//     epilogue (in-kernel reduction, deterministic).
+// Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocator + UMMA issuer (one
+// lane), warps 2..5 = epilogue (TMEM -> registers -> alpha/beta/bias -> global).
+// Operands arrive through 3-D tensor maps (inner, rows, batch) with 128-byte swizzle; edges in
+// M, N and K rely on TMA zero fill, so no divisibility is required beyond the 16-byte stride
+// rule.  Replaces Klas.GEMM.TensorCore2D (wmma fragments, kuiops/mm/Kuiops.Mm.Inst.fst.j2:9-11).
+#include "gemm.cuh"
+#include "tc_ptx.cuh"
+#include <mutex>
+#include <type_traits>
+
+namespace kuiops {
+
+constexpr int TBM = 128;   // TMEM lanes = rows of the P operand per tile
+constexpr int TBK = 64;    // K elements per pipeline stage (one 128-byte swizzle span)
+constexpr int kTcThreads = 192;
+
+struct TcParams {
+  uint32_t rowsP, rowsQ, K, batch;
+  uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split;
+  int swapped, out_f32;
+  uint32_t M, N;
+  float alpha, beta;
+  const void* Cin; int64_t ldcin, stride_cin;
+  void* C; int64_t ldc, stride_c;
+  float* partials; int* counters; unsigned int* err;
+};
+
+__device__ unsigned int g_tc_error = 0;
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait on an mbarrier phase for at most ~2 s of wall time.
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity) {
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  while (!tc::mbar_try_wait(bar, parity)) {
+    if (global_ns() - t0 > 2000000000ull) return false;
+  }
+  return true;
+}
+
+template <typename TIN>
+__device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32_t lane_row, uint32_t col, float acc) {
+  const uint32_t m = p.swapped ? col : lane_row;
+  const uint32_t n = p.swapped ? lane_row : col;
+  if (m >= p.M || n >= p.N) return;
+  float v = p.alpha * acc;
+  if (p.Cin) {
+    const TIN* cin = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin;
+    v += p.beta * ElemTraits<TIN>::to_f(cin[size_t(m) * p.ldcin + n]);
+  }
+  const size_t off = size_t(b) * p.stride_c + size_t(m) * p.ldc + n;
+  if (p.out_f32) static_cast<float*>(p.C)[off] = v;
+  else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
+}
+
+template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
+               const TcParams p) {
+  constexpr uint32_t P_BYTES = TBM * TBK * 2;
+  constexpr uint32_t Q_BYTES = BN * TBK * 2;
+  constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
+  constexpr uint32_t TMEM_COLS = (ACC_STAGES * BN) < 32 ? 32 : (ACC_STAGES * BN);
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+  static_assert(!Q_MN || BN % 64 == 0, "an MN-major Q tile is loaded in 64-element boxes");
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle atoms need
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < ACC_STAGES; ++s) { tc::mbar_init(&acc_full[s], 1); tc::mbar_init(&acc_empty[s], 4); }
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmapP);
+    tc::prefetch_tmap(&tmapQ);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
+  const uint32_t units = tiles_per_batch * p.batch * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const uint32_t split = u % p.splits, tile = u / p.splits;
+        const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
+        const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+        const uint32_t kb0 = split * p.kb_per_split;
+        const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!bounded_wait(&empty_bar[s], ph ^ 1)) { atomicExch(p.err, 1u); ok = false; break; }
+          unsigned char* ps = smem + s * STAGE_BYTES;
+          unsigned char* qs = ps + P_BYTES;
+          tc::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k0 = int(kb * TBK);
+          if (P_MN) {
+#pragma unroll
+            for (int j = 0; j < TBM / 64; ++j)
+              tc::tma_load_3d(ps + j * (TBK * 128), &tmapP, &full_bar[s], int(tp * TBM) + j * 64, k0, int(b));
+          } else {
+            tc::tma_load_3d(ps, &tmapP, &full_bar[s], k0, int(tp * TBM), int(b));
+          }
+          if (Q_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tc::tma_load_3d(qs + j * (TBK * 128), &tmapQ, &full_bar[s], int(tq * BN) + j * 64, k0, int(b));
+          } else {
+            tc::tma_load_3d(qs, &tmapQ, &full_bar[s], k0, int(tq * BN), int(b));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ UMMA issuer -------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc(std::is_same<TIN, __nv_bfloat16>::value ? 1 : 0, P_MN ? 1 : 0, Q_MN ? 1 : 0, TBM, BN);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++acc_it) {
+        const uint32_t split = u % p.splits;
+        const uint32_t kb0 = split * p.kb_per_split;
+        const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
+        const uint32_t as = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1;
+        if (!bounded_wait(&acc_empty[as], aph ^ 1)) { atomicExch(p.err, 2u); ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!bounded_wait(&full_bar[s], ph)) { atomicExch(p.err, 3u); ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t pa = tc::smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t qa = pa + P_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < TBK / 16; ++kk) {
+            // K-major: 16 elements = 32 bytes inside the swizzle span, 8-row groups 1024 B apart.
+            // MN-major: 16 k-rows = 2048 B, 8-row groups 1024 B apart, 64-element column blocks
+            // TBK * 128 B apart.
+            const uint64_t da = P_MN ? tc::make_smem_desc(pa + kk * 2048, TBK * 128, 1024)
+                                     : tc::make_smem_desc(pa + kk * 32, 16, 1024);
+            const uint64_t db = Q_MN ? tc::make_smem_desc(qa + kk * 2048, TBK * 128, 1024)
+                                     : tc::make_smem_desc(qa + kk * 32, 16, 1024);
+            tc::umma_f16(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          tc::umma_commit(&empty_bar[s]);     // stage may be refilled once these MMAs have read it
+        }
+        if (ok) tc::umma_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------------------
+    const uint32_t quarter = warp & 3;                    // TMEM lanes this warp may touch
+    const uint32_t lane_in_tile = quarter * 32 + lane;
+    const uint32_t epi_tid = threadIdx.x - 64;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++acc_it) {
+      const uint32_t split = u % p.splits, tile = u / p.splits;
+      const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
+      const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+      const uint32_t as = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1;
+      if (!bounded_wait(&acc_full[as], aph)) { atomicExch(p.err, 4u); ok = false; break; }
+      tc::tc_fence_after();
+      const uint32_t taddr = tmem_base + as * BN + ((quarter * 32) << 16);
+      const uint32_t row = tp * TBM + lane_in_tile;
+      const uint32_t col0 = tq * BN;
+      // columns beyond the Q extent hold zeros (TMA fill) and are never stored
+      const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
+      float v[16];
+      if (p.splits == 1) {
+        for (uint32_t c = 0; c < ncols; c += 16) {
+          tc::tmem_ld16(taddr + c, v);
+          tc::tmem_ld_wait();
+          bool vec_done = false;
+          if (!p.swapped && !p.out_f32 && !p.Cin && row < p.M && col0 + c + 16 <= p.N &&
+              (p.ldc % 8 == 0) && (p.stride_c % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0)) {
+            // 16 consecutive outputs of one row: two 16-byte stores
+            TIN* dst = static_cast<TIN*>(p.C) + size_t(b) * p.stride_c + size_t(row) * p.ldc + col0 + c;
+            Vec16<TIN> o0, o1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { o0.v[j] = ElemTraits<TIN>::from_f(p.alpha * v[j]); o1.v[j] = ElemTraits<TIN>::from_f(p.alpha * v[8 + j]); }
+            st16(dst, o0);
+            st16(dst + 8, o1);
+            vec_done = true;
+          }
+          if (!vec_done) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j]);
+          }
+        }
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&acc_empty[as]);
+      } else {
+        // split-K: park the fp32 partial, then the last split to arrive reduces the tile
+        float* part = p.partials + (size_t(tile) * p.splits + split) * (size_t(BN) * TBM);
+        for (uint32_t c = 0; c < ncols; c += 16) {
+          tc::tmem_ld16(taddr + c, v);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) __stcg(&part[size_t(c + j) * TBM + lane_in_tile], v[j]);
+        }
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&acc_empty[as]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0) {
+          const int old = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (old == int(p.splits) - 1) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* base = p.partials + size_t(tile) * p.splits * (size_t(BN) * TBM);
+          for (uint32_t c = 0; c < ncols; ++c) {
+            float sum = 0.f;
+            for (uint32_t s2 = 0; s2 < p.splits; ++s2)
+              sum += __ldcg(&base[size_t(s2) * (size_t(BN) * TBM) + size_t(c) * TBM + lane_in_tile]);
+            store_elem<TIN>(p, b, row, col0 + c, sum);
+          }
+          if (epi_tid == 0) p.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+  // ------------------------------ teardown ------------------------------------------------
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+bool encode_tmap_2byte(CUtensorMap* map, const void* base, uint32_t rank, const uint64_t* dims,
+                       const uint64_t* strides_elems, const uint32_t* box) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  if (!g_encode) return false;
+  cuuint64_t gdim[5], gstride[4];
+  cuuint32_t gbox[5], estride[5];
+  for (uint32_t i = 0; i < rank; ++i) { gdim[i] = dims[i]; gbox[i] = box[i]; estride[i] = 1; }
+  for (uint32_t i = 1; i < rank; ++i) gstride[i - 1] = strides_elems[i] * 2;
+  // bf16 and f16 move identically; the type only matters for OOB fill, which is zero
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdim, gstride, gbox,
+                        estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+unsigned int* tc_error_word_device() {
+  unsigned int* ptr = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_tc_error) != cudaSuccess) return nullptr;
+  return ptr;
+}
+
+bool gemm_tc_eligible(const GemmArgs& a) {
+  if (a.dtype != KUIOPS_BF16 && a.dtype != KUIOPS_F16) return false;
+  if (a.M == 0 || a.N == 0 || a.K == 0 || a.batch == 0) return false;
+  if (!aligned16(a.A) || !aligned16(a.B)) return false;
+  if (a.lda % 8 || a.ldb % 8) return false;
+  if (a.batch > 1 && (a.stride_a % 8 || a.stride_b % 8)) return false;
+  // tensor-map extents are 32-bit boxes over 64-bit dims; strides must stay below 2^40 bytes
+  if (uint64_t(a.lda) * 2 >= (1ull << 40) || uint64_t(a.ldb) * 2 >= (1ull << 40)) return false;
+  return true;
+}
+
+struct TcPlan { bool swapped; int bn; uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split; };
+
+static TcPlan make_plan(const GemmArgs& a) {
+  TcPlan pl = {};
+  pl.kblocks = (a.K + TBK - 1) / TBK;
+  pl.swapped = a.M <= 128;
+  if (pl.swapped) {
+    pl.bn = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128));
+    pl.tilesP = (a.N + TBM - 1) / TBM;
+    pl.tilesQ = 1;
+  } else {
+    pl.bn = a.N > 128 ? 256 : 128;
+    pl.tilesP = (a.M + TBM - 1) / TBM;
+    pl.tilesQ = (a.N + pl.bn - 1) / pl.bn;
+  }
+  const uint64_t tiles = uint64_t(pl.tilesP) * pl.tilesQ * a.batch;
+  pl.splits = 1;
+  if (pl.swapped && tiles < 2 * uint64_t(kNumSMs) && tiles <= KUIOPS_GEMM_COUNTER_BYTES / 4) {
+    uint32_t want = uint32_t((2 * uint64_t(kNumSMs) + tiles - 1) / tiles);
+    uint32_t cap = pl.kblocks / 8;                 // keep at least 8 k-blocks (512 of K) per split
+    if (cap < 1) cap = 1;
+    pl.splits = want < cap ? want : cap;
+    if (pl.splits > 32) pl.splits = 32;
+  }
+  pl.kb_per_split = (pl.kblocks + pl.splits - 1) / pl.splits;
+  pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;   // no empty split
+  return pl;
+}
+
+size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K) {
+  GemmArgs a = {};
+  a.batch = batch ? batch : 1; a.M = M; a.N = N; a.K = K;
+  TcPlan pl = make_plan(a);
+  size_t bytes = KUIOPS_GEMM_COUNTER_BYTES;
+  if (pl.splits > 1)
+    bytes += size_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits * size_t(pl.bn) * TBM * sizeof(float);
+  return bytes;
+}
+
+template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
+static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, unsigned grid, cudaStream_t st) {
+  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256;
+  auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
+  // per-device attribute; cheap enough to set on every call and safe with several devices
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    return KUIOPS_ELAUNCH;
+  kern<<<grid, kTcThreads, smem, st>>>(mp, mq, p);
+  return check_launch();
+}
+
+template <typename TIN>
+static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  const TcPlan pl = make_plan(a);
+  if (pl.splits > 1) {
+    if (!workspace || workspace_bytes < gemm_tc_workspace_bytes(a.batch, a.M, a.N, a.K)) return KUIOPS_EWORKSPACE;
+  }
+  // Tensor maps.  "Rows" of an operand are the index that is NOT K.
+  // A is always K-major: dims (K, M, batch).  B is K-major when trans_b (stored [N, K]) and
+  // MN-major otherwise (stored [K, N]: dims (N, K, batch)).
+  CUtensorMap mapA, mapB;
+  const uint32_t a_box_rows = pl.swapped ? uint32_t(pl.bn) : uint32_t(TBM);
+  {
+    const uint64_t dims[3] = {a.K, a.M, a.batch};
+    const uint64_t strides[3] = {1, uint64_t(a.lda), uint64_t(a.batch > 1 ? a.stride_a : int64_t(a.lda) * a.M)};
+    const uint32_t box[3] = {TBK, a_box_rows, 1};
+    if (!encode_tmap_2byte(&mapA, a.A, 3, dims, strides, box)) return KUIOPS_EDRIVER;
+  }
+  const uint32_t b_box_rows = pl.swapped ? uint32_t(TBM) : uint32_t(pl.bn);
+  if (a.trans_b) {
+    const uint64_t dims[3] = {a.K, a.N, a.batch};
+    const uint64_t strides[3] = {1, uint64_t(a.ldb), uint64_t(a.batch > 1 ? a.stride_b : int64_t(a.ldb) * a.N)};
+    const uint32_t box[3] = {TBK, b_box_rows, 1};
+    if (!encode_tmap_2byte(&mapB, a.B, 3, dims, strides, box)) return KUIOPS_EDRIVER;
+  } else {
+    const uint64_t dims[3] = {a.N, a.K, a.batch};
+    const uint64_t strides[3] = {1, uint64_t(a.ldb), uint64_t(a.batch > 1 ? a.stride_b : int64_t(a.ldb) * a.K)};
+    const uint32_t box[3] = {64, TBK, 1};
+    if (!encode_tmap_2byte(&mapB, a.B, 3, dims, strides, box)) return KUIOPS_EDRIVER;
+  }
+  TcParams p = {};
+  p.K = a.K; p.batch = a.batch;
+  p.tilesP = pl.tilesP; p.tilesQ = pl.tilesQ; p.splits = pl.splits; p.kblocks = pl.kblocks; p.kb_per_split = pl.kb_per_split;
+  p.swapped = pl.swapped ? 1 : 0; p.out_f32 = a.out_dtype == KUIOPS_F32 ? 1 : 0;
+  p.M = a.M; p.N = a.N;
+  p.rowsP = pl.swapped ? a.N : a.M; p.rowsQ = pl.swapped ? a.M : a.N;
+  p.alpha = a.alpha; p.beta = a.beta;
+  p.Cin = a.Cin; p.ldcin = a.ldcin; p.stride_cin = a.stride_cin;
+  p.C = a.C; p.ldc = a.ldc; p.stride_c = a.stride_c;
+  p.counters = static_cast<int*>(workspace);
+  p.partials = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + KUIOPS_GEMM_COUNTER_BYTES) : nullptr;
+  p.err = tc_error_word_device();
+  if (!p.err) return KUIOPS_ELAUNCH;
+  const uint64_t units = uint64_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits;
+  if (units >= (1ull << 31)) return KUIOPS_EUNSUPPORTED;
+  const bool b_mn = !a.trans_b;
+  if (pl.swapped) {
+    // one unit per CTA so several small CTAs share an SM and keep more loads in flight
+    const unsigned grid = unsigned(units);
+    const CUtensorMap& mp = mapB; const CUtensorMap& mq = mapA;
+#define KUIOPS_SW(BNV)                                                                             \
+  case BNV: return b_mn ? launch_tc<TIN, BNV, 4, 1, true, false>(mp, mq, p, grid, st)              \
+                        : launch_tc<TIN, BNV, 4, 1, false, false>(mp, mq, p, grid, st);
+    switch (pl.bn) { KUIOPS_SW(16) KUIOPS_SW(32) KUIOPS_SW(64) KUIOPS_SW(128) }
+#undef KUIOPS_SW
+    return KUIOPS_EUNSUPPORTED;
+  }
+  const unsigned grid = unsigned(units < uint64_t(kNumSMs) ? units : uint64_t(kNumSMs));
+  if (pl.bn == 256)
+    return b_mn ? launch_tc<TIN, 256, 4, 2, false, true>(mapA, mapB, p, grid, st)
+                : launch_tc<TIN, 256, 4, 2, false, false>(mapA, mapB, p, grid, st);
+  return b_mn ? launch_tc<TIN, 128, 6, 2, false, true>(mapA, mapB, p, grid, st)
+              : launch_tc<TIN, 128, 6, 2, false, false>(mapA, mapB, p, grid, st);
+}
+
+int gemm_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  if (a.dtype == KUIOPS_BF16) return gemm_tc_typed<__nv_bfloat16>(a, workspace, workspace_bytes, st);
+  return gemm_tc_typed<__half>(a, workspace, workspace_bytes, st);
+}
+
+}  // namespace kuiops

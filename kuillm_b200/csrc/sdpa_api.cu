@@ -1,0 +1,46 @@
+// C-ABI entry point of scaled dot-product attention: contract checks and kernel choice.
+#include "sdpa.cuh"
+
+using namespace kuiops;
+
+static int fill_args(SdpaArgs& a, int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e,
+                     uint32_t ev) {
+  if (dtype != KUIOPS_F32 && dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EINVAL;
+  if (n == 0 || h == 0 || h_kv == 0 || l == 0 || s == 0 || e == 0 || ev == 0) return KUIOPS_EINVAL;
+  if (h % h_kv) return KUIOPS_EINVAL;
+  a.dtype = dtype; a.n = n; a.h = h; a.h_kv = h_kv; a.l = l; a.s = s; a.e = e; a.ev = ev;
+  return KUIOPS_OK;
+}
+
+extern "C" {
+
+size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s,
+                                   uint32_t e, uint32_t ev) {
+  SdpaArgs a = {};
+  if (fill_args(a, dtype, n, h, h_kv, l, s, e, ev) != KUIOPS_OK) return 0;
+  return sdpa_rows_workspace_bytes(a);
+}
+
+int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                const void* bias, float scale, int is_causal,
+                void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl, float* lse,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
+  SdpaArgs a = {};
+  int rc = fill_args(a, dtype, n, h, h_kv, l, s, e, ev);
+  if (rc != KUIOPS_OK) return rc;
+  if (!Q || !K || !V || !out) return KUIOPS_EINVAL;
+  if (q_sl < int64_t(e) || k_ss < int64_t(e) || v_ss < int64_t(ev) || o_sl < int64_t(ev)) return KUIOPS_EINVAL;
+  a.Q = Q; a.q_sn = q_sn; a.q_sh = q_sh; a.q_sl = q_sl;
+  a.K = K; a.k_sn = k_sn; a.k_sh = k_sh; a.k_ss = k_ss;
+  a.V = V; a.v_sn = v_sn; a.v_sh = v_sh; a.v_ss = v_ss;
+  a.bias = bias; a.scale = scale; a.is_causal = is_causal ? 1 : 0;
+  a.out = out; a.o_sn = o_sn; a.o_sh = o_sh; a.o_sl = o_sl; a.lse = lse;
+  cudaStream_t st = as_stream(stream);
+  if (sdpa_flash_eligible(a)) return sdpa_flash(a, st);
+  return sdpa_rows(a, workspace, workspace_bytes, st);
+}
+
+}  // extern "C"

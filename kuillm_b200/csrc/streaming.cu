@@ -1,0 +1,505 @@
+// HBM-streaming reductions: row softmax, last-axis mean, whole-tensor folds, row arg-max.
+// All are memory bound: 16-byte loads/stores, warp shuffles, fp32 statistics.
+#include "common.cuh"
+#include <cooperative_groups.h>
+#include <climits>
+
+namespace cg = cooperative_groups;
+namespace kuiops {
+
+// --------------------------------------------------------------------------------------
+// Row softmax.
+// A row is split over the CTAs of one thread-block cluster (1, 2, 4 or 8 CTAs) so that a
+// handful of very long rows (64 x 128256 logits) still covers every SM.  Each CTA makes one
+// pass over its slice keeping an online (max, sum-of-exp) pair, the pairs are exchanged
+// through distributed shared memory, and a second pass writes exp(x - M) / S.  The slice is
+// held in registers between the passes when it fits (CACHE_VECS 16-byte vectors per thread),
+// so HBM sees one read and one write; longer slices are re-read (served by L2 when the
+// matrix fits there).
+// Replaces Klas.RowSoftmax.inst_gpu, one block per row, in place
+// (kuiops/softmax/Kuiops.Softmax.Inst.fst.j2:10-11).
+// --------------------------------------------------------------------------------------
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct MaxSum { float m, s; };
+
+__device__ __forceinline__ void online_add(MaxSum& a, float x) {
+  // fold one value into (m, s) with s = sum exp(x_i - m)
+  if (x > a.m) {
+    a.s = a.s * exp2f((a.m - x) * kLog2e) + 1.f;
+    a.m = x;
+  } else {
+    a.s += exp2f((x - a.m) * kLog2e);
+  }
+}
+__device__ __forceinline__ MaxSum online_merge(MaxSum a, MaxSum b) {
+  if (b.m == -INFINITY) return a;
+  if (a.m == -INFINITY) return b;
+  float m = fmaxf(a.m, b.m);
+  MaxSum r;
+  r.m = m;
+  r.s = a.s * exp2f((a.m - m) * kLog2e) + b.s * exp2f((b.m - m) * kLog2e);
+  return r;
+}
+
+template <typename T, int CACHE_VECS>
+__global__ void __launch_bounds__(1024)
+softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
+                    uint32_t cluster_ctas, int vec_ok) {
+  constexpr int VN = Vec16<T>::N;
+  __shared__ float red_m[32], red_s[32];
+  __shared__ MaxSum cta_pair;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
+  const uint32_t row = blockIdx.x / cluster_ctas;
+  // slice boundaries in elements, multiples of VN so vector accesses stay aligned
+  const uint32_t nv_total = (n + VN - 1) / VN;
+  const uint32_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
+  const uint32_t lo = min(part * nv_per * VN, n);
+  const uint32_t hi = min(lo + nv_per * VN, n);
+  const T* x = X + size_t(row) * n;
+  T* y = Y + size_t(row) * n;
+  const int tid = threadIdx.x, nt = blockDim.x;
+
+  Vec16<T> cache[CACHE_VECS > 0 ? CACHE_VECS : 1];
+  MaxSum acc{-INFINITY, 0.f};
+
+  if (row < m) {
+    if (vec_ok) {
+      const uint32_t nvec = (hi - lo) / VN;           // full vectors in the slice
+      if (CACHE_VECS > 0) {
+#pragma unroll
+        for (int c = 0; c < CACHE_VECS; ++c) {
+          uint32_t v = tid + c * nt;
+          if (v < nvec) {
+            cache[c] = ld16_stream(x + lo + size_t(v) * VN);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) online_add(acc, ElemTraits<T>::to_f(cache[c].v[e]));
+          }
+        }
+      } else {
+        for (uint32_t v = tid; v < nvec; v += nt) {
+          Vec16<T> t = ld16(x + lo + size_t(v) * VN);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) online_add(acc, ElemTraits<T>::to_f(t.v[e]));
+        }
+      }
+      for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt)
+        online_add(acc, ElemTraits<T>::to_f(x[i]));
+    } else {
+      for (uint32_t i = lo + tid; i < hi; i += nt) online_add(acc, ElemTraits<T>::to_f(x[i]));
+    }
+  }
+  // block merge
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum b{__shfl_xor_sync(0xffffffffu, acc.m, o), __shfl_xor_sync(0xffffffffu, acc.s, o)};
+    acc = online_merge(acc, b);
+  }
+  const int lane = tid & 31, w = tid >> 5, nw = (nt + 31) >> 5;
+  if (lane == 0) { red_m[w] = acc.m; red_s[w] = acc.s; }
+  __syncthreads();
+  if (w == 0) {
+    MaxSum t = lane < nw ? MaxSum{red_m[lane], red_s[lane]} : MaxSum{-INFINITY, 0.f};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MaxSum b{__shfl_xor_sync(0xffffffffu, t.m, o), __shfl_xor_sync(0xffffffffu, t.s, o)};
+      t = online_merge(t, b);
+    }
+    if (lane == 0) cta_pair = t;
+  }
+  MaxSum tot;
+  if (cluster_ctas > 1) {
+    cluster.sync();
+    tot = MaxSum{-INFINITY, 0.f};
+    for (uint32_t r = 0; r < cluster_ctas; ++r) {
+      const MaxSum* remote = cluster.map_shared_rank(&cta_pair, r);
+      tot = online_merge(tot, *remote);
+    }
+    cluster.sync();   // nobody leaves while a peer may still read its pair
+  } else {
+    __syncthreads();
+    tot = cta_pair;
+  }
+  if (row >= m) return;
+  const float M = tot.m;
+  const float inv = 1.f / tot.s;
+  const float mb = -M * kLog2e;
+  if (vec_ok) {
+    const uint32_t nvec = (hi - lo) / VN;
+    if (CACHE_VECS > 0) {
+#pragma unroll
+      for (int c = 0; c < CACHE_VECS; ++c) {
+        uint32_t v = tid + c * nt;
+        if (v < nvec) {
+          Vec16<T> o;
+#pragma unroll
+          for (int e = 0; e < VN; ++e)
+            o.v[e] = ElemTraits<T>::from_f(
+                exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, mb)) * inv);
+          st16(y + lo + size_t(v) * VN, o);
+        }
+      }
+    } else {
+      for (uint32_t v = tid; v < nvec; v += nt) {
+        Vec16<T> t = ld16(x + lo + size_t(v) * VN), o;
+#pragma unroll
+        for (int e = 0; e < VN; ++e)
+          o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(t.v[e]), kLog2e, mb)) * inv);
+        st16(y + lo + size_t(v) * VN, o);
+      }
+    }
+    for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt)
+      y[i] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
+  } else {
+    for (uint32_t i = lo + tid; i < hi; i += nt)
+      y[i] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
+  }
+}
+
+template <typename T>
+static int softmax_launch(uint32_t m, uint32_t n, const void* X, void* Y, cudaStream_t st) {
+  if (m == 0 || n == 0) return KUIOPS_EINVAL;
+  if (!X || !Y) return KUIOPS_EINVAL;
+  constexpr int VN = Vec16<T>::N;
+  // a row start is 16-byte aligned for every row only when n is a multiple of VN
+  const int vec_ok = aligned16(X) && aligned16(Y) && (n % VN == 0);
+  // cluster width: enough CTAs to cover the SMs when rows are few and long
+  uint32_t c = 1;
+  while (c < 8 && uint64_t(m) * c < 2 * kNumSMs && n / (c * 2) >= 8192) c *= 2;
+  const uint32_t slice = (n + c - 1) / c;
+  uint32_t threads = (slice / VN + 3) / 4;             // ~4 vectors per thread
+  threads = ((threads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 1024) threads = 1024;
+  const uint32_t nv_per = ((n + VN - 1) / VN + c - 1) / c;   // vectors per CTA slice
+  const bool cached = vec_ok && nv_per <= threads * 4;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(m * c);
+  cfg.blockDim = dim3(threads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = c; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  const T* x = static_cast<const T*>(X);
+  T* y = static_cast<T*>(Y);
+  cudaError_t e = cached
+      ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<T, 4>, m, n, x, y, c, vec_ok)
+      : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<T, 0>, m, n, x, y, c, vec_ok);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+}
+
+// --------------------------------------------------------------------------------------
+// Last-axis mean.  One warp per row for short rows, one CTA per row for long ones.
+// Replaces Kuiper.Kernel.HReduce.Block.reduce_batched_block (kuiops/mean/Kuiops.Mean.fst:47-50),
+// whose pre-map divides every element by n before the tree sum (Kuiops.Mean.fsti:25-32);
+// here the sum is accumulated in fp32 and scaled once.
+// --------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float row_partial_sum(const T* x, uint64_t n, int lane_id, int lanes,
+                                                 bool vec_ok) {
+  constexpr int VN = Vec16<T>::N;
+  float s0 = 0.f, s1 = 0.f;
+  if (vec_ok) {
+    const uint64_t nvec = n / VN;
+    uint64_t v = lane_id;
+    for (; v + lanes < nvec; v += 2 * uint64_t(lanes)) {
+      Vec16<T> a = ld16_stream(x + v * VN), b = ld16_stream(x + (v + lanes) * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) { s0 += ElemTraits<T>::to_f(a.v[e]); s1 += ElemTraits<T>::to_f(b.v[e]); }
+    }
+    for (; v < nvec; v += lanes) {
+      Vec16<T> a = ld16_stream(x + v * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) s0 += ElemTraits<T>::to_f(a.v[e]);
+    }
+    for (uint64_t i = nvec * VN + lane_id; i < n; i += lanes) s1 += ElemTraits<T>::to_f(x[i]);
+  } else {
+    for (uint64_t i = lane_id; i < n; i += lanes) s0 += ElemTraits<T>::to_f(x[i]);
+  }
+  return s0 + s1;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+mean_warp_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, T* __restrict__ out, int vec_ok) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps_total = uint64_t(gridDim.x) * (blockDim.x >> 5);
+  const float inv = 1.f / float(n);
+  for (uint64_t row = uint64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m;
+       row += warps_total) {
+    float s = row_partial_sum(X + row * n, n, lane, 32, vec_ok);
+    s = warp_sum(s);
+    if (lane == 0) out[row] = ElemTraits<T>::from_f(s * inv);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+mean_block_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, T* __restrict__ out, int vec_ok) {
+  __shared__ float red[32];
+  const float inv = 1.f / float(n);
+  for (uint64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    float s = row_partial_sum(X + row * n, n, threadIdx.x, blockDim.x, vec_ok);
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) out[row] = ElemTraits<T>::from_f(s * inv);
+  }
+}
+
+template <typename T>
+static int mean_launch(uint64_t m, uint64_t n, const void* in, void* out, cudaStream_t st) {
+  if (m == 0 || n == 0 || !in || !out) return KUIOPS_EINVAL;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = aligned16(in) && (n % VN == 0);
+  const T* x = static_cast<const T*>(in);
+  T* o = static_cast<T*>(out);
+  if (n <= 16384 && m >= 8) {
+    unsigned grid = stream_grid(m, 8, 16);
+    mean_warp_rows_kernel<T><<<grid, 256, 0, st>>>(m, n, x, o, vec_ok);
+  } else {
+    unsigned threads = n >= 8192 ? 1024 : 256;
+    unsigned grid = unsigned(m < uint64_t(kNumSMs) * 8 ? m : uint64_t(kNumSMs) * 8);
+    mean_block_rows_kernel<T><<<grid, threads, 0, st>>>(m, n, x, o, vec_ok);
+  }
+  return check_launch();
+}
+
+// --------------------------------------------------------------------------------------
+// Whole-tensor folds (all / any over bool bytes, max over int64 / fp32).
+// Every CTA folds a grid-strided part, stores its partial and takes a ticket; the CTA that
+// draws the last ticket folds the partials in index order and resets the ticket.  The folds
+// are associative and commutative on these types, so the result equals the left-to-right
+// fold of Kuiops.HReducePoly.Exact.reduce (kuiops/reduce/Kuiops.HReducePoly.Exact.fsti:26-46)
+// bit for bit.
+// --------------------------------------------------------------------------------------
+template <typename T, int OP> struct Fold;
+template <> struct Fold<uint8_t, KUIOPS_REDUCE_ALL> {
+  using Acc = unsigned;
+  static __device__ Acc init() { return 1u; }
+  static __device__ Acc pre(uint8_t v) { return v != 0; }
+  static __device__ Acc f(Acc a, Acc b) { return a & b; }
+  static __device__ uint8_t fin(Acc a) { return uint8_t(a); }
+};
+template <> struct Fold<uint8_t, KUIOPS_REDUCE_ANY> {
+  using Acc = unsigned;
+  static __device__ Acc init() { return 0u; }
+  static __device__ Acc pre(uint8_t v) { return v != 0; }
+  static __device__ Acc f(Acc a, Acc b) { return a | b; }
+  static __device__ uint8_t fin(Acc a) { return uint8_t(a); }
+};
+template <> struct Fold<int64_t, KUIOPS_REDUCE_MAX> {
+  using Acc = long long;
+  static __device__ Acc init() { return LLONG_MIN; }
+  static __device__ Acc pre(int64_t v) { return v; }
+  static __device__ Acc f(Acc a, Acc b) { return a > b ? a : b; }
+  static __device__ int64_t fin(Acc a) { return a; }
+};
+template <> struct Fold<float, KUIOPS_REDUCE_MAX> {
+  using Acc = float;
+  static __device__ Acc init() { return -INFINITY; }
+  static __device__ Acc pre(float v) { return v; }
+  // NaN propagates, as torch.max does
+  static __device__ Acc f(Acc a, Acc b) { return (a != a) ? a : ((b != b) ? b : (a > b ? a : b)); }
+  static __device__ float fin(Acc a) { return a; }
+};
+
+template <typename Acc, typename F>
+__device__ __forceinline__ Acc block_fold(Acc v, Acc* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = F::f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  Acc t = lane < nw ? sh[lane] : F::init();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t = F::f(t, __shfl_xor_sync(0xffffffffu, t, o));
+  return t;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512)
+fold_kernel(uint64_t n, const T* __restrict__ in, T* __restrict__ out, unsigned long long* ticket,
+            typename Fold<T, OP>::Acc* partials, int vec_ok) {
+  using F = Fold<T, OP>;
+  using Acc = typename F::Acc;
+  __shared__ Acc sh[32];
+  __shared__ bool is_last;
+  constexpr int VN = Vec16<T>::N;
+  Acc a = F::init();
+  const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
+  if (vec_ok) {
+    const uint64_t nvec = n / VN;
+    for (uint64_t v = gt; v < nvec; v += gs) {
+      Vec16<T> t = ld16_stream(in + v * VN);
+#pragma unroll
+      for (int e = 0; e < VN; ++e) a = F::f(a, F::pre(t.v[e]));
+    }
+    for (uint64_t i = nvec * VN + gt; i < n; i += gs) a = F::f(a, F::pre(in[i]));
+  } else {
+    for (uint64_t i = gt; i < n; i += gs) a = F::f(a, F::pre(in[i]));
+  }
+  a = block_fold<Acc, F>(a, sh);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = a;
+    __threadfence();
+    unsigned long long t = atomicAdd(ticket, 1ull);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  Acc b = F::init();
+  for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) b = F::f(b, __ldcg(&partials[i]));
+  b = block_fold<Acc, F>(b, sh);
+  if (threadIdx.x == 0) {
+    *out = F::fin(b);
+    *ticket = 0ull;   // leave the workspace ready for the next call
+  }
+}
+
+template <typename T, int OP>
+static int fold_launch(uint64_t n, const void* in, void* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (n == 0 || !in || !out) return KUIOPS_EINVAL;
+  if (!ws || ws_bytes < KUIOPS_REDUCE_WORKSPACE_BYTES) return KUIOPS_EWORKSPACE;
+  using Acc = typename Fold<T, OP>::Acc;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = aligned16(in);
+  unsigned grid = stream_grid((n + VN - 1) / VN, 512 * 4, 4);
+  const unsigned max_partials = (KUIOPS_REDUCE_WORKSPACE_BYTES - 64) / sizeof(Acc);
+  if (grid > max_partials) grid = max_partials;
+  auto* ticket = static_cast<unsigned long long*>(ws);
+  auto* partials = reinterpret_cast<Acc*>(static_cast<char*>(ws) + 64);
+  fold_kernel<T, OP><<<grid, 512, 0, st>>>(n, static_cast<const T*>(in), static_cast<T*>(out), ticket,
+                                           partials, vec_ok);
+  return check_launch();
+}
+
+// --------------------------------------------------------------------------------------
+// Row arg-max (greedy sampling over the vocabulary), ties to the lowest index.
+// --------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __restrict__ out, int vec_ok) {
+  __shared__ float sv[32];
+  __shared__ long long si[32];
+  constexpr int VN = Vec16<T>::N;
+  for (uint64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    const T* x = X + row * n;
+    float bv = -INFINITY;
+    long long bi = LLONG_MAX;
+    auto consider = [&](float v, long long i) {
+      // NaN counts as the maximum, as in torch.argmax; equal keys keep the lowest index
+      const bool vnan = v != v, bnan = bv != bv;
+      bool better;
+      if (bi == LLONG_MAX) better = true;
+      else if (vnan != bnan) better = vnan;
+      else if (vnan) better = i < bi;
+      else better = v > bv || (v == bv && i < bi);
+      if (better) { bv = v; bi = i; }
+    };
+    if (vec_ok) {
+      const uint64_t nvec = n / VN;
+      for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        Vec16<T> t = ld16_stream(x + v * VN);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) consider(ElemTraits<T>::to_f(t.v[e]), (long long)(v * VN + e));
+      }
+      for (uint64_t i = nvec * VN + threadIdx.x; i < n; i += blockDim.x)
+        consider(ElemTraits<T>::to_f(x[i]), (long long)i);
+    } else {
+      for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) consider(ElemTraits<T>::to_f(x[i]), (long long)i);
+    }
+    auto merge = [&](float ov, long long oi) {
+      if (oi == LLONG_MAX) return;
+      consider(ov, oi);
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      merge(ov, oi);
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+      bv = lane < nw ? sv[lane] : -INFINITY;
+      bi = lane < nw ? si[lane] : LLONG_MAX;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        merge(ov, oi);
+      }
+      if (lane == 0) out[row] = bi;
+    }
+  }
+}
+
+template <typename T>
+static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cudaStream_t st) {
+  if (m == 0 || n == 0 || !X || !out) return KUIOPS_EINVAL;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = aligned16(X) && (n % VN == 0);
+  unsigned threads = n >= 32768 ? 1024 : (n >= 2048 ? 256 : 64);
+  unsigned grid = unsigned(m < uint64_t(kNumSMs) * 8 ? m : uint64_t(kNumSMs) * 8);
+  argmax_rows_kernel<T><<<grid, threads, 0, st>>>(m, n, static_cast<const T*>(X), out, vec_ok);
+  return check_launch();
+}
+
+}  // namespace kuiops
+
+using namespace kuiops;
+
+extern "C" {
+
+int kuiops_softmax_f32(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t s) {
+  return softmax_launch<float>(m, n, X, Y, as_stream(s));
+}
+int kuiops_softmax_bf16(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t s) {
+  return softmax_launch<__nv_bfloat16>(m, n, X, Y, as_stream(s));
+}
+int kuiops_softmax_f16(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t s) {
+  return softmax_launch<__half>(m, n, X, Y, as_stream(s));
+}
+
+int kuiops_mean_f32(uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t s) {
+  return mean_launch<float>(m, n, in, out, as_stream(s));
+}
+int kuiops_mean_bf16(uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t s) {
+  return mean_launch<__nv_bfloat16>(m, n, in, out, as_stream(s));
+}
+int kuiops_mean_f16(uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t s) {
+  return mean_launch<__half>(m, n, in, out, as_stream(s));
+}
+
+int kuiops_reduce_u8(int op, uint64_t n, const void* in, void* out, void* ws, size_t wsb, kuiops_stream_t s) {
+  if (op == KUIOPS_REDUCE_ALL) return fold_launch<uint8_t, KUIOPS_REDUCE_ALL>(n, in, out, ws, wsb, as_stream(s));
+  if (op == KUIOPS_REDUCE_ANY) return fold_launch<uint8_t, KUIOPS_REDUCE_ANY>(n, in, out, ws, wsb, as_stream(s));
+  return KUIOPS_EUNSUPPORTED;
+}
+int kuiops_reduce_i64(int op, uint64_t n, const void* in, void* out, void* ws, size_t wsb, kuiops_stream_t s) {
+  if (op == KUIOPS_REDUCE_MAX) return fold_launch<int64_t, KUIOPS_REDUCE_MAX>(n, in, out, ws, wsb, as_stream(s));
+  return KUIOPS_EUNSUPPORTED;
+}
+int kuiops_reduce_f32(int op, uint64_t n, const void* in, void* out, void* ws, size_t wsb, kuiops_stream_t s) {
+  if (op == KUIOPS_REDUCE_MAX) return fold_launch<float, KUIOPS_REDUCE_MAX>(n, in, out, ws, wsb, as_stream(s));
+  return KUIOPS_EUNSUPPORTED;
+}
+
+int kuiops_argmax(int dtype, uint64_t m, uint64_t n, const void* X, int64_t* out, kuiops_stream_t s) {
+  switch (dtype) {
+    case KUIOPS_F32: return argmax_launch<float>(m, n, X, out, as_stream(s));
+    case KUIOPS_BF16: return argmax_launch<__nv_bfloat16>(m, n, X, out, as_stream(s));
+    case KUIOPS_F16: return argmax_launch<__half>(m, n, X, out, as_stream(s));
+  }
+  return KUIOPS_EINVAL;
+}
+
+}  // extern "C"

@@ -1,0 +1,553 @@
+"""ctypes binding of ``libkuiops.so`` (the C ABI declared in ``include/kuiops.h``).
+
+This is the only place that touches the shared library.  It plays the part of the reference's
+generated pybind wrappers (kuiops/<op>/wrapper_<op>.cu.j2): make inputs contiguous, allocate the
+output with the kernel's output dtype, pass raw pointers, sizes and the current CUDA stream.
+Unlike those wrappers it never synchronises the stream (include/kuiops.h:11-18 of the reference
+does before every launch), and there is no CPU path: if the library cannot be loaded, every call
+raises.
+"""
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+LIB_PATH = Path(os.environ.get("KUIOPS_LIB", _PKG / "lib" / "libkuiops.so"))
+
+OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ELAUNCH, EDRIVER, ELIMIT = 0, -1, -2, -3, -4, -5, -6
+F32, BF16, F16 = 0, 1, 2
+GEMM_COUNTER_BYTES = 16384
+REDUCE_WORKSPACE_BYTES = 16384
+REDUCE_ALL, REDUCE_ANY, REDUCE_MAX = 0, 1, 2
+MAP = dict(silu=0, neg=1, rsqrt=2, cos=3, sin=4, pow=5, square=6, add=7, mul=8, sub=9, div=10,
+           bnot=11, band=12, bor=13, eq=14, le=15, lt=16, gelu=17)
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+class KuiopsError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__(f"{what}: {strerror(code)} (code {code})")
+
+
+_lib = None
+_load_error = None
+
+c_void_p, c_int, c_u32, c_u64, c_i64, c_float, c_double, c_size_t = (
+    ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int64,
+    ctypes.c_float, ctypes.c_double, ctypes.c_size_t)
+_P64 = ctypes.POINTER(ctypes.c_uint64)
+_PI64 = ctypes.POINTER(ctypes.c_int64)
+_PP = ctypes.POINTER(ctypes.c_void_p)
+
+# name -> (restype, argtypes); mirrors include/kuiops.h declaration by declaration
+SIGNATURES = {
+    "kuiops_abi_version": (c_int, []),
+    "kuiops_strerror": (ctypes.c_char_p, [c_int]),
+    "kuiops_debug_tc_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
+    "kuiops_launch_count": (c_u64, []),
+    "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),
+    "kuiops_gemm": (c_int, [c_int, c_int, c_u32, c_u32, c_u32, c_u32,
+                            c_void_p, c_i64, c_i64, c_void_p, c_i64, c_i64, c_int,
+                            c_void_p, c_i64, c_i64, c_float, c_float,
+                            c_void_p, c_i64, c_i64, c_void_p, c_size_t, c_void_p]),
+    "kuiops_sdpa_workspace_bytes": (c_size_t, [c_int] + [c_u32] * 7),
+    "kuiops_sdpa": (c_int, [c_int] + [c_u32] * 7 +
+                    [c_void_p, c_i64, c_i64, c_i64] * 3 +
+                    [c_void_p, c_float, c_int, c_void_p, c_i64, c_i64, c_i64, c_void_p,
+                     c_void_p, c_size_t, c_void_p]),
+    "kuiops_topk_f32": (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_gather": (c_int, [c_u32, c_u32, c_u32, _P64, _P64, c_void_p, c_void_p, c_void_p, c_u64,
+                              c_void_p, c_void_p]),
+    "kuiops_scatter": (c_int, [c_u32, c_u32, c_u32, _P64, _P64, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_u64, c_void_p, c_void_p]),
+    "kuiops_cat": (c_int, [c_u32, c_u32, c_u32, _P64, c_u64, c_void_p, c_void_p, c_void_p, c_u64, c_void_p]),
+    "kuiops_cat_n": (c_int, [c_u32, c_u32, c_u32, c_u32, _P64, _P64, _PP, c_void_p, c_void_p]),
+    "kuiops_index": (c_int, [c_u32, c_u32, _P64, c_u32, c_u32, _PP, c_u32, _P64, _PI64,
+                             c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_isin_i64": (c_int, [c_u64, c_void_p, c_u64, c_void_p, c_int, c_void_p, c_void_p]),
+    "kuiops_map": (c_int, [c_int, c_int, c_u64, c_void_p, c_void_p, c_double, c_double, c_void_p]),
+    "kuiops_map2": (c_int, [c_int, c_int, c_u64, c_void_p, c_void_p, c_void_p, c_double, c_void_p]),
+    "kuiops_map_u8": (c_int, [c_int, c_u64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_map_nip": (c_int, [c_int, c_int, c_u64, c_void_p, c_void_p, c_double, c_void_p]),
+    "kuiops_map3": (c_int, [c_u32, c_u64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_rmsnorm": (c_int, [c_int, c_u64, c_u32, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                               c_void_p, c_void_p]),
+    "kuiops_swiglu": (c_int, [c_int, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),
+    "kuiops_rope_qkv": (c_int, [c_int, c_u64, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_float,
+                                c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
+    "kuiops_embedding": (c_int, [c_u32, c_u64, c_u64, c_u64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
+}
+for _sfx in ("f32", "bf16", "f16"):
+    SIGNATURES[f"kuiops_mm_{_sfx}"] = (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_size_t, c_void_p])
+    SIGNATURES[f"kuiops_addmm_{_sfx}"] = (c_int, [c_u32, c_u32, c_u32, c_float, c_float, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_size_t, c_void_p])
+    SIGNATURES[f"kuiops_bmm_{_sfx}"] = (c_int, [c_u32, c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_size_t, c_void_p])
+    SIGNATURES[f"kuiops_softmax_{_sfx}"] = (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p])
+    SIGNATURES[f"kuiops_mean_{_sfx}"] = (c_int, [c_u64, c_u64, c_void_p, c_void_p, c_void_p])
+for _sfx in ("u8", "i64", "f32"):
+    SIGNATURES[f"kuiops_reduce_{_sfx}"] = (c_int, [c_int, c_u64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p])
+
+
+def lib():
+    """The loaded library.  Raises if it is missing: there is no fallback path."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if _load_error is not None:
+        raise _load_error
+    try:
+        if not LIB_PATH.exists():
+            raise OSError(f"{LIB_PATH} not found; build it with `python {_PKG / 'csrc' / 'build.py'}`")
+        L = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+        return L
+    except (OSError, AttributeError) as e:
+        _load_error = RuntimeError(f"kuiops: cannot load the CUDA library: {e}")
+        raise _load_error
+
+
+def is_loadable() -> bool:
+    try:
+        lib()
+        return True
+    except RuntimeError:
+        return False
+
+
+def strerror(code: int) -> str:
+    try:
+        return lib().kuiops_strerror(code).decode()
+    except RuntimeError:
+        return f"kuiops error {code}"
+
+
+def launch_count() -> int:
+    return int(lib().kuiops_launch_count())
+
+
+def tc_error(reset=True) -> int:
+    v = ctypes.c_uint(0)
+    _check(lib().kuiops_debug_tc_error(ctypes.byref(v), 1 if reset else 0), "debug_tc_error")
+    return int(v.value)
+
+
+def _check(rc, what):
+    if rc != OK:
+        raise KuiopsError(rc, what)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dt):
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KuiopsError(EINVAL, f"dtype {dt}")
+
+
+def _sfx(dt):
+    return {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}[dt]
+
+
+def _u64arr(vals):
+    return (ctypes.c_uint64 * len(vals))(*[int(v) for v in vals])
+
+
+# --------------------------------------------------------------------------------------------
+# caller-owned scratch: one zero-initialised buffer per (purpose, device, stream); the kernels
+# keep the leading counter words zero between calls
+# --------------------------------------------------------------------------------------------
+_scratch = {}
+
+
+def workspace(kind, device, nbytes):
+    key = (kind, device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        cap = max(int(nbytes), 1 << 20)
+        buf = torch.zeros(cap, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+# --------------------------------------------------------------------------------------------
+# GEMM family
+# --------------------------------------------------------------------------------------------
+def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dtype=None):
+    """C = alpha * A @ (B.T if trans_b else B) + beta * Cin.  A: [M,K] or [b,M,K].
+    B: [K,N] ([N,K] if trans_b), optionally batched.  Cin: [M,N], [b,M,N] or a length-N bias."""
+    batched = A.dim() == 3
+    if batched:
+        bsz, M, K = A.shape
+    else:
+        bsz, (M, K) = 1, A.shape
+    N = B.shape[-2] if trans_b else B.shape[-1]
+    dt = A.dtype
+    odt = out_dtype or dt
+    if A.stride(-1) != 1 or (batched and A.stride(0) < M * A.stride(1) and bsz > 1):
+        A = A.contiguous()
+    if B.stride(-1) != 1:
+        B = B.contiguous()
+    lda, ldb = A.stride(-2), B.stride(-2)
+    if M == 1:
+        lda = max(lda, K)
+    if (K if not trans_b else N) == 1:
+        ldb = max(ldb, K if trans_b else N)
+    sa = A.stride(0) if batched else 0
+    sb = B.stride(0) if B.dim() == 3 else 0
+    if out is None:
+        out = torch.empty((bsz, M, N) if batched else (M, N), dtype=odt, device=A.device)
+    ldc, sc = out.stride(-2), (out.stride(0) if batched else 0)
+    if M == 1:
+        ldc = max(ldc, N)
+    cin_p, ldcin, scin = None, 0, 0
+    if Cin is not None:
+        if Cin.dim() == 1:
+            Cin = Cin.contiguous()
+            cin_p, ldcin, scin = Cin.data_ptr(), 0, 0
+        else:
+            if Cin.stride(-1) != 1:
+                Cin = Cin.contiguous()
+            cin_p, ldcin = Cin.data_ptr(), max(Cin.stride(-2), N)
+            scin = Cin.stride(0) if Cin.dim() == 3 else 0
+    L = lib()
+    code = dtype_code(dt)
+    wsb = L.kuiops_gemm_workspace_bytes(code, bsz, M, N, K)
+    ws = workspace("gemm", A.device, wsb)
+    _check(L.kuiops_gemm(code, dtype_code(odt), bsz, M, N, K,
+                         A.data_ptr(), lda, sa, B.data_ptr(), ldb, sb, 1 if trans_b else 0,
+                         cin_p, ldcin, scin, float(alpha), float(beta),
+                         out.data_ptr(), ldc, sc, ws.data_ptr(), ws.numel(), _stream()), "gemm")
+    return out
+
+
+def mm(A, B):
+    """aten.mm through the reference-order entry point (dense row-major operands)."""
+    A, B = A.contiguous(), B.contiguous()
+    M, K = A.shape
+    N = B.shape[1]
+    C = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    L = lib()
+    ws = workspace("gemm", A.device, L.kuiops_gemm_workspace_bytes(dtype_code(A.dtype), 1, M, N, K))
+    fn = getattr(L, f"kuiops_mm_{_sfx(A.dtype)}")
+    _check(fn(M, N, K, A.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "mm")
+    return C
+
+
+def addmm(C, A, B, alpha, beta):
+    """aten.addmm with a full [M,N] C, through the reference-order entry point (M, K, N)."""
+    A, B = A.contiguous(), B.contiguous()
+    out = C.contiguous().clone()
+    M, K = A.shape
+    N = B.shape[1]
+    L = lib()
+    ws = workspace("gemm", A.device, L.kuiops_gemm_workspace_bytes(dtype_code(A.dtype), 1, M, N, K))
+    fn = getattr(L, f"kuiops_addmm_{_sfx(A.dtype)}")
+    _check(fn(M, K, N, float(alpha), float(beta), A.data_ptr(), B.data_ptr(), out.data_ptr(),
+              ws.data_ptr(), ws.numel(), _stream()), "addmm")
+    return out
+
+
+def bmm(A, B):
+    A, B = A.contiguous(), B.contiguous()
+    bsz, M, K = A.shape
+    N = B.shape[2]
+    C = torch.empty((bsz, M, N), dtype=A.dtype, device=A.device)
+    L = lib()
+    ws = workspace("gemm", A.device, L.kuiops_gemm_workspace_bytes(dtype_code(A.dtype), bsz, M, N, K))
+    fn = getattr(L, f"kuiops_bmm_{_sfx(A.dtype)}")
+    _check(fn(bsz, M, K, N, A.data_ptr(), B.data_ptr(), C.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "bmm")
+    return C
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+def sdpa(Q, K, V, *, bias=None, scale=None, is_causal=False, need_lse=True, out=None):
+    """Q (n,h,l,e), K (n,h_kv,s,e), V (n,h_kv,s,ev) -> out (n,h,l,ev), lse (n,h,l) fp32."""
+    n, h, l, e = Q.shape
+    _, hkv, s, _ = K.shape
+    ev = V.shape[3]
+    if Q.stride(3) != 1:
+        Q = Q.contiguous()
+    if K.stride(3) != 1:
+        K = K.contiguous()
+    if V.stride(3) != 1:
+        V = V.contiguous()
+    if bias is not None:
+        bias = bias.expand(n, h, l, s).contiguous()
+    if scale is None:
+        scale = 1.0 / (e ** 0.5)
+    if out is None:
+        out = torch.empty((n, h, l, ev), dtype=Q.dtype, device=Q.device)
+    lse = torch.empty((n, h, l), dtype=torch.float32, device=Q.device) if need_lse else None
+    L = lib()
+    code = dtype_code(Q.dtype)
+    wsb = L.kuiops_sdpa_workspace_bytes(code, n, h, hkv, l, s, e, ev)
+    ws = workspace("sdpa", Q.device, wsb) if wsb else None
+    _check(L.kuiops_sdpa(code, n, h, hkv, l, s, e, ev,
+                         Q.data_ptr(), Q.stride(0), Q.stride(1), Q.stride(2),
+                         K.data_ptr(), K.stride(0), K.stride(1), K.stride(2),
+                         V.data_ptr(), V.stride(0), V.stride(1), V.stride(2),
+                         _ptr(bias), float(scale), 1 if is_causal else 0,
+                         out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), _ptr(lse),
+                         _ptr(ws), ws.numel() if ws is not None else 0, _stream()), "sdpa")
+    return out, lse
+
+
+# --------------------------------------------------------------------------------------------
+# streaming reductions
+# --------------------------------------------------------------------------------------------
+def softmax(X2d, out=None):
+    """Row softmax of a contiguous [m, n] matrix; out may be X2d (in place)."""
+    m, n = X2d.shape
+    if out is None:
+        out = torch.empty_like(X2d)
+    fn = getattr(lib(), f"kuiops_softmax_{_sfx(X2d.dtype)}")
+    _check(fn(m, n, X2d.data_ptr(), out.data_ptr(), _stream()), "softmax")
+    return out
+
+
+def mean_lastdim(X):
+    Xc = X.contiguous()
+    n = Xc.shape[-1]
+    m = Xc.numel() // n
+    out = torch.empty(tuple(Xc.shape[:-1]) + (1,), dtype=Xc.dtype, device=Xc.device)
+    fn = getattr(lib(), f"kuiops_mean_{_sfx(Xc.dtype)}")
+    _check(fn(m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "mean")
+    return out
+
+
+def reduce(op, X):
+    """Whole-tensor fold to a 0-d device tensor: op in {"all", "any", "max"}."""
+    Xc = X.contiguous()
+    code = dict(all=REDUCE_ALL, any=REDUCE_ANY, max=REDUCE_MAX)[op]
+    if Xc.dtype in (torch.bool, torch.uint8):
+        fn, odt = lib().kuiops_reduce_u8, Xc.dtype
+    elif Xc.dtype == torch.int64:
+        fn, odt = lib().kuiops_reduce_i64, torch.int64
+    elif Xc.dtype == torch.float32:
+        fn, odt = lib().kuiops_reduce_f32, torch.float32
+    else:
+        raise KuiopsError(EUNSUPPORTED, f"reduce over {Xc.dtype}")
+    out = torch.empty((), dtype=odt, device=Xc.device)
+    ws = workspace("reduce", Xc.device, REDUCE_WORKSPACE_BYTES)
+    _check(fn(code, Xc.numel(), Xc.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "reduce")
+    return out
+
+
+def topk(X, k):
+    """Largest-k over the last axis of fp32 X, sorted; equal values by ascending index."""
+    Xc = X.contiguous()
+    n = Xc.shape[-1]
+    m = Xc.numel() // n
+    vals = torch.empty(tuple(Xc.shape[:-1]) + (k,), dtype=torch.float32, device=Xc.device)
+    idx = torch.empty(tuple(Xc.shape[:-1]) + (k,), dtype=torch.int64, device=Xc.device)
+    _check(lib().kuiops_topk_f32(m, n, k, Xc.data_ptr(), vals.data_ptr(), idx.data_ptr(), _stream()), "topk")
+    return vals, idx
+
+
+def argmax_lastdim(X):
+    Xc = X.contiguous()
+    n = Xc.shape[-1]
+    m = Xc.numel() // n
+    out = torch.empty(tuple(Xc.shape[:-1]), dtype=torch.int64, device=Xc.device)
+    _check(lib().kuiops_argmax(dtype_code(Xc.dtype), m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# indexed data movement
+# --------------------------------------------------------------------------------------------
+def _status(device):
+    return workspace("status", device, 64)
+
+
+def check_status(device):
+    """Synchronising read of the out-of-range-index flag set by gather/scatter/index/embedding."""
+    st = _status(device)
+    flag = int(st[:4].view(torch.int32).item())
+    if flag:
+        st[:4].zero_()
+    return flag
+
+
+def gather(Inp, dim, Idx):
+    Inp, Idx = Inp.contiguous(), Idx.contiguous()
+    out = torch.empty(Idx.shape, dtype=Inp.dtype, device=Inp.device)
+    _check(lib().kuiops_gather(Inp.element_size(), Inp.dim(), dim, _u64arr(Inp.shape), _u64arr(Idx.shape),
+                               Inp.data_ptr(), Idx.data_ptr(), out.data_ptr(), Idx.numel(),
+                               _status(Inp.device).data_ptr(), _stream()), "gather")
+    return out
+
+
+def scatter(Self, dim, Idx, Src):
+    Self, Idx, Src = Self.contiguous(), Idx.contiguous(), Src.contiguous()
+    out = torch.empty_like(Self)
+    _check(lib().kuiops_scatter(Self.element_size(), Self.dim(), dim, _u64arr(Self.shape), _u64arr(Src.shape),
+                                Self.data_ptr(), Src.data_ptr(), Idx.data_ptr(), out.data_ptr(), Src.numel(),
+                                _status(Self.device).data_ptr(), _stream()), "scatter")
+    return out
+
+
+def cat2(A, B, dim):
+    """Binary cat through the reference-order entry point."""
+    A, B = A.contiguous(), B.contiguous()
+    shape = list(A.shape)
+    shape[dim] = A.shape[dim] + B.shape[dim]
+    out = torch.empty(shape, dtype=A.dtype, device=A.device)
+    _check(lib().kuiops_cat(A.element_size(), A.dim(), dim, _u64arr(A.shape), B.shape[dim],
+                            A.data_ptr(), B.data_ptr(), out.data_ptr(), out.numel(), _stream()), "cat")
+    return out
+
+
+def cat(tensors, dim):
+    tensors = [t.contiguous() for t in tensors]
+    shape = list(tensors[0].shape)
+    sizes = [t.shape[dim] for t in tensors]
+    shape[dim] = sum(sizes)
+    out = torch.empty(shape, dtype=tensors[0].dtype, device=tensors[0].device)
+    ptrs = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    _check(lib().kuiops_cat_n(out.element_size(), out.dim(), dim, len(tensors), _u64arr(tensors[0].shape),
+                              _u64arr(sizes), ptrs, out.data_ptr(), _stream()), "cat_n")
+    return out
+
+
+def index(Self, first_dim, indices):
+    """Self[..., i0, i1, ..., ...] with int64 index tensors on adjacent dims starting at first_dim."""
+    Self = Self.contiguous()
+    bshape = torch.broadcast_shapes(*[i.shape for i in indices])
+    exp = [i.expand(bshape) for i in indices]     # views: broadcast dims get stride 0
+    keep = []                                     # the expanded views must stay dense elsewhere
+    strides = []
+    for v, orig in zip(exp, indices):
+        if not orig.is_contiguous():
+            orig = orig.contiguous()
+            v = orig.expand(bshape)
+        keep.append(orig)
+        strides += list(v.stride())
+    out_shape = tuple(Self.shape[:first_dim]) + tuple(bshape) + tuple(Self.shape[first_dim + len(indices):])
+    out = torch.empty(out_shape, dtype=Self.dtype, device=Self.device)
+    if out.numel() == 0:
+        return out
+    ptrs = (ctypes.c_void_p * len(indices))(*[k.data_ptr() for k in keep])
+    stride_arr = (ctypes.c_int64 * max(1, len(strides)))(*strides)
+    _check(lib().kuiops_index(Self.element_size(), Self.dim(), _u64arr(Self.shape), first_dim, len(indices), ptrs,
+                              len(bshape), _u64arr(bshape) if len(bshape) else None, stride_arr,
+                              Self.data_ptr(), out.data_ptr(), _status(Self.device).data_ptr(), _stream()), "index")
+    return out
+
+
+def isin(elements, test_elements, invert=False):
+    e, t = elements.contiguous(), test_elements.contiguous().reshape(-1)
+    out = torch.empty(e.shape, dtype=torch.bool, device=e.device)
+    if e.numel() == 0:
+        return out
+    _check(lib().kuiops_isin_i64(e.numel(), e.data_ptr(), t.numel(), _ptr(t) if t.numel() else None,
+                                 1 if invert else 0, out.data_ptr(), _stream()), "isin")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# elementwise maps
+# --------------------------------------------------------------------------------------------
+def map1(op, X, c0=0.0, c1=1.0, out=None):
+    Xc = X.contiguous()
+    if out is None:
+        out = torch.empty_like(Xc)
+    _check(lib().kuiops_map(dtype_code(Xc.dtype), MAP[op], Xc.numel(), Xc.data_ptr(), out.data_ptr(),
+                            float(c0), float(c1), _stream()), f"map {op}")
+    return out
+
+
+def map2(op, X, B, c1=1.0, out=None):
+    Xc, Bc = X.contiguous(), B.contiguous()
+    if out is None:
+        out = torch.empty_like(Xc)
+    _check(lib().kuiops_map2(dtype_code(Xc.dtype), MAP[op], Xc.numel(), Xc.data_ptr(), Bc.data_ptr(),
+                             out.data_ptr(), float(c1), _stream()), f"map2 {op}")
+    return out
+
+
+def map_u8(op, X, B=None):
+    Xc = X.contiguous()
+    Bc = B.contiguous() if B is not None else None
+    out = torch.empty_like(Xc)
+    _check(lib().kuiops_map_u8(MAP[op], Xc.numel(), Xc.data_ptr(), _ptr(Bc), out.data_ptr(), _stream()), f"map_u8 {op}")
+    return out
+
+
+def map_nip(op, X, c0):
+    Xc = X.contiguous()
+    out = torch.empty(Xc.shape, dtype=torch.bool, device=Xc.device)
+    _check(lib().kuiops_map_nip(dtype_code(Xc.dtype), MAP[op], Xc.numel(), Xc.data_ptr(), out.data_ptr(),
+                                float(c0), _stream()), f"map_nip {op}")
+    return out
+
+
+def where(cond, A, B):
+    c, a, b = cond.contiguous(), A.contiguous(), B.contiguous()
+    out = torch.empty_like(a)
+    _check(lib().kuiops_map3(a.element_size(), a.numel(), c.data_ptr(), a.data_ptr(), b.data_ptr(),
+                             out.data_ptr(), _stream()), "where")
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# fused decoder-layer helpers
+# --------------------------------------------------------------------------------------------
+def rmsnorm(x, weight, eps, residual=None, out=None, residual_out=None):
+    n = x.shape[-1]
+    m = x.numel() // n
+    if out is None:
+        out = torch.empty_like(x)
+    if residual is not None and residual_out is None:
+        residual_out = residual
+    _check(lib().kuiops_rmsnorm(dtype_code(x.dtype), m, n, x.data_ptr(), _ptr(residual), weight.data_ptr(),
+                                float(eps), out.data_ptr(), _ptr(residual_out), _stream()), "rmsnorm")
+    return out
+
+
+def swiglu(gate_up, out=None):
+    n2 = gate_up.shape[-1]
+    m = gate_up.numel() // n2
+    if out is None:
+        out = torch.empty(tuple(gate_up.shape[:-1]) + (n2 // 2,), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().kuiops_swiglu(dtype_code(gate_up.dtype), m, n2 // 2, gate_up.data_ptr(), out.data_ptr(),
+                               _stream()), "swiglu")
+    return out
+
+
+def rope_qkv(qkv, hq, hk, d, positions, theta, k_cache=None, v_cache=None, rows_per_seq=1):
+    rows = qkv.numel() // qkv.shape[-1]
+    cap = k_cache.shape[2] if k_cache is not None else 0
+    _check(lib().kuiops_rope_qkv(dtype_code(qkv.dtype), rows, hq, hk, d, qkv.data_ptr(), qkv.stride(-2) if qkv.dim() > 1 else qkv.shape[-1],
+                                 positions.data_ptr(), float(theta), _ptr(k_cache), _ptr(v_cache), cap,
+                                 rows_per_seq, _stream()), "rope_qkv")
+    return qkv
+
+
+def embedding(table, ids):
+    ids_c = ids.contiguous()
+    out = torch.empty(tuple(ids_c.shape) + (table.shape[1],), dtype=table.dtype, device=table.device)
+    _check(lib().kuiops_embedding(table.element_size(), ids_c.numel(), table.shape[1], table.shape[0],
+                                  table.data_ptr(), ids_c.data_ptr(), out.data_ptr(),
+                                  _status(table.device).data_ptr(), _stream()), "embedding")
+    return out

@@ -1,0 +1,298 @@
+"""CPU restatement of what each kuiops operator computes.  TEST INFRASTRUCTURE ONLY.
+
+Nothing in the product imports this module: it is the checker used by ``tests/``, by
+``__graft_entry__.smoke()`` and by the ``cpu_baseline`` / ``--impl reference`` legs of
+``bench.py``.  The product path fails loudly when the CUDA library is missing instead of
+falling back to anything here.
+
+Where the reference states an operator's meaning itself (the F* specifications of the data
+movement kernels, the wrapper conventions) the function below restates that text in numpy loops
+or index arithmetic and cites it.  Where the arithmetic lives in the external, un-vendored
+Kuiper repository (GEMM, softmax, attention, maps: see the ``open`` lines cited per function)
+the restatement follows the published definition of the aten op, which is also what every test
+of the reference compares against (tests/test_jit_ops.py:58,93,150,187,227,270,309,394 there).
+Parity pin: ``tests/test_oracle_golden.py`` checks every function here against
+``tests/golden/ops_golden.npz``, produced by ``tests/golden/gen_op_golden.py`` from PyTorch
+eager (the reference tests' own oracle), and the comparator against the reference's
+``kuipy._verify_compare`` outputs recorded in ``tests/golden/verify_golden.json``.  For topk,
+isin, index, reduce and causal / grouped-query attention the reference has neither kernel nor
+test: those are pinned by PyTorch semantics only.
+"""
+import math
+
+import numpy as np
+
+# ---------------------------------------------------------------------------------------------
+# data movement: restated from the F* specifications
+# ---------------------------------------------------------------------------------------------
+
+
+def gather(inp: np.ndarray, dim: int, idx: np.ndarray) -> np.ndarray:
+    """out[x] = inp[x with x[dim] := idx[x]] for every cell x of idx
+    (kuiops/gather/Kuiops.Gather.fsti:25-36, kernel body Kuiops.Gather.fst:93-99)."""
+    assert inp.ndim == idx.ndim
+    out = np.empty(idx.shape, dtype=inp.dtype)
+    for x in np.ndindex(*idx.shape):
+        src = list(x)
+        j = int(idx[x])
+        assert 0 <= j < inp.shape[dim], "index outside the gathered axis"
+        src[dim] = j
+        out[x] = inp[tuple(src)]
+    return out
+
+
+def gather_fast(inp, dim, idx):
+    """Vectorised form of ``gather`` for sizes the loop cannot finish; equal by construction
+    (numpy's take_along_axis on the leading idx-shaped block of inp)."""
+    sl = tuple(slice(0, idx.shape[d]) if d != dim else slice(None) for d in range(inp.ndim))
+    return np.take_along_axis(inp[sl], idx, axis=dim)
+
+
+def scatter(self_: np.ndarray, dim: int, idx: np.ndarray, src: np.ndarray) -> np.ndarray:
+    """out = copy of self; out[i with i[dim] := idx[i]] = src[i] for every cell i of src, visited
+    in row-major order (kuiops/scatter/Kuiops.Scatter.fsti:29-52; the kernel needs the index map
+    to be injective, :36-41, so the visiting order cannot matter for valid inputs)."""
+    assert idx.shape == src.shape and self_.ndim == src.ndim
+    out = self_.copy()
+    for i in np.ndindex(*src.shape):
+        dst = list(i)
+        j = int(idx[i])
+        assert 0 <= j < self_.shape[dim]
+        dst[dim] = j
+        out[tuple(dst)] = src[i]
+    return out
+
+
+def scatter_fast(self_, dim, idx, src):
+    out = self_.copy()
+    sl = tuple(slice(0, src.shape[d]) if d != dim else slice(None) for d in range(out.ndim))
+    np.put_along_axis(out[sl], idx, src, axis=dim)
+    return out
+
+
+def cat(tensors, dim: int) -> np.ndarray:
+    """Output cell x comes from the input whose range along `dim` contains x[dim], at that
+    coordinate minus the range start (binary form: kuiops/cat/Kuiops.Cat.fsti:40-60, fcat in
+    Kuiops.Cat.fst:150-186; n-ary is the fold of the binary form)."""
+    first = tensors[0]
+    shape = list(first.shape)
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    out = np.empty(shape, dtype=first.dtype)
+    start = 0
+    for t in tensors:
+        sl = [slice(None)] * out.ndim
+        sl[dim] = slice(start, start + t.shape[dim])
+        out[tuple(sl)] = t
+        start += t.shape[dim]
+    return out
+
+
+def index(self_: np.ndarray, first_dim: int, indices) -> np.ndarray:
+    """aten.index.Tensor with index tensors on the adjacent dims starting at first_dim: the
+    broadcast index shape replaces those dims; negative indices wrap (signature recorded in the
+    reference's KERNELS.md:67; no reference kernel)."""
+    bshape = np.broadcast_shapes(*[i.shape for i in indices])
+    ib = [np.broadcast_to(i, bshape) for i in indices]
+    pre, post = self_.shape[:first_dim], self_.shape[first_dim + len(indices):]
+    out = np.empty(tuple(pre) + tuple(bshape) + tuple(post), dtype=self_.dtype)
+    for p in np.ndindex(*pre):
+        for b in np.ndindex(*bshape):
+            coord = []
+            for k, i in enumerate(ib):
+                v = int(i[b])
+                ext = self_.shape[first_dim + k]
+                if v < 0:
+                    v += ext
+                assert 0 <= v < ext
+                coord.append(v)
+            out[p + b] = self_[p + tuple(coord)]
+    return out
+
+
+def isin(elements: np.ndarray, test_elements: np.ndarray, invert: bool = False) -> np.ndarray:
+    """Membership of each element in the test set (KERNELS.md:56-57; no reference kernel)."""
+    members = set(int(v) for v in np.asarray(test_elements).reshape(-1))
+    flat = np.fromiter((int(v) in members for v in elements.reshape(-1)), dtype=bool, count=elements.size)
+    out = flat.reshape(elements.shape)
+    return ~out if invert else out
+
+
+def topk(x: np.ndarray, k: int):
+    """Largest-k per row, sorted by value descending and, among equal values, index ascending;
+    NaN ranks above +inf (aten.topk signature in KERNELS.md:58; no reference kernel; the tie
+    rule is the stable descending sort)."""
+    rows = x.reshape(-1, x.shape[-1])
+    vals = np.empty((rows.shape[0], k), dtype=x.dtype)
+    idxs = np.empty((rows.shape[0], k), dtype=np.int64)
+    for r in range(rows.shape[0]):
+        row = rows[r]
+        key = np.where(np.isnan(row), np.inf, row).astype(np.float64)
+        nan_rank = np.isnan(row).astype(np.int64)
+        # lexsort: last key is primary.  primary: NaN first, then value descending, then index
+        order = np.lexsort((np.arange(row.size), -key, -nan_rank))[:k]
+        idxs[r] = order
+        vals[r] = row[order]
+    return vals.reshape(x.shape[:-1] + (k,)), idxs.reshape(x.shape[:-1] + (k,))
+
+
+def reduce_fold(op: str, a: np.ndarray):
+    """Exact left-to-right fold of the flat tensor under an associative f
+    (kuiops/reduce/Kuiops.HReducePoly.Exact.fsti:26-46): all / any over bool, max."""
+    flat = a.reshape(-1)
+    if op == "all":
+        acc = True
+        for v in flat:
+            acc = acc and bool(v)
+        return np.bool_(acc)
+    if op == "any":
+        acc = False
+        for v in flat:
+            acc = acc or bool(v)
+        return np.bool_(acc)
+    if op == "max":
+        acc = flat[0]
+        for v in flat[1:]:
+            if np.isnan(acc):
+                break
+            if np.isnan(v) or v > acc:
+                acc = v
+        return acc
+    raise ValueError(op)
+
+
+# ---------------------------------------------------------------------------------------------
+# floating point operators (fp64 accumulation, compared within the stated tolerances)
+# ---------------------------------------------------------------------------------------------
+
+
+def mm(A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    """C[M,N] = A[M,K] B[K,N] (Klas.GEMM.* opened at kuiops/mm/Kuiops.Mm.Inst.fst.j2:9-15)."""
+    return A.astype(np.float64) @ B.astype(np.float64)
+
+
+def addmm(C: np.ndarray, A: np.ndarray, B: np.ndarray, alpha=1.0, beta=1.0) -> np.ndarray:
+    """beta*C + alpha*(A B) with C broadcast over rows when 1-D
+    (kuiops/addmm/wrapper_addmm.cu.j2:7-24, Kuiops.Addmm.Inst.fst.j2:11-12)."""
+    return beta * C.astype(np.float64) + alpha * (A.astype(np.float64) @ B.astype(np.float64))
+
+
+def bmm(A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    """C[b] = A[b] B[b] (kuiops/bmm/Kuiops.Bmm.fst:13-23)."""
+    return np.einsum("bmk,bkn->bmn", A.astype(np.float64), B.astype(np.float64))
+
+
+def softmax_lastdim(X: np.ndarray) -> np.ndarray:
+    """exp(x - max) / sum over the last axis (Klas.RowSoftmax, kuiops/softmax/Kuiops.Softmax.Inst.fst.j2:8-11)."""
+    x = X.astype(np.float64)
+    z = np.exp(x - x.max(axis=-1, keepdims=True))
+    return z / z.sum(axis=-1, keepdims=True)
+
+
+def mean_lastdim(X: np.ndarray) -> np.ndarray:
+    """sum_j (x[i,j] / n), keepdim: the division is part of the pre-map
+    (kuiops/mean/Kuiops.Mean.fsti:25-32)."""
+    x = X.astype(np.float64)
+    return (x / x.shape[-1]).sum(axis=-1, keepdims=True)
+
+
+def sdpa(Q, K, V, bias=None, scale=None, is_causal=False):
+    """out = softmax(scale * Q K^T + bias, causal mask bottom-right aligned) V, and
+    lse = log sum exp of the masked scores (kuiops/sdpa/Kuiops.Sdpa.fst.1:13-27 for the biased,
+    unmasked form and the host-side bias convention at kuipy/kuiops.py:673-677; LSE check at
+    tests/test_jit_ops.py:191-193).  Q (n,h,l,e), K (n,h_kv,s,e), V (n,h_kv,s,ev)."""
+    Q, K, V = Q.astype(np.float64), K.astype(np.float64), V.astype(np.float64)
+    n, h, l, e = Q.shape
+    hkv, s = K.shape[1], K.shape[2]
+    g = h // hkv
+    if scale is None:
+        scale = 1.0 / math.sqrt(e)
+    Kx, Vx = np.repeat(K, g, axis=1), np.repeat(V, g, axis=1)
+    sc = np.einsum("nhle,nhse->nhls", Q, Kx) * scale
+    if bias is not None:
+        sc = sc + np.broadcast_to(bias.astype(np.float64), sc.shape)
+    if is_causal:
+        i = np.arange(l)[:, None]
+        j = np.arange(s)[None, :]
+        sc = np.where(j <= i + (s - l), sc, -np.inf)
+    mx = sc.max(axis=-1, keepdims=True)
+    mx = np.where(np.isfinite(mx), mx, 0.0)
+    p = np.exp(sc - mx)
+    den = p.sum(axis=-1, keepdims=True)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        lse = (np.log(den) + mx)[..., 0]
+        out = np.einsum("nhls,nhse->nhle", np.where(den > 0, p / den, 0.0), Vx)
+    return out, lse
+
+
+_MAPS = {
+    "silu": lambda x, c0, c1: x / (1.0 + np.exp(-x)),          # x * 1/(1+exp(-x)), Kuiops.Elementwise.fsti
+    "neg": lambda x, c0, c1: -x,
+    "rsqrt": lambda x, c0, c1: 1.0 / np.sqrt(x),
+    "cos": lambda x, c0, c1: np.cos(x),
+    "sin": lambda x, c0, c1: np.sin(x),
+    "pow": lambda x, c0, c1: np.power(x, c0),
+    "square": lambda x, c0, c1: x * x,
+    "add": lambda x, c0, c1: x + c1 * c0,
+    "mul": lambda x, c0, c1: x * c0,
+    "sub": lambda x, c0, c1: x - c1 * c0,
+    "div": lambda x, c0, c1: x / c0,
+    "gelu": lambda x, c0, c1: 0.5 * x * (1.0 + np.vectorize(math.erf)(x / math.sqrt(2.0))),
+}
+
+
+def map_op(op: str, X: np.ndarray, other=0.0, alpha=1.0) -> np.ndarray:
+    """Elementwise map; ``other`` is a scalar or a same-shape array
+    (kuiops/elementwise/Kuiops.Elementwise.fsti, lambdas built at kuipy/kuiops.py:292-296)."""
+    x = X.astype(np.float64)
+    o = other.astype(np.float64) if isinstance(other, np.ndarray) else float(other)
+    with np.errstate(all="ignore"):
+        return _MAPS[op](x, o, float(alpha))
+
+
+def compare_scalar(op: str, X: np.ndarray, c: float) -> np.ndarray:
+    return {"eq": X == c, "le": X <= c, "lt": X < c}[op]
+
+
+def where(cond, a, b):
+    return np.where(cond.astype(bool), a, b)
+
+
+def rmsnorm(x, w, eps, residual=None):
+    """Llama RMSNorm: h = x (+ residual); y = w * (h * rsqrt(mean(h^2) + eps)) with fp32 statistics."""
+    h = x.astype(np.float64) + (residual.astype(np.float64) if residual is not None else 0.0)
+    y = h / np.sqrt((h * h).mean(axis=-1, keepdims=True) + eps)
+    return y * w.astype(np.float64), h
+
+
+def rope(x, positions, theta):
+    """Rotate-half rotary embedding on x (rows, heads, d) at integer positions (rows,)."""
+    rows, heads, d = x.shape
+    half = d // 2
+    inv = theta ** (-np.arange(half, dtype=np.float64) * 2.0 / d)
+    ang = positions.astype(np.float64)[:, None] * inv[None, :]
+    cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+    x = x.astype(np.float64)
+    lo, hi = x[..., :half], x[..., half:]
+    return np.concatenate([lo * cos - hi * sin, hi * cos + lo * sin], axis=-1)
+
+
+# ---------------------------------------------------------------------------------------------
+# comparators
+# ---------------------------------------------------------------------------------------------
+
+
+def rel_frobenius(out: np.ndarray, ref: np.ndarray) -> float:
+    """||out - ref|| / (||ref|| + 1e-12) over positions where both are finite: the reference's
+    verify-mode metric (kuipy/__init__.py:193-224)."""
+    o, r = out.astype(np.float64), ref.astype(np.float64)
+    ok = np.isfinite(o) & np.isfinite(r)
+    if not ok.any():
+        return 0.0
+    return float(np.linalg.norm((o - r)[ok]) / (np.linalg.norm(r[ok]) + 1e-12))
+
+
+def max_rel_err(out: np.ndarray, ref: np.ndarray) -> float:
+    """max |out - ref| / max |ref|: the "max relative error" of the bf16 GEMM / attention bar."""
+    o, r = out.astype(np.float64), ref.astype(np.float64)
+    scale = np.abs(r).max()
+    return float(np.abs(o - r).max() / (scale if scale > 0 else 1.0))

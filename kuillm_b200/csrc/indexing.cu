@@ -339,7 +339,8 @@ int kuiops_scatter(uint32_t elem_bytes, uint32_t rank, uint32_t dim, const uint6
   if (!self_shape || !src_shape || !self_ || !src || !idx || !out) return KUIOPS_EINVAL;
   uint64_t numel = 1, total_addr = 1;
   for (uint32_t d = 0; d < rank; ++d) {
-    if (d != dim && src_shape[d] > self_shape[d]) return KUIOPS_EINVAL;
+    // an injective index map cannot address more cells than the axis has, so <= holds on `dim` too
+    if (src_shape[d] > self_shape[d]) return KUIOPS_EINVAL;
     numel *= src_shape[d];
     total_addr *= self_shape[d];
   }

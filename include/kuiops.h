@@ -168,6 +168,22 @@ KUIOPS_API int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
                 float* lse,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
 
+/* Same, with the number of keys of each batch entry read from device memory:
+ * kv_lens[b] (int64, clamped to [0, s]) replaces s for entry b, s stays the
+ * upper bound (the cache capacity in use).  A decode step whose launch
+ * arguments never change can then be captured once in a CUDA graph and replayed
+ * while the cache grows.  kv_lens == NULL is kuiops_sdpa.  Always runs on the
+ * split-KV SIMT kernel.  No counterpart in the reference. */
+KUIOPS_API int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
+                uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                const void* bias, float scale, int is_causal,
+                void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl,
+                float* lse, const int64_t* kv_lens,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
 /* ======================================================================== */
 /* Streaming reductions                                                     */
 /* ======================================================================== */
@@ -305,6 +321,9 @@ KUIOPS_API int kuiops_isin_i64(uint64_t n, const int64_t* elements, uint64_t m, 
 /* Unary map, or binary with a scalar constant: Y[i] = op(X[i], c0, c1). */
 KUIOPS_API int kuiops_map (int dtype, int op, uint64_t len, const void* X, void* Y, double c0, double c1,
                 kuiops_stream_t stream);
+/* x[i] += delta over int64, in place (aten.add.Tensor(T(1,int64), int), listed as not
+ * connected in the reference's KERNELS.md:9; used for device-side position counters). */
+KUIOPS_API int kuiops_add_i64(uint64_t len, int64_t* x, int64_t delta, kuiops_stream_t stream);
 /* Binary same-shape map: Y[i] = op(X[i], B[i]); c1 is the `alpha` of add/sub. */
 KUIOPS_API int kuiops_map2(int dtype, int op, uint64_t len, const void* X, const void* B, void* Y, double c1,
                 kuiops_stream_t stream);

@@ -299,6 +299,13 @@ embedding_kernel(uint64_t rows, uint64_t width_p, uint64_t vocab, const P* __res
   }
 }
 
+// x[i] += delta over int64 (position counters kept on the device between captured decode steps)
+__global__ void __launch_bounds__(256)
+add_i64_kernel(uint64_t len, long long* x, long long delta) {
+  const uint64_t gs = uint64_t(gridDim.x) * blockDim.x;
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < len; i += gs) x[i] += delta;
+}
+
 }  // namespace kuiops
 
 using namespace kuiops;
@@ -312,6 +319,12 @@ int kuiops_map(int dtype, int op, uint64_t len, const void* X, void* Y, double c
     case KUIOPS_F16: return map_launch<__half, false>(op, len, X, nullptr, Y, c0, c1, as_stream(s));
   }
   return KUIOPS_EINVAL;
+}
+
+int kuiops_add_i64(uint64_t len, int64_t* x, int64_t delta, kuiops_stream_t s) {
+  if (len == 0 || !x) return KUIOPS_EINVAL;
+  add_i64_kernel<<<stream_grid(len, 256, 8), 256, 0, as_stream(s)>>>(len, reinterpret_cast<long long*>(x), delta);
+  return check_launch();
 }
 
 int kuiops_map2(int dtype, int op, uint64_t len, const void* X, const void* B, void* Y, double c1, kuiops_stream_t s) {

@@ -263,6 +263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();                      // the allocator instructions want the whole warp converged
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -297,8 +298,14 @@ bool encode_tmap_2byte(CUtensorMap* map, const void* base, uint32_t rank, const 
 }
 
 unsigned int* tc_error_word_device() {
-  unsigned int* ptr = nullptr;
+  // the symbol has one address per device; look it up once for each
+  static std::atomic<unsigned int*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  unsigned int* ptr = cache[dev & 63].load(std::memory_order_acquire);
+  if (ptr) return ptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_tc_error) != cudaSuccess) return nullptr;
+  cache[dev & 63].store(ptr, std::memory_order_release);
   return ptr;
 }
 
@@ -356,9 +363,16 @@ template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, unsigned grid, cudaStream_t st) {
   constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256;
   auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
-  // per-device attribute; cheap enough to set on every call and safe with several devices
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
-    return KUIOPS_ELAUNCH;
+  // the opt-in for large dynamic shared memory is per device: do it once per (kernel, device)
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+      return KUIOPS_ELAUNCH;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
   kern<<<grid, kTcThreads, smem, st>>>(mp, mq, p);
   return check_launch();
 }

@@ -15,6 +15,7 @@ struct SdpaArgs {
   int is_causal;
   void* out; int64_t o_sn, o_sh, o_sl;
   float* lse;
+  const int64_t* kv_lens;   // optional per-batch key counts on the device (<= s)
 };
 
 struct SdpaRowsPlan {

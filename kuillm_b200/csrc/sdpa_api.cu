@@ -21,12 +21,13 @@ size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h
   return sdpa_rows_workspace_bytes(a);
 }
 
-int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
                 const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
                 const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
                 const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
                 const void* bias, float scale, int is_causal,
                 void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl, float* lse,
+                const int64_t* kv_lens,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
   SdpaArgs a = {};
   int rc = fill_args(a, dtype, n, h, h_kv, l, s, e, ev);
@@ -37,10 +38,21 @@ int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, ui
   a.K = K; a.k_sn = k_sn; a.k_sh = k_sh; a.k_ss = k_ss;
   a.V = V; a.v_sn = v_sn; a.v_sh = v_sh; a.v_ss = v_ss;
   a.bias = bias; a.scale = scale; a.is_causal = is_causal ? 1 : 0;
-  a.out = out; a.o_sn = o_sn; a.o_sh = o_sh; a.o_sl = o_sl; a.lse = lse;
+  a.out = out; a.o_sn = o_sn; a.o_sh = o_sh; a.o_sl = o_sl; a.lse = lse; a.kv_lens = kv_lens;
   cudaStream_t st = as_stream(stream);
   if (sdpa_flash_eligible(a)) return sdpa_flash(a, st);
   return sdpa_rows(a, workspace, workspace_bytes, st);
+}
+
+int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                const void* bias, float scale, int is_causal,
+                void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl, float* lse,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
+  return kuiops_sdpa_varlen(dtype, n, h, h_kv, l, s, e, ev, Q, q_sn, q_sh, q_sl, K, k_sn, k_sh, k_ss, V, v_sn, v_sh, v_ss,
+                            bias, scale, is_causal, out, o_sn, o_sh, o_sl, lse, nullptr, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

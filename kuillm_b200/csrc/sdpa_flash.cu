@@ -1,7 +1,344 @@
-// tcgen05 flash-attention forward (placeholder until the kernel lands: nothing is eligible, so
-// every call takes the SIMT kernel).
+// Flash-attention forward on tcgen05 for prefill: bf16 / f16, head dim 128, optional causal mask
+// (bottom-right aligned), grouped-query heads, no bias.
+//
+// A CTA owns 128 query rows of one (batch, head).  K and V arrive in 64-key tiles through a
+// two-slot TMA ring.  Per tile:
+//     S = Q K^T        UMMA 128 x 64 x 128, both operands K-major in shared memory, S in TMEM
+//     softmax          4 warps, one query row per thread: tcgen05.ld S, online max / sum in the
+//                      log2 domain in registers, P = exp2(S - m) written as bf16 into a K-major
+//                      128-byte-swizzled shared tile; the O accumulator in TMEM is rescaled only
+//                      when a row's running max grew by more than 2^8 (the stale max stays exact
+//                      because the final normalisation uses the same max)
+//     O += P V         UMMA 128 x 128 x 64, P K-major from shared memory, V MN-major as loaded
+// The CTA is small enough (112 KB of shared memory, 256 TMEM columns) for two CTAs per SM, so one
+// CTA's softmax overlaps the other's MMAs.  Epilogue: O / l to global, natural-log LSE.
+// This is the causal / grouped-query attention the dispatcher reaches as
+// aten._scaled_dot_product_flash_attention; the reference only has the naive biased kernel
+// (kuiops/sdpa/Kuiops.Sdpa.fst.1) and keeps it disconnected.
 #include "sdpa.cuh"
+#include "tc_ptx.cuh"
+#include <type_traits>
+
 namespace kuiops {
-bool sdpa_flash_eligible(const SdpaArgs&) { return false; }
-int sdpa_flash(const SdpaArgs&, cudaStream_t) { return KUIOPS_EUNSUPPORTED; }
+
+constexpr int FBM = 128;      // query rows per CTA (TMEM lanes)
+constexpr int FBN = 64;       // keys per tile
+constexpr int FD = 128;       // head dim
+constexpr int kFlashThreads = 192;
+constexpr uint32_t F_Q_BYTES = FBM * FD * 2;        // 32 KB: two 64-column halves of 16 KB
+constexpr uint32_t F_K_BYTES = FBN * FD * 2;        // 16 KB: two halves of 8 KB
+constexpr uint32_t F_V_BYTES = FBN * FD * 2;        // 16 KB: two 64-column boxes of 8 KB
+constexpr uint32_t F_P_BYTES = FBM * FBN * 2;       // 16 KB
+constexpr uint32_t F_SMEM = F_Q_BYTES + 2 * (F_K_BYTES + F_V_BYTES) + F_P_BYTES;   // 112 KB
+constexpr uint32_t F_TMEM_COLS = 256;               // S at column 0 (64 used), O at column 128
+constexpr float kRescaleThreshold = 8.0f;           // log2 units
+
+struct FlashParams {
+  uint32_t n, h, h_kv, l, s;
+  float scale_log2;
+  int is_causal;
+  void* out; int64_t o_sn, o_sh, o_sl;
+  float* lse;
+  unsigned int* err;
+};
+
+__device__ __forceinline__ uint64_t flash_global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool flash_wait(uint64_t* bar, uint32_t parity) {
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = flash_global_ns();
+  while (!tc::mbar_try_wait(bar, parity)) {
+    if (flash_global_ns() - t0 > 2000000000ull) return false;
+  }
+  return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kFlashThreads, 2)
+sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  // The 128-byte swizzle atoms need a 1024-byte aligned base.  The dynamic shared window of a
+  // kernel without static shared memory starts on such a boundary; there is no room for padding
+  // (two CTAs must fit one SM), so a misaligned base is reported instead of worked around.
+  extern __shared__ __align__(1024) unsigned char smem[];
+  if ((tc::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.err, 10u);
+    return;
+  }
+  unsigned char* q_s = smem;
+  unsigned char* kv_s = q_s + F_Q_BYTES;                       // slot i: K at kv_s + i*32K, V right after K
+  unsigned char* p_s = kv_s + 2 * (F_K_BYTES + F_V_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + F_P_BYTES);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* v_full = bars + 3;      // 2
+  uint64_t* kv_empty = bars + 5;    // 2
+  uint64_t* s_full = bars + 7;      // 1
+  uint64_t* p_ready = bars + 8;     // 1
+  uint64_t* o_done = bars + 9;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest query tiles (most visible keys under the causal mask) are scheduled first
+  const uint32_t q_tiles = (p.l + FBM - 1) / FBM;
+  const uint32_t qt = q_tiles - 1 - (blockIdx.x % q_tiles);
+  const uint32_t head = (blockIdx.x / q_tiles) % p.h;
+  const uint32_t b = blockIdx.x / (q_tiles * p.h);
+  const uint32_t kvh = head / (p.h / p.h_kv);
+  const uint32_t row0 = qt * FBM;
+  // keys visible to this tile: all of them, or up to the diagonal of its last row
+  uint32_t s_end = p.s;
+  if (p.is_causal) {
+    const uint64_t lim = uint64_t(min(row0 + FBM, p.l) - 1) + (p.s - p.l) + 1;
+    s_end = uint32_t(lim < p.s ? lim : p.s);
+  }
+  const uint32_t n_tiles = (s_end + FBN - 1) / FBN;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
+    tc::mbar_init(s_full, 1);
+    tc::mbar_init(p_ready, 4);
+    tc::mbar_init(o_done, 1);
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmQ); tc::prefetch_tmap(&tmK); tc::prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, F_TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (lane == 0) {
+      tc::mbar_expect_tx(q_full, F_Q_BYTES);
+      tc::tma_load_4d(q_s, &tmQ, q_full, 0, int(row0), int(head), int(b));
+      tc::tma_load_4d(q_s + FBM * 128, &tmQ, q_full, 64, int(row0), int(head), int(b));
+      for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        if (!flash_wait(&kv_empty[slot], ph ^ 1)) { atomicExch(p.err, 11u); break; }
+        unsigned char* ks = kv_s + slot * (F_K_BYTES + F_V_BYTES);
+        unsigned char* vs = ks + F_K_BYTES;
+        const int key0 = int(j * FBN);
+        tc::mbar_expect_tx(&k_full[slot], F_K_BYTES);
+        tc::tma_load_4d(ks, &tmK, &k_full[slot], 0, key0, int(kvh), int(b));
+        tc::tma_load_4d(ks + FBN * 128, &tmK, &k_full[slot], 64, key0, int(kvh), int(b));
+        tc::mbar_expect_tx(&v_full[slot], F_V_BYTES);
+        tc::tma_load_4d(vs, &tmV, &v_full[slot], 0, key0, int(kvh), int(b));
+        tc::tma_load_4d(vs + FBN * 128, &tmV, &v_full[slot], 64, key0, int(kvh), int(b));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ UMMA issuer -------------------------------------------
+    if (lane == 0) {
+      constexpr int is_bf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_qk = tc::make_idesc(is_bf16, 0, 0, FBM, FBN);
+      constexpr uint32_t idesc_pv = tc::make_idesc(is_bf16, 0, 1, FBM, FD);
+      bool ok = flash_wait(q_full, 0);
+      if (!ok) atomicExch(p.err, 12u);
+      const uint32_t qa = tc::smem_u32(q_s), pa = tc::smem_u32(p_s);
+      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        const uint32_t ka = tc::smem_u32(kv_s + slot * (F_K_BYTES + F_V_BYTES));
+        const uint32_t va = ka + F_K_BYTES;
+        if (!flash_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); ok = false; break; }
+        tc::tc_fence_after();
+        // S = Q K^T over the 128 head-dim elements: two 64-wide halves x four 16-wide steps
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = tc::make_smem_desc(qa + hh * (FBM * 128) + kk * 32, 16, 1024);
+            const uint64_t db = tc::make_smem_desc(ka + hh * (FBN * 128) + kk * 32, 16, 1024);
+            tc::umma_f16(tmem_S, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
+          }
+        tc::umma_commit(s_full);
+        if (!flash_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
+        if (!flash_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
+        tc::tc_fence_after();
+        // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, 1024);
+          const uint64_t db = tc::make_smem_desc(va + kk * 2048, FBN * 128, 1024);
+          tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc::umma_commit(&kv_empty[slot]);
+        tc::umma_commit(o_done);
+      }
+    }
+  } else {
+    // ------------------------------ softmax + epilogue ------------------------------------
+    const uint32_t quarter = warp & 3;
+    const uint32_t r = quarter * 32 + lane;               // row inside the tile
+    const uint32_t row = row0 + r;
+    const uint32_t lane_addr = (quarter * 32) << 16;
+    // last key this row may see (inclusive); rows beyond l see nothing useful but stay finite
+    const int64_t row_lim = p.is_causal ? int64_t(min(row, p.l - 1)) + int64_t(p.s) - int64_t(p.l) : int64_t(p.s) - 1;
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+      if (!flash_wait(s_full, j & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      tc::tc_fence_after();
+      float sv[FBN];
+      tc::tmem_ld32(tmem_S + lane_addr, sv);
+      tc::tmem_ld32(tmem_S + lane_addr + 32, sv + 32);
+      tc::tmem_ld_wait();
+      const int64_t key0 = int64_t(j) * FBN;
+      const bool edge = key0 + FBN - 1 > row_lim;          // tile crosses this row's limit (or the end of the keys)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < FBN; ++c) {
+        float v = sv[c] * p.scale_log2;
+        if (edge && key0 + c > row_lim) v = -INFINITY;
+        sv[c] = v;
+        mx = fmaxf(mx, v);
+      }
+      float corr = 1.f;
+      if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
+        const float m_new = fmaxf(mx, m_used);
+        corr = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        m_used = m_new;
+      }
+      const float mm = (m_used == -INFINITY) ? 0.f : m_used;   // a fully masked row keeps p = 0
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < FBN; ++c) { sv[c] = exp2f(sv[c] - mm); rs += sv[c]; }
+      l_run = l_run * corr + rs;
+      if (j > 0) {
+        // the previous P V must be done before P's buffer is overwritten or O is touched
+        if (!flash_wait(o_done, (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+        tc::tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+          for (int c0 = 0; c0 < FD; c0 += 32) {
+            float ov[32];
+            tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
+            tc::tmem_ld_wait();
+            uint32_t ou[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ou[c] = __float_as_uint(ov[c] * corr);
+            tc::tmem_st32(tmem_O + lane_addr + c0, ou);
+          }
+          tc::tmem_st_wait();
+        }
+      }
+      // P row -> K-major 128-byte-swizzled tile: 16-byte chunk c of row r sits at chunk (c ^ (r & 7))
+      unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < FBN / 8; ++c) {
+        Vec16<T> pk;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pk.v[e] = ElemTraits<T>::from_f(sv[c * 8 + e]);
+        *reinterpret_cast<Vec16<T>*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+      }
+      tc::fence_proxy_async();          // make the generic-proxy writes visible to the UMMA (async proxy)
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(p_ready);
+    }
+    if (ok && n_tiles > 0) {
+      if (!flash_wait(o_done, (n_tiles - 1) & 1)) { atomicExch(p.err, 18u); ok = false; }
+    }
+    if (ok) {
+      tc::tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      T* orow = static_cast<T*>(p.out) + size_t(b) * p.o_sn + size_t(head) * p.o_sh + size_t(row) * p.o_sl;
+#pragma unroll
+      for (int c0 = 0; c0 < FD; c0 += 32) {
+        float ov[32];
+        if (n_tiles > 0) {
+          tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
+          tc::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ov[c] = 0.f;
+        }
+        if (row < p.l) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            Vec16<T> o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o.v[e] = ElemTraits<T>::from_f(ov[c + e] * inv);
+            st16(orow + c0 + c, o);
+          }
+        }
+      }
+      if (p.lse && row < p.l)
+        p.lse[(size_t(b) * p.h + head) * p.l + row] = l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, F_TMEM_COLS);
+  }
+}
+
+bool sdpa_flash_eligible(const SdpaArgs& a) {
+  if (a.dtype != KUIOPS_BF16 && a.dtype != KUIOPS_F16) return false;
+  if (a.e != FD || a.ev != FD || a.bias != nullptr || a.kv_lens != nullptr) return false;
+  if (a.l < 64) return false;                       // short query blocks belong to the split-KV kernel
+  if (a.is_causal && a.l > a.s) return false;       // rows without any visible key
+  auto ok_stride = [](int64_t s) { return s > 0 && s % 8 == 0 && uint64_t(s) * 2 < (1ull << 40); };
+  if (!ok_stride(a.q_sl) || !ok_stride(a.k_ss) || !ok_stride(a.v_ss) || a.o_sl % 8) return false;
+  if ((a.h > 1 && (!ok_stride(a.q_sh) || a.o_sh % 8)) || (a.h_kv > 1 && (!ok_stride(a.k_sh) || !ok_stride(a.v_sh)))) return false;
+  if (a.n > 1 && (!ok_stride(a.q_sn) || !ok_stride(a.k_sn) || !ok_stride(a.v_sn) || a.o_sn % 8)) return false;
+  if (!aligned16(a.Q) || !aligned16(a.K) || !aligned16(a.V) || !aligned16(a.out)) return false;
+  const uint64_t ctas = uint64_t(a.n) * a.h * ((a.l + FBM - 1) / FBM);
+  return ctas < (1ull << 31);
+}
+
+template <typename T>
+static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  auto enc = [](CUtensorMap* m, const void* base, uint32_t rows, uint32_t heads, uint32_t n, int64_t s_row,
+                int64_t s_head, int64_t s_n, uint32_t box_rows) {
+    const uint64_t dims[4] = {FD, rows, heads, n};
+    // a dimension of extent 1 may carry any stride; keep it a legal multiple of 16 bytes
+    const uint64_t strides[4] = {1, uint64_t(s_row), uint64_t(heads > 1 ? s_head : s_row * rows),
+                                 uint64_t(n > 1 ? s_n : (heads > 1 ? s_head * heads : s_row * rows))};
+    const uint32_t box[4] = {64, box_rows, 1, 1};
+    return encode_tmap_2byte(m, base, 4, dims, strides, box);
+  };
+  if (!enc(&mq, a.Q, a.l, a.h, a.n, a.q_sl, a.q_sh, a.q_sn, FBM)) return KUIOPS_EDRIVER;
+  if (!enc(&mk, a.K, a.s, a.h_kv, a.n, a.k_ss, a.k_sh, a.k_sn, FBN)) return KUIOPS_EDRIVER;
+  if (!enc(&mv, a.V, a.s, a.h_kv, a.n, a.v_ss, a.v_sh, a.v_sn, FBN)) return KUIOPS_EDRIVER;
+  FlashParams p = {};
+  p.n = a.n; p.h = a.h; p.h_kv = a.h_kv; p.l = a.l; p.s = a.s;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.is_causal = a.is_causal;
+  p.out = a.out; p.o_sn = a.o_sn; p.o_sh = a.o_sh; p.o_sl = a.o_sl; p.lse = a.lse;
+  p.err = tc_error_word_device();
+  if (!p.err) return KUIOPS_ELAUNCH;
+  constexpr size_t smem = F_SMEM + 128;
+  auto kern = sdpa_flash_kernel<T>;
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return KUIOPS_ELAUNCH;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  const unsigned grid = unsigned(uint64_t(a.n) * a.h * ((a.l + FBM - 1) / FBM));
+  kern<<<grid, kFlashThreads, smem, st>>>(mq, mk, mv, p);
+  return check_launch();
+}
+
+int sdpa_flash(const SdpaArgs& a, cudaStream_t st) {
+  if (a.dtype == KUIOPS_BF16) return flash_launch<__nv_bfloat16>(a, st);
+  return flash_launch<__half>(a, st);
+}
+
 }  // namespace kuiops

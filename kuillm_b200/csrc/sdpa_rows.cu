@@ -67,9 +67,15 @@ sdpa_rows_kernel(const SdpaArgs p, const SdpaRowsPlan pl) {
   const uint32_t kvh = (hgrp * pl.rows_h) / G;
   const uint32_t rows = pl.rows_h * pl.rows_l;
 
+  // keys of this batch entry (a device-side count lets one captured launch serve a growing cache)
+  uint32_t S = p.s;
+  if (p.kv_lens) {
+    const long long kl = p.kv_lens[b];
+    S = kl < 0 ? 0u : (kl < (long long)p.s ? uint32_t(kl) : p.s);
+  }
   // key slice of this split
-  const uint32_t per = (p.s + pl.splits - 1) / pl.splits;
-  const uint32_t s_lo = min(split * per, p.s), s_hi_raw = min(s_lo + per, p.s);
+  const uint32_t per = (S + pl.splits - 1) / pl.splits;
+  const uint32_t s_lo = min(split * per, S), s_hi_raw = min(s_lo + per, S);
 
   // stage the query rows (pre-multiplied by scale * log2 e) and find the causal limits
   const float qmul = p.scale * kLog2eF;
@@ -91,8 +97,8 @@ sdpa_rows_kernel(const SdpaArgs p, const SdpaRowsPlan pl) {
   for (int r = 0; r < R; ++r) {
     const uint32_t li = lblk * pl.rows_l + uint32_t(r) % pl.rows_l;
     if (uint32_t(r) < rows && li < p.l) {
-      const long long c = p.is_causal ? (long long)li + (long long)p.s - (long long)p.l : (long long)p.s - 1;
-      lim[r] = int(c < (long long)p.s - 1 ? c : (long long)p.s - 1);
+      const long long c = p.is_causal ? (long long)li + (long long)S - (long long)p.l : (long long)S - 1;
+      lim[r] = int(c < (long long)S - 1 ? c : (long long)S - 1);
     } else {
       lim[r] = -1;
     }

@@ -1,0 +1,233 @@
+"""A Llama-shaped decoder built only from kuiops kernels: the whole-model harness of the library.
+
+The reference runs HuggingFace ``model.generate`` under its dispatch mode (infer.py:135-148) and
+so pays one Python dispatch per aten op.  This harness issues the same operator sequence
+directly through the C ABI (embedding, RMSNorm, fused QKV GEMM, rotary + KV append, attention,
+output GEMM, SwiGLU MLP, final norm, vocabulary GEMM, arg-max), with a static KV cache instead
+of the per-token ``cat`` along the sequence axis.  It exists to measure decode + prefill
+throughput on the Llama-3-8B shape and to check the operator library end to end; it is not a
+model zoo.  Every compute op inside ``prefill`` / ``decode_step`` is a kuiops kernel; PyTorch is
+used for buffers, the position / length bookkeeping tensors, copies between static buffers, and
+CUDA-graph capture of the decode step.
+
+Parallel forms: batch data-parallel is "one Decoder per rank on its slice of the batch, no
+collective"; tensor-parallel splits QKV / gate-up by output columns and O / down by input rows
+across ``tp`` ranks with one all-reduce after each row-split GEMM (two per layer).
+"""
+from dataclasses import dataclass
+
+import torch
+
+from .kuipy import _ffi
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    d_ff: int = 14336
+    vocab: int = 128256
+    eps: float = 1e-5
+    rope_theta: float = 5e5
+    dtype: torch.dtype = torch.bfloat16
+
+    @staticmethod
+    def llama3_8b():
+        return DecoderConfig()
+
+    @staticmethod
+    def tiny(**kw):
+        base = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=1000)
+        base.update(kw)
+        return DecoderConfig(**base)
+
+    def params(self):
+        per_layer = (self.d_model * (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+                     + self.n_heads * self.head_dim * self.d_model + 3 * self.d_model * self.d_ff + 2 * self.d_model)
+        return self.n_layers * per_layer + 2 * self.vocab * self.d_model + self.d_model
+
+
+class Decoder:
+    """Weights are stored as [out_features, in_features] (the Linear layout), i.e. the
+    ``trans_b`` operand form of ``kuiops_gemm``, so no transpose is ever materialised."""
+
+    def __init__(self, cfg: DecoderConfig, device="cuda", seed=0, tp_rank=0, tp_size=1, tp_group=None,
+                 init_std=0.02):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
+        assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.d_ff % tp_size == 0
+        self.hq, self.hk = cfg.n_heads // tp_size, cfg.n_kv_heads // tp_size
+        self.ff = cfg.d_ff // tp_size
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        d, hd, dt = cfg.d_model, cfg.head_dim, cfg.dtype
+
+        def w(*shape):
+            return (torch.randn(*shape, generator=g, device=self.device, dtype=torch.float32) * init_std).to(dt)
+
+        # every rank draws the full-size tensors from the same seed and keeps its shard, so a
+        # tensor-parallel run holds exactly the weights of the single-GPU run
+        def shard_rows(t, n_blocks_total, block):   # split output features in whole blocks
+            per = n_blocks_total // tp_size
+            return t[tp_rank * per * block:(tp_rank + 1) * per * block].contiguous()
+
+        self.embed = w(cfg.vocab, d)
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            wq, wk, wv = w(cfg.n_heads * hd, d), w(cfg.n_kv_heads * hd, d), w(cfg.n_kv_heads * hd, d)
+            wo = w(d, cfg.n_heads * hd)
+            wg, wu, wd = w(cfg.d_ff, d), w(cfg.d_ff, d), w(d, cfg.d_ff)
+            layer = dict(
+                wqkv=torch.cat([shard_rows(wq, cfg.n_heads, hd), shard_rows(wk, cfg.n_kv_heads, hd),
+                                shard_rows(wv, cfg.n_kv_heads, hd)], 0).contiguous(),
+                wo=wo[:, tp_rank * self.hq * hd:(tp_rank + 1) * self.hq * hd].contiguous(),
+                wgu=torch.cat([shard_rows(wg, cfg.d_ff, 1), shard_rows(wu, cfg.d_ff, 1)], 0).contiguous(),
+                wd=wd[:, tp_rank * self.ff:(tp_rank + 1) * self.ff].contiguous(),
+                n1=torch.ones(d, device=self.device, dtype=dt), n2=torch.ones(d, device=self.device, dtype=dt))
+            del wq, wk, wv, wo, wg, wu, wd
+            self.layers.append(layer)
+        self.norm_f = torch.ones(d, device=self.device, dtype=dt)
+        self.lm_head = w(cfg.vocab, d)
+        self.k_cache = self.v_cache = None
+        self.cap = 0
+        self.length = 0
+
+    # ---- state ---------------------------------------------------------------------------
+    def alloc_cache(self, batch, capacity):
+        shape = (self.cfg.n_layers, batch, self.hk, capacity, self.cfg.head_dim)
+        self.k_cache = torch.zeros(shape, device=self.device, dtype=self.cfg.dtype)
+        self.v_cache = torch.zeros(shape, device=self.device, dtype=self.cfg.dtype)
+        self.cap, self.length, self.batch = capacity, 0, batch
+
+    def _allreduce(self, t):
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(t, group=self.tp_group)
+        return t
+
+    # ---- one forward over `seq` new positions per sequence -------------------------------------
+    def _forward(self, ids, positions, seq, last_only=True, kv_lens=None):
+        """kv_lens: device int64 [B] key counts; when given the attention reads the whole cache
+        capacity bounded by them, so the launch arguments do not depend on the step."""
+        cfg = self.cfg
+        B = ids.shape[0]
+        hd, hq, hk = cfg.head_dim, self.hq, self.hk
+        rows = B * seq
+        x = _ffi.embedding(self.embed, ids.reshape(-1))                  # [rows, d]
+        resid = None
+        start, end = self.length, self.length + seq
+        for li, L in enumerate(self.layers):
+            if resid is None:
+                h = _ffi.rmsnorm(x, L["n1"], cfg.eps)
+                resid = x
+            else:
+                h = _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)      # resid += x ; h = norm(resid)
+            qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)                  # [rows, (hq + 2 hk) * hd]
+            _ffi.rope_qkv(qkv, hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
+            W = qkv.shape[1]
+            q4 = qkv.as_strided((B, hq, seq, hd), (seq * W, hd, W, 1))
+            attn = torch.empty((rows, hq * hd), device=self.device, dtype=cfg.dtype)
+            o4 = attn.as_strided((B, hq, seq, hd), (seq * hq * hd, hd, hq * hd, 1))
+            if start == 0:
+                # prefill: keys and values of this call are still in the packed projection
+                k4 = qkv.as_strided((B, hk, seq, hd), (seq * W, hd, W, 1), hq * hd)
+                v4 = qkv.as_strided((B, hk, seq, hd), (seq * W, hd, W, 1), (hq + hk) * hd)
+            elif kv_lens is not None:
+                k4, v4 = self.k_cache[li], self.v_cache[li]
+            else:
+                k4 = self.k_cache[li][:, :, :end]
+                v4 = self.v_cache[li][:, :, :end]
+            _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4, kv_lens=kv_lens)
+            o = self._allreduce(_ffi.gemm(attn, L["wo"], trans_b=True))
+            h2 = _ffi.rmsnorm(o, L["n2"], cfg.eps, residual=resid)
+            act = _ffi.swiglu(_ffi.gemm(h2, L["wgu"], trans_b=True))
+            x = self._allreduce(_ffi.gemm(act, L["wd"], trans_b=True))
+        self.length = end
+        if last_only and seq > 1:
+            # only the last position of each sequence feeds the vocabulary GEMM
+            last = torch.arange(seq - 1, rows, seq, device=self.device)
+            x = _ffi.index(x, 0, [last])
+            resid = _ffi.index(resid, 0, [last])
+        hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
+        return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab]
+
+    def prefill(self, ids):
+        B, S = ids.shape
+        assert self.k_cache is not None and S <= self.cap and self.length == 0
+        positions = torch.arange(S, device=self.device).repeat(B)
+        return self._forward(ids, positions, S)
+
+    def decode_step(self, ids):
+        B = ids.shape[0]
+        positions = torch.full((B,), self.length, device=self.device, dtype=torch.int64)
+        return self._forward(ids.reshape(B, 1), positions, 1)
+
+    # ---- captured decode step -----------------------------------------------------------------
+    def _graph_step(self):
+        """One self-advancing decode step on static buffers: token in -> logits -> arg-max ->
+        token out, then the token is fed back and the device-side counters move on."""
+        B = self._tok.shape[0]
+        logits = self._forward(self._tok.reshape(B, 1), self._pos, 1, kv_lens=self._kvlen)
+        self.length -= 1                        # the host counter is advanced by the caller per replay
+        nxt = _ffi.argmax_lastdim(logits)
+        self._tok_out.copy_(nxt)
+        self._tok.copy_(nxt)
+        _ffi.add_i64_(self._pos, 1)
+        _ffi.add_i64_(self._kvlen, 1)
+
+    def capture_decode(self, batch):
+        """Capture the decode step in a CUDA graph (launch-bound otherwise: ~290 kernels per token)."""
+        dev = self.device
+        self._tok = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self._tok_out = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self._pos = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self._kvlen = torch.ones(batch, dtype=torch.int64, device=dev)
+        saved = self.length
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                  # warm-up on the capture stream: scratch buffers get allocated here
+                self.length = 1
+                self._pos.fill_(1)
+                self._kvlen.fill_(2)
+                self._graph_step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self._graph = torch.cuda.CUDAGraph()
+        self.length = 1
+        n0 = _ffi.launch_count()
+        with torch.cuda.graph(self._graph, stream=side):
+            self._graph_step()
+        self.graph_launches = _ffi.launch_count() - n0      # kuiops kernels replayed per captured step
+        self.length = saved
+        return self._graph
+
+    def decode_graph(self, first_tok, steps, out=None):
+        """Run `steps` captured decode steps starting from token `first_tok` at the current length."""
+        B = first_tok.shape[0]
+        if out is None:
+            out = torch.empty((B, steps), dtype=torch.int64, device=self.device)
+        self._tok.copy_(first_tok)
+        self._pos.fill_(self.length)
+        self._kvlen.fill_(self.length + 1)
+        for t in range(steps):
+            self._graph.replay()
+            out[:, t].copy_(self._tok_out)
+            self.length += 1
+        return out
+
+    def generate(self, ids, new_tokens, use_graph=False):
+        """Greedy decoding; returns the [B, new_tokens] generated ids."""
+        logits = self.prefill(ids)
+        tok = _ffi.argmax_lastdim(logits)
+        if use_graph and new_tokens > 1:
+            if getattr(self, "_graph", None) is None or self._tok.shape[0] != ids.shape[0]:
+                self.capture_decode(ids.shape[0])
+            rest = self.decode_graph(tok, new_tokens - 1)
+            return torch.cat([tok[:, None], rest], 1)
+        out = [tok]
+        for _ in range(new_tokens - 1):
+            tok = _ffi.argmax_lastdim(self.decode_step(tok))
+            out.append(tok)
+        return torch.stack(out, 1)

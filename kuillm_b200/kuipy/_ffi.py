@@ -59,6 +59,11 @@ SIGNATURES = {
                     [c_void_p, c_i64, c_i64, c_i64] * 3 +
                     [c_void_p, c_float, c_int, c_void_p, c_i64, c_i64, c_i64, c_void_p,
                      c_void_p, c_size_t, c_void_p]),
+    "kuiops_sdpa_varlen": (c_int, [c_int] + [c_u32] * 7 +
+                           [c_void_p, c_i64, c_i64, c_i64] * 3 +
+                           [c_void_p, c_float, c_int, c_void_p, c_i64, c_i64, c_i64, c_void_p, c_void_p,
+                            c_void_p, c_size_t, c_void_p]),
+    "kuiops_add_i64": (c_int, [c_u64, c_void_p, c_i64, c_void_p]),
     "kuiops_topk_f32": (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "kuiops_gather": (c_int, [c_u32, c_u32, c_u32, _P64, _P64, c_void_p, c_void_p, c_void_p, c_u64,
                               c_void_p, c_void_p]),
@@ -280,8 +285,9 @@ def bmm(A, B):
 # --------------------------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------------------------
-def sdpa(Q, K, V, *, bias=None, scale=None, is_causal=False, need_lse=True, out=None):
-    """Q (n,h,l,e), K (n,h_kv,s,e), V (n,h_kv,s,ev) -> out (n,h,l,ev), lse (n,h,l) fp32."""
+def sdpa(Q, K, V, *, bias=None, scale=None, is_causal=False, need_lse=True, out=None, kv_lens=None):
+    """Q (n,h,l,e), K (n,h_kv,s,e), V (n,h_kv,s,ev) -> out (n,h,l,ev), lse (n,h,l) fp32.
+    kv_lens: optional int64 device tensor [n] with the number of valid keys per batch entry."""
     n, h, l, e = Q.shape
     _, hkv, s, _ = K.shape
     ev = V.shape[3]
@@ -302,13 +308,17 @@ def sdpa(Q, K, V, *, bias=None, scale=None, is_causal=False, need_lse=True, out=
     code = dtype_code(Q.dtype)
     wsb = L.kuiops_sdpa_workspace_bytes(code, n, h, hkv, l, s, e, ev)
     ws = workspace("sdpa", Q.device, wsb) if wsb else None
-    _check(L.kuiops_sdpa(code, n, h, hkv, l, s, e, ev,
-                         Q.data_ptr(), Q.stride(0), Q.stride(1), Q.stride(2),
-                         K.data_ptr(), K.stride(0), K.stride(1), K.stride(2),
-                         V.data_ptr(), V.stride(0), V.stride(1), V.stride(2),
-                         _ptr(bias), float(scale), 1 if is_causal else 0,
-                         out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), _ptr(lse),
-                         _ptr(ws), ws.numel() if ws is not None else 0, _stream()), "sdpa")
+    args = (code, n, h, hkv, l, s, e, ev,
+            Q.data_ptr(), Q.stride(0), Q.stride(1), Q.stride(2),
+            K.data_ptr(), K.stride(0), K.stride(1), K.stride(2),
+            V.data_ptr(), V.stride(0), V.stride(1), V.stride(2),
+            _ptr(bias), float(scale), 1 if is_causal else 0,
+            out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), _ptr(lse))
+    tail = (_ptr(ws), ws.numel() if ws is not None else 0, _stream())
+    if kv_lens is None:
+        _check(L.kuiops_sdpa(*args, *tail), "sdpa")
+    else:
+        _check(L.kuiops_sdpa_varlen(*args, kv_lens.data_ptr(), *tail), "sdpa_varlen")
     return out, lse
 
 
@@ -475,6 +485,12 @@ def map1(op, X, c0=0.0, c1=1.0, out=None):
     _check(lib().kuiops_map(dtype_code(Xc.dtype), MAP[op], Xc.numel(), Xc.data_ptr(), out.data_ptr(),
                             float(c0), float(c1), _stream()), f"map {op}")
     return out
+
+
+def add_i64_(x, delta):
+    """In-place x += delta on an int64 device tensor."""
+    _check(lib().kuiops_add_i64(x.numel(), x.data_ptr(), int(delta), _stream()), "add_i64")
+    return x
 
 
 def map2(op, X, B, c1=1.0, out=None):

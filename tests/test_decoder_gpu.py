@@ -1,0 +1,83 @@
+"""The kuiops-only decoder against HuggingFace's Llama in PyTorch eager with the same weights
+(tiny config): logits of prefill and of a decode step within the bf16 bar, and equal greedy
+tokens where the top-2 margin is not within rounding."""
+import numpy as np
+import pytest
+import torch
+
+from _util import to_np
+from oracle import kuiops_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _hf_twin(dec):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    c = dec.cfg
+    hf = LlamaConfig(hidden_size=c.d_model, intermediate_size=c.d_ff, num_hidden_layers=c.n_layers,
+                     num_attention_heads=c.n_heads, num_key_value_heads=c.n_kv_heads, head_dim=c.head_dim,
+                     vocab_size=c.vocab, rms_norm_eps=c.eps, rope_theta=c.rope_theta, max_position_embeddings=512,
+                     tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
+    m = LlamaForCausalLM(hf).to(torch.bfloat16).cuda().eval()
+    hq, hk, hd = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim, c.head_dim
+    with torch.no_grad():
+        m.model.embed_tokens.weight.copy_(dec.embed)
+        m.lm_head.weight.copy_(dec.lm_head)
+        m.model.norm.weight.copy_(dec.norm_f)
+        for L, H in zip(dec.layers, m.model.layers):
+            H.self_attn.q_proj.weight.copy_(L["wqkv"][:hq])
+            H.self_attn.k_proj.weight.copy_(L["wqkv"][hq:hq + hk])
+            H.self_attn.v_proj.weight.copy_(L["wqkv"][hq + hk:])
+            H.self_attn.o_proj.weight.copy_(L["wo"])
+            H.mlp.gate_proj.weight.copy_(L["wgu"][:c.d_ff])
+            H.mlp.up_proj.weight.copy_(L["wgu"][c.d_ff:])
+            H.mlp.down_proj.weight.copy_(L["wd"])
+            H.input_layernorm.weight.copy_(L["n1"])
+            H.post_attention_layernorm.weight.copy_(L["n2"])
+    return m
+
+
+def test_decoder_matches_hf_llama(cuda):
+    from kuillm_b200.decoder import Decoder, DecoderConfig
+    dec = Decoder(DecoderConfig.tiny(), device="cuda", seed=0, init_std=0.05)
+    twin = _hf_twin(dec)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 1000, (3, 17), generator=g).cuda()
+    dec.alloc_cache(3, 40)
+    logits = dec.prefill(ids)
+    with torch.no_grad():
+        ref = twin(ids, use_cache=True)
+    rel = O.rel_frobenius(to_np(logits), to_np(ref.logits[:, -1]))
+    assert rel < 3e-2, rel
+    nxt = ref.logits[:, -1].argmax(-1)
+    step = dec.decode_step(nxt)
+    with torch.no_grad():
+        ref2 = twin(nxt[:, None], past_key_values=ref.past_key_values, use_cache=True)
+    rel2 = O.rel_frobenius(to_np(step), to_np(ref2.logits[:, -1]))
+    assert rel2 < 3e-2, rel2
+
+
+def test_generate_is_deterministic_and_cache_consistent(cuda):
+    from kuillm_b200.decoder import Decoder, DecoderConfig
+    dec = Decoder(DecoderConfig.tiny(), device="cuda", seed=1, init_std=0.05)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 1000, (2, 12), generator=g).cuda()
+    dec.alloc_cache(2, 32)
+    a = dec.generate(ids, 6)
+    dec.length = 0
+    b = dec.generate(ids, 6)
+    assert torch.equal(a, b)
+    dec.length = 0
+    c = dec.generate(ids, 6, use_graph=True)          # captured decode step, device-side counters
+    assert torch.equal(a, c)
+    dec.length = 0
+    assert torch.equal(a, dec.generate(ids, 6, use_graph=True))   # replaying the same graph again
+    # decoding token by token equals prefilling the longer prompt (cache append is consistent)
+    dec.length = 0
+    full = torch.cat([ids, a[:, :3]], 1)
+    l_full = dec.prefill(full)
+    dec.length = 0
+    dec.prefill(ids)
+    for t in range(3):
+        l_step = dec.decode_step(a[:, t].contiguous())
+    assert O.rel_frobenius(to_np(l_step), to_np(l_full)) < 3e-2

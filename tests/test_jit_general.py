@@ -76,7 +76,6 @@ def test_sampling_path_under_dispatch_mode(cuda, gates):
     g = torch.Generator().manual_seed(0)
     logits = (torch.randn(8, 5000, generator=g) * 3).cuda()
     stop = torch.randint(0, 5000, (64,), generator=g).cuda()
-    before = kuipy._ffi.launch_count() if hasattr(kuipy, "_ffi") else None
     from kuipy import _ffi
     n0 = _ffi.launch_count()
     with kuipy.KuiperMode():

@@ -188,9 +188,11 @@ class Decoder:
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(2):                  # warm-up on the capture stream: scratch buffers get allocated here
-                self.length = 1
-                self._pos.fill_(1)
-                self._kvlen.fill_(2)
+                # it runs at the last cache slot, which is rewritten before any real step reads it,
+                # so a cache that already holds a prompt stays intact
+                self.length = self.cap - 1
+                self._pos.fill_(self.cap - 1)
+                self._kvlen.fill_(self.cap)
                 self._graph_step()
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)

@@ -184,6 +184,36 @@ KUIOPS_API int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_
                 float* lse, const int64_t* kv_lens,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
 
+/* Attention for callers that must not allocate device memory.
+ * Has no counterpart in the reference.
+ * Some hosts of this library cannot call cudaMalloc around an attention call: a
+ * plugin loaded into another runtime that has already claimed the whole device
+ * for its own pool, or a serving loop that may not take the device-wide stall an
+ * allocation can cause.  kuiops_sdpa leaves the split-KV scratch to the caller;
+ * this variant needs none: the partial (max, sum, output) records of the split
+ * keys go to a fixed array of KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES that is part of
+ * the library image (each GPU that loads the library holds one copy until the
+ * process exits).  Inputs and outputs are still the caller's.  Arguments and
+ * results are those of kuiops_sdpa_varlen (kv_lens may be NULL).
+ *   - A problem whose scratch need (kuiops_sdpa_workspace_bytes) exceeds the
+ *     array is refused with KUIOPS_ELIMIT; nothing is launched.
+ *   - The first call on a device looks up the array's device address; make that
+ *     first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the last call's contents; the
+ *     entry point clears the ticket words it relies on, on `stream`, before the
+ *     kernel.  Two calls that overlap on the GPU (different streams) race on it:
+ *     serialise them.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called. */
+#define KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES (8u << 20)
+KUIOPS_API int kuiops_sdpa_noalloc(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
+                uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                const void* bias, float scale, int is_causal,
+                void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl,
+                float* lse, const int64_t* kv_lens, kuiops_stream_t stream);
+
 /* ======================================================================== */
 /* Streaming reductions                                                     */
 /* ======================================================================== */

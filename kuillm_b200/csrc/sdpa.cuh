@@ -29,6 +29,7 @@ struct SdpaRowsPlan {
 
 SdpaRowsPlan sdpa_rows_plan(const SdpaArgs& a);
 size_t sdpa_rows_workspace_bytes(const SdpaArgs& a);
+size_t sdpa_rows_counter_bytes(const SdpaArgs& a);   // leading ticket words of that workspace
 int sdpa_rows(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // tcgen05 flash-attention forward (bf16 / f16, head dim 128, no bias).

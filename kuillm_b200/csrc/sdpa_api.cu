@@ -1,5 +1,6 @@
 // C-ABI entry point of scaled dot-product attention: contract checks and kernel choice.
 #include "sdpa.cuh"
+#include <mutex>
 
 using namespace kuiops;
 
@@ -9,6 +10,26 @@ static int fill_args(SdpaArgs& a, int dtype, uint32_t n, uint32_t h, uint32_t h_
   if (n == 0 || h == 0 || h_kv == 0 || l == 0 || s == 0 || e == 0 || ev == 0) return KUIOPS_EINVAL;
   if (h % h_kv) return KUIOPS_EINVAL;
   a.dtype = dtype; a.n = n; a.h = h; a.h_kv = h_kv; a.l = l; a.s = s; a.e = e; a.ev = ev;
+  return KUIOPS_OK;
+}
+
+// Scratch for kuiops_sdpa_noalloc: lives in the library image, one copy per GPU that loads it.
+// In host code the name below is only a handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_sdpa_static_scratch[KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES];
+
+static int sdpa_static_scratch(void** out) {
+  static std::mutex mu;
+  static void* per_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KUIOPS_ELAUNCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sdpa_static_scratch) != cudaSuccess || !ptr) return KUIOPS_ELAUNCH;
+    per_device[dev] = ptr;
+  }
+  *out = per_device[dev];
   return KUIOPS_OK;
 }
 
@@ -53,6 +74,32 @@ int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, ui
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
   return kuiops_sdpa_varlen(dtype, n, h, h_kv, l, s, e, ev, Q, q_sn, q_sh, q_sl, K, k_sn, k_sh, k_ss, V, v_sn, v_sh, v_ss,
                             bias, scale, is_causal, out, o_sn, o_sh, o_sl, lse, nullptr, workspace, workspace_bytes, stream);
+}
+
+int kuiops_sdpa_noalloc(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
+                        const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,
+                        const void* K, int64_t k_sn, int64_t k_sh, int64_t k_ss,
+                        const void* V, int64_t v_sn, int64_t v_sh, int64_t v_ss,
+                        const void* bias, float scale, int is_causal,
+                        void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl, float* lse,
+                        const int64_t* kv_lens, kuiops_stream_t stream) {
+  SdpaArgs a = {};
+  int rc = fill_args(a, dtype, n, h, h_kv, l, s, e, ev);
+  if (rc != KUIOPS_OK) return rc;
+  const size_t need = sdpa_rows_workspace_bytes(a);
+  if (need > size_t(KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES)) return KUIOPS_ELIMIT;   // beyond the built-in scratch
+  void* scratch = nullptr;
+  rc = sdpa_static_scratch(&scratch);
+  if (rc != KUIOPS_OK) return rc;
+  if (need) {
+    // every call shares the array and it keeps the previous call's contents: the ticket words
+    // at its head have to be zero when the kernel starts
+    const size_t head = sdpa_rows_counter_bytes(a);
+    if (cudaMemsetAsync(scratch, 0, head, as_stream(stream)) != cudaSuccess) return KUIOPS_ELAUNCH;
+  }
+  return kuiops_sdpa_varlen(dtype, n, h, h_kv, l, s, e, ev, Q, q_sn, q_sh, q_sl, K, k_sn, k_sh, k_ss, V, v_sn, v_sh, v_ss,
+                            bias, scale, is_causal, out, o_sn, o_sh, o_sl, lse, kv_lens, scratch,
+                            size_t(KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

@@ -356,6 +356,11 @@ size_t sdpa_rows_workspace_bytes(const SdpaArgs& a) {
   return counters + size_t(pl.units) * pl.splits * pl.r_pad * (pl.dv * 32 + 2) * sizeof(float);
 }
 
+size_t sdpa_rows_counter_bytes(const SdpaArgs& a) {
+  SdpaRowsPlan pl = sdpa_rows_plan(a);
+  return pl.splits == 1 ? 0 : ((size_t(pl.units) * 4 + 255) & ~size_t(255));
+}
+
 int sdpa_rows(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (a.ev > 256 || a.e > 1024) return KUIOPS_EUNSUPPORTED;
   SdpaRowsPlan pl = sdpa_rows_plan(a);

@@ -19,6 +19,7 @@ LIB_PATH = Path(os.environ.get("KUIOPS_LIB", _PKG / "lib" / "libkuiops.so"))
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ELAUNCH, EDRIVER, ELIMIT = 0, -1, -2, -3, -4, -5, -6
 F32, BF16, F16 = 0, 1, 2
 GEMM_COUNTER_BYTES = 16384
+SDPA_NOALLOC_SCRATCH_BYTES = 8 << 20
 REDUCE_WORKSPACE_BYTES = 16384
 REDUCE_ALL, REDUCE_ANY, REDUCE_MAX = 0, 1, 2
 MAP = dict(silu=0, neg=1, rsqrt=2, cos=3, sin=4, pow=5, square=6, add=7, mul=8, sub=9, div=10,
@@ -63,6 +64,9 @@ SIGNATURES = {
                            [c_void_p, c_i64, c_i64, c_i64] * 3 +
                            [c_void_p, c_float, c_int, c_void_p, c_i64, c_i64, c_i64, c_void_p, c_void_p,
                             c_void_p, c_size_t, c_void_p]),
+    "kuiops_sdpa_noalloc": (c_int, [c_int] + [c_u32] * 7 +
+                            [c_void_p, c_i64, c_i64, c_i64] * 3 +
+                            [c_void_p, c_float, c_int, c_void_p, c_i64, c_i64, c_i64, c_void_p, c_void_p, c_void_p]),
     "kuiops_add_i64": (c_int, [c_u64, c_void_p, c_i64, c_void_p]),
     "kuiops_topk_f32": (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "kuiops_gather": (c_int, [c_u32, c_u32, c_u32, _P64, _P64, c_void_p, c_void_p, c_void_p, c_u64,

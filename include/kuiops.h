@@ -81,13 +81,15 @@ KUIOPS_API uint64_t    kuiops_launch_count(void);
  * rows (the fused bias of addmm).  Inputs are `dtype`; C is `out_dtype`
  * (same as dtype, or KUIOPS_F32).  Accumulation is always fp32.
  * bf16/f16 operands whose pointers are 16-byte aligned and whose leading
- * dimensions are multiples of 8 run on the tcgen05 tensor-core kernels; M <= 64
- * uses the weight-streaming split-K kernel with its in-kernel reduction.
- * Everything else (fp32, odd strides) runs on the SIMT kernel.
- * `workspace` must hold kuiops_gemm_workspace_bytes(...) bytes, and its first
- * KUIOPS_GEMM_COUNTER_BYTES bytes must be zero the first time it is used; the
- * kernels leave them zero.  Replaces the launchers at wrapper_mm.cu.j2:15-19,
- * wrapper_addmm.cu.j2:18-24 and wrapper_bmm.cu.j2:16-20. */
+ * dimensions are multiples of 8 run on the tcgen05 tensor-core kernels; M <= 128
+ * uses the weight-streaming placement, which splits K over the CTAs of a
+ * thread-block cluster and reduces the partials in shared memory (in-kernel,
+ * deterministic).  Everything else (fp32, odd strides) runs on the SIMT kernel.
+ * `workspace` is reserved: the current kernels keep their partials on chip and
+ * ignore it (NULL is accepted); kuiops_gemm_workspace_bytes reports the size a
+ * caller should provide to stay compatible with kernels that may use it.
+ * Replaces the launchers at wrapper_mm.cu.j2:15-19, wrapper_addmm.cu.j2:18-24
+ * and wrapper_bmm.cu.j2:16-20. */
 #define KUIOPS_GEMM_COUNTER_BYTES 16384
 KUIOPS_API size_t kuiops_gemm_workspace_bytes(int dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
 KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,

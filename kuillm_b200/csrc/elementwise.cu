@@ -151,25 +151,29 @@ where_kernel(uint64_t len, const uint8_t* __restrict__ cnd, const P* A, const P*
 // --------------------------------------------------------------------------------------
 // RMSNorm with optional residual add: the dispatcher sees this as
 // to(f32) -> pow 2 -> mean -> add eps -> rsqrt -> mul -> to(bf16) -> mul weight, seven HBM
-// round trips; fused it is one read and one write per row.  One warp per row of up to 8192
-// elements held in registers between the statistics and the scaling pass.
+// round trips; fused it is one read and one write per row.  One to eight warps share a row of up
+// to 1024 vectors, held in registers between the statistics and the scaling pass.
 // --------------------------------------------------------------------------------------
-template <typename T, int VECS>
+template <typename T, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residual, const T* __restrict__ w,
                float eps, T* __restrict__ y, T* residual_out) {
-  constexpr int VN = Vec16<T>::N;
-  const int lane = threadIdx.x & 31;
-  const uint64_t warps_total = uint64_t(gridDim.x) * (blockDim.x >> 5);
+  // WPR warps share a row (1, 2, 4 or 8), each thread keeps at most 4 vectors of it in registers
+  constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row_in_block = warp / WPR, wsub = warp % WPR;
   const uint32_t nvec = n / VN;
-  for (uint64_t row = uint64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m; row += warps_total) {
+  for (uint64_t base = uint64_t(blockIdx.x) * RPB; base < m; base += uint64_t(gridDim.x) * RPB) {
+    const uint64_t row = base + row_in_block;
+    const bool valid = row < m;
     const T* xr = x + row * n;
     Vec16<T> c[VECS];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VECS; ++i) {
-      uint32_t v = lane + i * 32;
-      if (v < nvec) {
+      const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+      if (valid && v < nvec) {
         c[i] = ld16(xr + size_t(v) * VN);
         if (residual) {
           Vec16<T> r = ld16(residual + row * n + size_t(v) * VN);
@@ -183,11 +187,19 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
       }
     }
     ss = warp_sum(ss);
+    if (WPR > 1) {
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < WPR; ++k) ss += red[row_in_block * WPR + k];
+      __syncthreads();
+    }
     const float r = rsqrtf(ss / float(n) + eps);
 #pragma unroll
     for (int i = 0; i < VECS; ++i) {
-      uint32_t v = lane + i * 32;
-      if (v < nvec) {
+      const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+      if (valid && v < nvec) {
         Vec16<T> wv = ld16(w + size_t(v) * VN), o;
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
@@ -388,12 +400,13 @@ static int rmsnorm_launch(uint64_t m, uint32_t n, const void* x, const void* res
   if (n % VN || !aligned16(x) || !aligned16(w) || !aligned16(y) || (res && (!aligned16(res) || !aligned16(res_out))))
     return KUIOPS_EUNSUPPORTED;
   const uint32_t nvec = n / VN;
-  unsigned grid = stream_grid(m, 8, 8);
   auto X = static_cast<const T*>(x); auto R = static_cast<const T*>(res); auto W = static_cast<const T*>(w);
   auto Y = static_cast<T*>(y); auto RO = static_cast<T*>(res_out);
-  if (nvec <= 32 * 4) rmsnorm_kernel<T, 4><<<grid, 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else if (nvec <= 32 * 16) rmsnorm_kernel<T, 16><<<grid, 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else if (nvec <= 32 * 32) rmsnorm_kernel<T, 32><<<grid, 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
+  // warps per row so that a thread holds at most 4 vectors
+  if (nvec <= 128) rmsnorm_kernel<T, 1><<<stream_grid(m, 8, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
+  else if (nvec <= 256) rmsnorm_kernel<T, 2><<<stream_grid(m, 4, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
+  else if (nvec <= 512) rmsnorm_kernel<T, 4><<<stream_grid(m, 2, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
+  else if (nvec <= 1024) rmsnorm_kernel<T, 8><<<stream_grid(m, 1, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
   else return KUIOPS_EUNSUPPORTED;
   return check_launch();
 }

@@ -6,9 +6,10 @@
 //     with two accumulator stages so the epilogue of a tile overlaps the MMAs of the next.
 //   * swapped (M <= 128, decode shapes): P = B columns (n, the weight rows that have to be
 //     streamed from HBM), Q = A rows (m, padded to 16..128).  K is split over several CTAs per
-//     tile so that every SM streams weights; the fp32 partials meet in the workspace and the
-//     CTA that draws the last ticket of a tile reduces them in split order and runs the
-//     epilogue (in-kernel reduction, deterministic).
+//     tile (one thread-block cluster per tile) so that every SM streams weights; the fp32
+//     partials stay in shared memory and are summed in slice order through distributed shared
+//     memory, each CTA finishing a share of the tile's columns (in-kernel reduction,
+//     deterministic, no global scratch).
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocator + UMMA issuer (one
 // lane), warps 2..5 = epilogue (TMEM -> registers -> alpha/beta/bias -> global).
 // Operands arrive through 3-D tensor maps (inner, rows, batch) with 128-byte swizzle; edges in
@@ -16,9 +17,11 @@
 // rule.  Replaces Klas.GEMM.TensorCore2D (wmma fragments, kuiops/mm/Kuiops.Mm.Inst.fst.j2:9-11).
 #include "gemm.cuh"
 #include "tc_ptx.cuh"
+#include <cooperative_groups.h>
 #include <mutex>
 #include <type_traits>
 
+namespace cg = cooperative_groups;
 namespace kuiops {
 
 constexpr int TBM = 128;   // TMEM lanes = rows of the P operand per tile
@@ -33,7 +36,7 @@ struct TcParams {
   float alpha, beta;
   const void* Cin; int64_t ldcin, stride_cin;
   void* C; int64_t ldc, stride_c;
-  float* partials; int* counters; unsigned int* err;
+  unsigned int* err;
 };
 
 __device__ unsigned int g_tc_error = 0;
@@ -87,7 +90,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -185,11 +187,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     // ------------------------------ epilogue ----------------------------------------------
     const uint32_t quarter = warp & 3;                    // TMEM lanes this warp may touch
     const uint32_t lane_in_tile = quarter * 32 + lane;
-    const uint32_t epi_tid = threadIdx.x - 64;
+    // facts that allow 16-byte stores of 8 consecutive outputs of a row (normal placement only)
+    const bool c_vec = !p.swapped && !p.out_f32 && (p.ldc % 8 == 0) && (p.stride_c % 8 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+    const bool cin_vec = !p.Cin || (((reinterpret_cast<uintptr_t>(p.Cin) & 15u) == 0) && (p.ldcin % 8 == 0) &&
+                                    (p.stride_cin % 8 == 0));
     uint32_t acc_it = 0;
     bool ok = true;
     for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++acc_it) {
-      const uint32_t split = u % p.splits, tile = u / p.splits;
+      const uint32_t tile = u / p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
       const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
       const uint32_t as = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1;
@@ -205,19 +211,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         for (uint32_t c = 0; c < ncols; c += 16) {
           tc::tmem_ld16(taddr + c, v);
           tc::tmem_ld_wait();
-          bool vec_done = false;
-          if (!p.swapped && !p.out_f32 && !p.Cin && row < p.M && col0 + c + 16 <= p.N &&
-              (p.ldc % 8 == 0) && (p.stride_c % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0)) {
-            // 16 consecutive outputs of one row: two 16-byte stores
+          if (c_vec && cin_vec && row < p.M && col0 + c + 16 <= p.N) {
+            // 16 consecutive outputs of one row: two 16-byte stores, addend fetched the same way
+            float add[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) add[j] = 0.f;
+            if (p.Cin) {
+              const TIN* src = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin + size_t(row) * p.ldcin + col0 + c;
+              const Vec16<TIN> a0 = ld16(src), a1 = ld16(src + 8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { add[j] = p.beta * ElemTraits<TIN>::to_f(a0.v[j]); add[8 + j] = p.beta * ElemTraits<TIN>::to_f(a1.v[j]); }
+            }
             TIN* dst = static_cast<TIN*>(p.C) + size_t(b) * p.stride_c + size_t(row) * p.ldc + col0 + c;
             Vec16<TIN> o0, o1;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { o0.v[j] = ElemTraits<TIN>::from_f(p.alpha * v[j]); o1.v[j] = ElemTraits<TIN>::from_f(p.alpha * v[8 + j]); }
+            for (int j = 0; j < 8; ++j) {
+              o0.v[j] = ElemTraits<TIN>::from_f(fmaf(p.alpha, v[j], add[j]));
+              o1.v[j] = ElemTraits<TIN>::from_f(fmaf(p.alpha, v[8 + j], add[8 + j]));
+            }
             st16(dst, o0);
             st16(dst + 8, o1);
-            vec_done = true;
-          }
-          if (!vec_done) {
+          } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j]);
           }
@@ -226,38 +240,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&acc_empty[as]);
       } else {
-        // split-K: park the fp32 partial, then the last split to arrive reduces the tile
-        float* part = p.partials + (size_t(tile) * p.splits + split) * (size_t(BN) * TBM);
+        // split-K (one unit per CTA): park the fp32 partial in this CTA's shared memory, column-major.
+        // The pipeline buffers are free: every MMA that read them has completed.
+        float* red = reinterpret_cast<float*>(smem);
         for (uint32_t c = 0; c < ncols; c += 16) {
           tc::tmem_ld16(taddr + c, v);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) __stcg(&part[size_t(c + j) * TBM + lane_in_tile], v[j]);
+          for (int j = 0; j < 16; ++j) red[(c + j) * TBM + lane_in_tile] = v[j];
         }
         tc::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&acc_empty[as]);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (epi_tid == 0) {
-          const int old = atomicAdd(&p.counters[tile], 1);
-          *last_flag = (old == int(p.splits) - 1) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-          const float* base = p.partials + size_t(tile) * p.splits * (size_t(BN) * TBM);
-          for (uint32_t c = 0; c < ncols; ++c) {
-            float sum = 0.f;
-            for (uint32_t s2 = 0; s2 < p.splits; ++s2)
-              sum += __ldcg(&base[size_t(s2) * (size_t(BN) * TBM) + size_t(c) * TBM + lane_in_tile]);
-            store_elem<TIN>(p, b, row, col0 + c, sum);
-          }
-          if (epi_tid == 0) p.counters[tile] = 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
+  }
+  // ------------------------------ split-K reduction across the cluster ---------------------
+  // The CTAs of a cluster hold the K-slices of one output tile.  After a cluster barrier each CTA
+  // sums a share of the tile's columns over all slices, reading its peers' partials through
+  // distributed shared memory in slice order (deterministic), and runs the epilogue on them.
+  if (p.splits > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    // the producer and issuer lanes ran their loops alone: bring every warp back together first,
+    // the cluster barrier instructions are warp-collective
+    __syncwarp();
+    cluster.sync();
+    if (warp >= 2 && blockIdx.x < units) {
+      const uint32_t quarter = warp & 3, lane_in_tile = quarter * 32 + lane;
+      const uint32_t tile = blockIdx.x / p.splits, rank = blockIdx.x % p.splits;
+      const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
+      const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+      const uint32_t row = tp * TBM + lane_in_tile, col0 = tq * BN;
+      const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
+      float* red = reinterpret_cast<float*>(smem);
+      const float* peer[8];
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) peer[s2] = cluster.map_shared_rank(red, s2 < int(p.splits) ? s2 : 0);
+      for (uint32_t c = rank; c < ncols; c += p.splits) {
+        float part[8];
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) part[s2] = s2 < int(p.splits) ? peer[s2][c * TBM + lane_in_tile] : 0.f;
+        float sum = part[0];
+#pragma unroll
+        for (int s2 = 1; s2 < 8; ++s2) sum += part[s2];
+        store_elem<TIN>(p, b, row, col0 + c, sum);
+      }
+    }
+    __syncwarp();
+    cluster.sync();          // nobody's shared memory goes away while a peer may still read it
   }
   // ------------------------------ teardown ------------------------------------------------
   tc::tc_fence_before();
@@ -337,30 +365,36 @@ static TcPlan make_plan(const GemmArgs& a) {
   }
   const uint64_t tiles = uint64_t(pl.tilesP) * pl.tilesQ * a.batch;
   pl.splits = 1;
-  if (pl.swapped && tiles < 2 * uint64_t(kNumSMs) && tiles <= KUIOPS_GEMM_COUNTER_BYTES / 4) {
-    uint32_t want = uint32_t((2 * uint64_t(kNumSMs) + tiles - 1) / tiles);
-    uint32_t cap = pl.kblocks / 8;                 // keep at least 8 k-blocks (512 of K) per split
-    if (cap < 1) cap = 1;
-    pl.splits = want < cap ? want : cap;
-    if (pl.splits > 32) pl.splits = 32;
+  if (pl.swapped) {
+    // Too few output tiles to occupy the machine: split K over the CTAs of a cluster (at most 8, the
+    // portable cluster size).  Aim at as many CTAs as can be resident at once.
+    const uint32_t smem_cta = 4u * (TBM * TBK * 2 + uint32_t(pl.bn) * TBK * 2) + 2048;
+    uint32_t per_sm = (227u * 1024u) / smem_cta;
+    if (per_sm > 3) per_sm = 3;
+    if (per_sm < 1) per_sm = 1;
+    const uint64_t resident = uint64_t(kNumSMs) * per_sm;
+    if (tiles < resident) {
+      uint32_t want = uint32_t(resident / tiles);
+      uint32_t cap = pl.kblocks / 4;               // keep at least 4 k-blocks (256 of K) per slice
+      if (cap < 1) cap = 1;
+      pl.splits = want < cap ? want : cap;
+      if (pl.splits > 8) pl.splits = 8;
+      if (pl.splits < 1) pl.splits = 1;
+    }
   }
   pl.kb_per_split = (pl.kblocks + pl.splits - 1) / pl.splits;
-  pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;   // no empty split
+  pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;   // no empty slice
   return pl;
 }
 
-size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K) {
-  GemmArgs a = {};
-  a.batch = batch ? batch : 1; a.M = M; a.N = N; a.K = K;
-  TcPlan pl = make_plan(a);
-  size_t bytes = KUIOPS_GEMM_COUNTER_BYTES;
-  if (pl.splits > 1)
-    bytes += size_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits * size_t(pl.bn) * TBM * sizeof(float);
-  return bytes;
-}
+// The split-K partials live in shared memory, so the GEMM kernels need no global scratch; the
+// query is kept for callers written against the workspace contract.
+size_t gemm_tc_workspace_bytes(uint32_t, uint32_t, uint32_t, uint32_t) { return KUIOPS_GEMM_COUNTER_BYTES; }
 
 template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, unsigned grid, cudaStream_t st) {
+  static_assert(size_t(BN) * TBM * sizeof(float) <= size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2),
+                "the split-K partial is parked in the pipeline buffers");
   constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256;
   auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
   // the opt-in for large dynamic shared memory is per device: do it once per (kernel, device)
@@ -373,16 +407,25 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
       return KUIOPS_ELAUNCH;
     configured.fetch_or(bit, std::memory_order_release);
   }
-  kern<<<grid, kTcThreads, smem, st>>>(mp, mq, p);
-  return check_launch();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mp, mq, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
 }
 
 template <typename TIN>
 static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   const TcPlan pl = make_plan(a);
-  if (pl.splits > 1) {
-    if (!workspace || workspace_bytes < gemm_tc_workspace_bytes(a.batch, a.M, a.N, a.K)) return KUIOPS_EWORKSPACE;
-  }
+  (void)workspace; (void)workspace_bytes;
   // Tensor maps.  "Rows" of an operand are the index that is NOT K.
   // A is always K-major: dims (K, M, batch).  B is K-major when trans_b (stored [N, K]) and
   // MN-major otherwise (stored [K, N]: dims (N, K, batch)).
@@ -415,8 +458,6 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.alpha = a.alpha; p.beta = a.beta;
   p.Cin = a.Cin; p.ldcin = a.ldcin; p.stride_cin = a.stride_cin;
   p.C = a.C; p.ldc = a.ldc; p.stride_c = a.stride_c;
-  p.counters = static_cast<int*>(workspace);
-  p.partials = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + KUIOPS_GEMM_COUNTER_BYTES) : nullptr;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
   const uint64_t units = uint64_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits;

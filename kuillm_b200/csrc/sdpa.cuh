@@ -36,4 +36,10 @@ int sdpa_rows(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaSt
 bool sdpa_flash_eligible(const SdpaArgs& a);
 int sdpa_flash(const SdpaArgs& a, cudaStream_t st);
 
+// tcgen05 split-KV decode attention (bf16 / f16, head dim 128, G * l <= 128 query rows per KV head).
+bool sdpa_decode_tc_eligible(const SdpaArgs& a);
+size_t sdpa_decode_tc_workspace_bytes(const SdpaArgs& a);
+size_t sdpa_decode_tc_counter_bytes(const SdpaArgs& a);
+int sdpa_decode_tc(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+
 }  // namespace kuiops

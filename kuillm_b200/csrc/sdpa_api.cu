@@ -39,7 +39,13 @@ size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h
                                    uint32_t e, uint32_t ev) {
   SdpaArgs a = {};
   if (fill_args(a, dtype, n, h, h_kv, l, s, e, ev) != KUIOPS_OK) return 0;
-  return sdpa_rows_workspace_bytes(a);
+  // which kernel runs also depends on pointer alignment, unknown here: cover both
+  size_t need = sdpa_rows_workspace_bytes(a);
+  if (dtype != KUIOPS_F32 && e == 128 && ev == 128 && uint64_t(h / h_kv) * l <= 128 && l <= 16) {
+    const size_t t = sdpa_decode_tc_workspace_bytes(a);
+    if (t > need) need = t;
+  }
+  return need;
 }
 
 int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
@@ -62,6 +68,7 @@ int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_
   a.out = out; a.o_sn = o_sn; a.o_sh = o_sh; a.o_sl = o_sl; a.lse = lse; a.kv_lens = kv_lens;
   cudaStream_t st = as_stream(stream);
   if (sdpa_flash_eligible(a)) return sdpa_flash(a, st);
+  if (sdpa_decode_tc_eligible(a)) return sdpa_decode_tc(a, workspace, workspace_bytes, st);
   return sdpa_rows(a, workspace, workspace_bytes, st);
 }
 
@@ -86,7 +93,7 @@ int kuiops_sdpa_noalloc(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32
   SdpaArgs a = {};
   int rc = fill_args(a, dtype, n, h, h_kv, l, s, e, ev);
   if (rc != KUIOPS_OK) return rc;
-  const size_t need = sdpa_rows_workspace_bytes(a);
+  const size_t need = kuiops_sdpa_workspace_bytes(dtype, n, h, h_kv, l, s, e, ev);
   if (need > size_t(KUIOPS_SDPA_NOALLOC_SCRATCH_BYTES)) return KUIOPS_ELIMIT;   // beyond the built-in scratch
   void* scratch = nullptr;
   rc = sdpa_static_scratch(&scratch);
@@ -94,7 +101,8 @@ int kuiops_sdpa_noalloc(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32
   if (need) {
     // every call shares the array and it keeps the previous call's contents: the ticket words
     // at its head have to be zero when the kernel starts
-    const size_t head = sdpa_rows_counter_bytes(a);
+    size_t head = sdpa_rows_counter_bytes(a);
+    if (sdpa_decode_tc_counter_bytes(a) > head) head = sdpa_decode_tc_counter_bytes(a);
     if (cudaMemsetAsync(scratch, 0, head, as_stream(stream)) != cudaSuccess) return KUIOPS_ELAUNCH;
   }
   return kuiops_sdpa_varlen(dtype, n, h, h_kv, l, s, e, ev, Q, q_sn, q_sh, q_sl, K, k_sn, k_sh, k_ss, V, v_sn, v_sh, v_ss,

@@ -1,0 +1,461 @@
+// Split-KV attention on tcgen05 for decode: a few query tokens per sequence against a long KV
+// cache (bf16 / f16, head dim 128, grouped-query heads, optional device-side key counts).
+//
+// HBM bound: every K/V byte is read once per GQA group.  A CTA owns one (batch, KV head) and one
+// slice of the keys.  The query rows of the whole group - G heads x l positions, at most 128 -
+// are loaded as ONE TMA box into the first rows of a 128-row UMMA tile, so the G heads share
+// each K/V tile; the remaining rows of the tile are zero and ignored.  The pipeline is the one
+// of the prefill kernel (TMA ring of 64-key tiles -> S = Q K^T in TMEM -> online softmax in
+// registers -> P to shared memory -> O += P V in TMEM).  With more than one slice per (batch, KV
+// head) each CTA parks its (max, sum, unnormalised O) record in the workspace and the CTA that
+// draws the last ticket of the unit merges the records in slice order and writes the output.
+// Replaces the lane-per-key SIMT kernel for these shapes; the reference has no counterpart
+// (its only attention kernel is the naive biased one, kuiops/sdpa/Kuiops.Sdpa.fst.1).
+#include "sdpa.cuh"
+#include "tc_ptx.cuh"
+#include <type_traits>
+
+namespace kuiops {
+
+constexpr int DBM = 128;      // UMMA tile rows (TMEM lanes); only the first G*l carry queries
+constexpr int DBN = 64;       // keys per tile
+constexpr int DD = 128;       // head dim
+constexpr int kDecThreads = 192;
+constexpr uint32_t D_Q_BYTES = DBM * DD * 2;
+constexpr uint32_t D_K_BYTES = DBN * DD * 2;
+constexpr uint32_t D_V_BYTES = DBN * DD * 2;
+constexpr uint32_t D_P_BYTES = DBM * DBN * 2;
+constexpr uint32_t D_SMEM = D_Q_BYTES + 2 * (D_K_BYTES + D_V_BYTES) + D_P_BYTES;   // 112 KB: two CTAs per SM
+constexpr uint32_t D_TMEM_COLS = 256;
+constexpr float kDecRescale = 8.0f;
+constexpr int D_REC = DD + 4;  // floats per parked row: 128 accumulators, max, sum, 2 pad (keeps rows 16-byte aligned)
+
+struct DecParams {
+  uint32_t n, h, h_kv, l, s, G, rows, splits;
+  float scale_log2;
+  int is_causal;
+  const int64_t* kv_lens;
+  void* out; int64_t o_sn, o_sh, o_sl;
+  float* lse;
+  float* partials; int* counters;
+  unsigned int* err;
+};
+
+__device__ __forceinline__ uint64_t dec_global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool dec_wait(uint64_t* bar, uint32_t parity) {
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = dec_global_ns();
+  while (!tc::mbar_try_wait(bar, parity)) {
+    if (dec_global_ns() - t0 > 2000000000ull) return false;
+  }
+  return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads, 2)
+sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const DecParams p) {
+  // The 128-byte swizzle atoms need a 1024-byte aligned base.  The dynamic shared window of a
+  // kernel without static shared memory starts on such a boundary; there is no room for padding
+  // (two CTAs must fit one SM), so a misaligned base is reported instead of worked around.
+  extern __shared__ __align__(1024) unsigned char smem[];
+  if ((tc::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.err, 10u);
+    return;
+  }
+  unsigned char* q_s = smem;
+  unsigned char* kv_s = q_s + D_Q_BYTES;                       // slot i: K at kv_s + i*32K, V right after K
+  unsigned char* p_s = kv_s + 2 * (D_K_BYTES + D_V_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + D_P_BYTES);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* v_full = bars + 3;      // 2
+  uint64_t* kv_empty = bars + 5;    // 2
+  uint64_t* s_full = bars + 7;      // 1
+  uint64_t* p_ready = bars + 8;     // 1
+  uint64_t* o_done = bars + 9;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // unit = (batch, KV head); blockIdx.x = unit * splits + split
+  const uint32_t split = blockIdx.x % p.splits;
+  const uint32_t unit = blockIdx.x / p.splits;
+  const uint32_t kvh = unit % p.h_kv;
+  const uint32_t b = unit / p.h_kv;
+  // keys of this batch entry, optionally counted on the device
+  uint32_t S = p.s;
+  if (p.kv_lens) {
+    const long long kl = p.kv_lens[b];
+    S = kl < 0 ? 0u : (kl < (long long)p.s ? uint32_t(kl) : p.s);
+  }
+  // this CTA's slice of the keys, in whole tiles
+  const uint32_t tiles_total = (S + DBN - 1) / DBN;
+  const uint32_t tiles_per = (tiles_total + p.splits - 1) / p.splits;
+  const uint32_t s_lo = min(split * tiles_per * DBN, S);
+  const uint32_t s_hi = min(s_lo + tiles_per * DBN, S);
+  const uint32_t n_tiles = (s_hi - s_lo + DBN - 1) / DBN;
+
+  // rows of the tile that carry no query must not feed NaN bit patterns into the MMA
+  for (uint32_t i = threadIdx.x; i < D_Q_BYTES / 16; i += blockDim.x) reinterpret_cast<int4*>(q_s)[i] = make_int4(0, 0, 0, 0);
+  tc::fence_proxy_async();
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
+    tc::mbar_init(s_full, 1);
+    tc::mbar_init(p_ready, 4);
+    tc::mbar_init(o_done, 1);
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmQ); tc::prefetch_tmap(&tmK); tc::prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, D_TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (lane == 0) {
+      tc::mbar_expect_tx(q_full, 2u * p.rows * 128u);
+      tc::tma_load_4d(q_s, &tmQ, q_full, 0, 0, int(kvh * p.G), int(b));
+      tc::tma_load_4d(q_s + DBM * 128, &tmQ, q_full, 64, 0, int(kvh * p.G), int(b));
+      for (uint32_t j = 0; j < n_tiles; ++j) {
+        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        if (!dec_wait(&kv_empty[slot], ph ^ 1)) { atomicExch(p.err, 11u); break; }
+        unsigned char* ks = kv_s + slot * (D_K_BYTES + D_V_BYTES);
+        unsigned char* vs = ks + D_K_BYTES;
+        const int key0 = int(s_lo + j * DBN);
+        tc::mbar_expect_tx(&k_full[slot], D_K_BYTES);
+        tc::tma_load_4d(ks, &tmK, &k_full[slot], 0, key0, int(kvh), int(b));
+        tc::tma_load_4d(ks + DBN * 128, &tmK, &k_full[slot], 64, key0, int(kvh), int(b));
+        tc::mbar_expect_tx(&v_full[slot], D_V_BYTES);
+        tc::tma_load_4d(vs, &tmV, &v_full[slot], 0, key0, int(kvh), int(b));
+        tc::tma_load_4d(vs + DBN * 128, &tmV, &v_full[slot], 64, key0, int(kvh), int(b));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ UMMA issuer -------------------------------------------
+    if (lane == 0) {
+      constexpr int is_bf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_qk = tc::make_idesc(is_bf16, 0, 0, DBM, DBN);
+      constexpr uint32_t idesc_pv = tc::make_idesc(is_bf16, 0, 1, DBM, DD);
+      bool ok = dec_wait(q_full, 0);
+      if (!ok) atomicExch(p.err, 12u);
+      const uint32_t qa = tc::smem_u32(q_s), pa = tc::smem_u32(p_s);
+      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        const uint32_t ka = tc::smem_u32(kv_s + slot * (D_K_BYTES + D_V_BYTES));
+        const uint32_t va = ka + D_K_BYTES;
+        if (!dec_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); ok = false; break; }
+        tc::tc_fence_after();
+        // S = Q K^T over the 128 head-dim elements: two 64-wide halves x four 16-wide steps
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = tc::make_smem_desc(qa + hh * (DBM * 128) + kk * 32, 16, 1024);
+            const uint64_t db = tc::make_smem_desc(ka + hh * (DBN * 128) + kk * 32, 16, 1024);
+            tc::umma_f16(tmem_S, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
+          }
+        tc::umma_commit(s_full);
+        if (!dec_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
+        if (!dec_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
+        tc::tc_fence_after();
+        // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, 1024);
+          const uint64_t db = tc::make_smem_desc(va + kk * 2048, DBN * 128, 1024);
+          tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc::umma_commit(&kv_empty[slot]);
+        tc::umma_commit(o_done);
+      }
+    }
+  } else {
+    // ------------------------------ softmax + epilogue ------------------------------------
+    const uint32_t quarter = warp & 3;
+    const uint32_t r = quarter * 32 + lane;               // row of the tile: (head in group, position)
+    const uint32_t g = r / p.l, li = r % p.l;
+    const bool row_valid = r < p.rows;
+    const bool warp_active = quarter * 32 < p.rows;       // warps without a query row only keep the barriers in step
+    const uint32_t head = kvh * p.G + g;
+    const uint32_t lane_addr = (quarter * 32) << 16;
+    const uint32_t epi_tid = threadIdx.x - 64;
+    // last key this row may see (inclusive, bottom-right aligned causal mask), capped to this slice
+    int64_t row_lim = p.is_causal ? int64_t(li) + int64_t(S) - int64_t(p.l) : int64_t(S) - 1;
+    if (row_lim > int64_t(s_hi) - 1) row_lim = int64_t(s_hi) - 1;
+    if (!row_valid) row_lim = -1;
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+      if (!dec_wait(s_full, j & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      tc::tc_fence_after();
+      float sv[DBN];
+      float corr = 1.f;
+      if (warp_active) {
+        tc::tmem_ld32(tmem_S + lane_addr, sv);
+        tc::tmem_ld32(tmem_S + lane_addr + 32, sv + 32);
+        tc::tmem_ld_wait();
+        const int64_t key0 = int64_t(s_lo) + int64_t(j) * DBN;
+        const bool edge = key0 + DBN - 1 > row_lim;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < DBN; ++c) {
+          float v = sv[c] * p.scale_log2;
+          if (edge && key0 + c > row_lim) v = -INFINITY;
+          sv[c] = v;
+          mx = fmaxf(mx, v);
+        }
+        if (mx > m_used + kDecRescale || m_used == -INFINITY) {
+          const float m_new = fmaxf(mx, m_used);
+          corr = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+          m_used = m_new;
+        }
+        const float mm = (m_used == -INFINITY) ? 0.f : m_used;
+        float rs = 0.f;
+#pragma unroll
+        for (int c = 0; c < DBN; ++c) { sv[c] = exp2f(sv[c] - mm); rs += sv[c]; }
+        l_run = l_run * corr + rs;
+      }
+      if (j > 0) {
+        if (!dec_wait(o_done, (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+        tc::tc_fence_after();
+        if (warp_active && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+          for (int c0 = 0; c0 < DD; c0 += 32) {
+            float ov[32];
+            tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
+            tc::tmem_ld_wait();
+            uint32_t ou[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ou[c] = __float_as_uint(ov[c] * corr);
+            tc::tmem_st32(tmem_O + lane_addr + c0, ou);
+          }
+          tc::tmem_st_wait();
+        }
+      }
+      if (warp_active) {
+        unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < DBN / 8; ++c) {
+          Vec16<T> pk;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pk.v[e] = ElemTraits<T>::from_f(row_valid ? sv[c * 8 + e] : 0.f);
+          *reinterpret_cast<Vec16<T>*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+        }
+      } else if (j == 0) {
+        // rows that never carry a query: one zero fill keeps the P operand free of stale bit patterns
+        unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < DBN / 8; ++c) *reinterpret_cast<int4*>(prow + (c << 4)) = make_int4(0, 0, 0, 0);
+      }
+      tc::fence_proxy_async();
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(p_ready);
+    }
+    if (ok && n_tiles > 0) {
+      if (!dec_wait(o_done, (n_tiles - 1) & 1)) { atomicExch(p.err, 18u); ok = false; }
+    }
+    tc::tc_fence_after();
+    if (p.splits == 1) {
+      if (ok && warp_active) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        T* orow = static_cast<T*>(p.out) + size_t(b) * p.o_sn + size_t(head) * p.o_sh + size_t(li) * p.o_sl;
+#pragma unroll
+        for (int c0 = 0; c0 < DD; c0 += 32) {
+          float ov[32];
+          if (n_tiles > 0) {
+            tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
+            tc::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ov[c] = 0.f;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              Vec16<T> o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o.v[e] = ElemTraits<T>::from_f(ov[c + e] * inv);
+              st16(orow + c0 + c, o);
+            }
+          }
+        }
+        if (p.lse && row_valid)
+          p.lse[(size_t(b) * p.h + head) * p.l + li] = l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+    } else {
+      // park this slice's record, then the last slice of the unit to arrive merges them all
+      float* rec = p.partials + ((size_t(unit) * p.splits + split) * p.rows + r) * D_REC;
+      if (warp_active) {
+#pragma unroll
+        for (int c0 = 0; c0 < DD; c0 += 32) {
+          float ov[32];
+          if (ok && n_tiles > 0) {
+            tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
+            tc::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ov[c] = 0.f;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) __stcg(reinterpret_cast<float4*>(rec + c0 + c), make_float4(ov[c], ov[c + 1], ov[c + 2], ov[c + 3]));
+          }
+        }
+        if (row_valid) { __stcg(rec + DD, m_used); __stcg(rec + DD + 1, l_run); }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (epi_tid == 0) {
+        const int old = atomicAdd(&p.counters[unit], 1);
+        *last_flag = (old == int(p.splits) - 1) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        // thread d merges column d of every row: coalesced over the 128 threads
+        const uint32_t d = epi_tid;
+        const float* base = p.partials + size_t(unit) * p.splits * p.rows * D_REC;
+        for (uint32_t rr = 0; rr < p.rows; ++rr) {
+          float mm = -INFINITY;
+          for (uint32_t s2 = 0; s2 < p.splits; ++s2) mm = fmaxf(mm, __ldcg(base + (size_t(s2) * p.rows + rr) * D_REC + DD));
+          float acc = 0.f, den = 0.f;
+          for (uint32_t s2 = 0; s2 < p.splits; ++s2) {
+            const float* rc = base + (size_t(s2) * p.rows + rr) * D_REC;
+            const float mw = __ldcg(rc + DD);
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+            acc += f * __ldcg(rc + d);
+            den += f * __ldcg(rc + DD + 1);
+          }
+          const uint32_t hh = kvh * p.G + rr / p.l, ll = rr % p.l;
+          static_cast<T*>(p.out)[size_t(b) * p.o_sn + size_t(hh) * p.o_sh + size_t(ll) * p.o_sl + d] =
+              ElemTraits<T>::from_f(den > 0.f ? acc / den : 0.f);
+          if (p.lse && d == 0)
+            p.lse[(size_t(b) * p.h + hh) * p.l + ll] = den > 0.f ? (mm + log2f(den)) * 0.6931471805599453f : -INFINITY;
+        }
+        if (epi_tid == 0) p.counters[unit] = 0;
+      }
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, D_TMEM_COLS);
+  }
+}
+
+
+bool sdpa_decode_tc_eligible(const SdpaArgs& a) {
+  if (a.dtype != KUIOPS_BF16 && a.dtype != KUIOPS_F16) return false;
+  if (a.e != DD || a.ev != DD || a.bias != nullptr) return false;
+  const uint32_t G = a.h / a.h_kv;
+  if (a.l > 16 || uint64_t(G) * a.l > uint64_t(DBM) || G > 128) return false;
+  auto ok_stride = [](int64_t s) { return s > 0 && s % 8 == 0 && uint64_t(s) * 2 < (1ull << 40); };
+  if (!ok_stride(a.k_ss) || !ok_stride(a.v_ss) || a.o_sl % 8) return false;
+  if (a.l > 1 && !ok_stride(a.q_sl)) return false;
+  if (a.h > 1 && (!ok_stride(a.q_sh) || a.o_sh % 8)) return false;
+  if (a.h_kv > 1 && (!ok_stride(a.k_sh) || !ok_stride(a.v_sh))) return false;
+  if (a.n > 1 && (!ok_stride(a.q_sn) || !ok_stride(a.k_sn) || !ok_stride(a.v_sn) || a.o_sn % 8)) return false;
+  if (!aligned16(a.Q) || !aligned16(a.K) || !aligned16(a.V) || !aligned16(a.out)) return false;
+  return uint64_t(a.n) * a.h_kv * 64 < (1ull << 31);
+}
+
+static uint32_t decode_tc_splits(const SdpaArgs& a) {
+  const uint64_t units = uint64_t(a.n) * a.h_kv;
+  const uint64_t resident = 2 * uint64_t(kNumSMs);          // two CTAs per SM
+  if (units >= resident) return 1;
+  uint32_t want = uint32_t((resident + units - 1) / units);
+  uint32_t cap = a.s / (4 * DBN);                           // at least four key tiles per slice
+  if (cap < 1) cap = 1;
+  uint32_t splits = want < cap ? want : cap;
+  return splits > 64 ? 64 : splits;
+}
+
+size_t sdpa_decode_tc_workspace_bytes(const SdpaArgs& a) {
+  const uint32_t splits = decode_tc_splits(a);
+  if (splits == 1) return 0;
+  const uint64_t units = uint64_t(a.n) * a.h_kv;
+  const uint32_t rows = (a.h / a.h_kv) * a.l;
+  return ((units * 4 + 255) & ~size_t(255)) + size_t(units) * splits * rows * D_REC * sizeof(float);
+}
+
+size_t sdpa_decode_tc_counter_bytes(const SdpaArgs& a) {
+  return decode_tc_splits(a) == 1 ? 0 : ((uint64_t(a.n) * a.h_kv * 4 + 255) & ~size_t(255));
+}
+
+template <typename T>
+static int decode_tc_launch(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  const uint32_t G = a.h / a.h_kv;
+  DecParams p = {};
+  p.splits = decode_tc_splits(a);
+  if (p.splits > 1) {
+    if (!workspace || workspace_bytes < sdpa_decode_tc_workspace_bytes(a)) {
+      p.splits = 1;                 // no scratch: one CTA walks all keys of its (batch, KV head)
+    } else {
+      p.counters = static_cast<int*>(workspace);
+      p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + ((uint64_t(a.n) * a.h_kv * 4 + 255) & ~size_t(255)));
+    }
+  }
+  CUtensorMap mq, mk, mv;
+  {
+    // Q: (d, l, h, n); one box takes the l positions of the G heads of a group
+    const uint64_t dims[4] = {DD, a.l, a.h, a.n};
+    const uint64_t s_l = a.l > 1 ? uint64_t(a.q_sl) : uint64_t(DD);
+    const uint64_t s_h = a.h > 1 ? uint64_t(a.q_sh) : s_l * a.l;
+    const uint64_t strides[4] = {1, s_l, s_h, uint64_t(a.n > 1 ? uint64_t(a.q_sn) : s_h * a.h)};
+    const uint32_t box[4] = {64, a.l, G, 1};
+    if (!encode_tmap_2byte(&mq, a.Q, 4, dims, strides, box)) return KUIOPS_EDRIVER;
+  }
+  auto enc_kv = [](CUtensorMap* m, const void* base, uint32_t rows, uint32_t heads, uint32_t n, int64_t s_row,
+                   int64_t s_head, int64_t s_n) {
+    const uint64_t dims[4] = {DD, rows, heads, n};
+    const uint64_t sh = heads > 1 ? uint64_t(s_head) : uint64_t(s_row) * rows;
+    const uint64_t strides[4] = {1, uint64_t(s_row), sh, uint64_t(n > 1 ? uint64_t(s_n) : sh * heads)};
+    const uint32_t box[4] = {64, DBN, 1, 1};
+    return encode_tmap_2byte(m, base, 4, dims, strides, box);
+  };
+  if (!enc_kv(&mk, a.K, a.s, a.h_kv, a.n, a.k_ss, a.k_sh, a.k_sn)) return KUIOPS_EDRIVER;
+  if (!enc_kv(&mv, a.V, a.s, a.h_kv, a.n, a.v_ss, a.v_sh, a.v_sn)) return KUIOPS_EDRIVER;
+  p.n = a.n; p.h = a.h; p.h_kv = a.h_kv; p.l = a.l; p.s = a.s; p.G = G; p.rows = G * a.l;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.is_causal = a.is_causal;
+  p.kv_lens = a.kv_lens;
+  p.out = a.out; p.o_sn = a.o_sn; p.o_sh = a.o_sh; p.o_sl = a.o_sl; p.lse = a.lse;
+  p.err = tc_error_word_device();
+  if (!p.err) return KUIOPS_ELAUNCH;
+  constexpr size_t smem = D_SMEM + 128;
+  auto kern = sdpa_decode_tc_kernel<T>;
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return KUIOPS_ELAUNCH;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  const unsigned grid = unsigned(uint64_t(a.n) * a.h_kv * p.splits);
+  kern<<<grid, kDecThreads, smem, st>>>(mq, mk, mv, p);
+  return check_launch();
+}
+
+int sdpa_decode_tc(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (a.dtype == KUIOPS_BF16) return decode_tc_launch<__nv_bfloat16>(a, workspace, workspace_bytes, st);
+  return decode_tc_launch<__half>(a, workspace, workspace_bytes, st);
+}
+
+}  // namespace kuiops

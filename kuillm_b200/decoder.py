@@ -50,6 +50,26 @@ class DecoderConfig:
         return self.n_layers * per_layer + 2 * self.vocab * self.d_model + self.d_model
 
 
+def shard_out_features(t, n_blocks_total, block, rank, size):
+    """Rows [rank, rank + 1) / size of a [out, in] weight, in whole blocks of `block` output
+    features (a head's rows for Q / K / V, single rows for gate / up): the column-parallel split."""
+    per = n_blocks_total // size
+    return t[rank * per * block:(rank + 1) * per * block].contiguous()
+
+
+def shard_in_features(t, width_per_rank, rank):
+    """Columns of a [out, in] weight that multiply this rank's slice of the activations (O and
+    down projections): the row-parallel split whose partial products are summed by all-reduce."""
+    return t[:, rank * width_per_rank:(rank + 1) * width_per_rank].contiguous()
+
+
+def dp_slice(batch, rank, size):
+    """Sequences [lo, hi) of a global batch that rank `rank` of `size` data-parallel ranks serves."""
+    per = (batch + size - 1) // size
+    lo = min(rank * per, batch)
+    return lo, min(lo + per, batch)
+
+
 class Decoder:
     """Weights are stored as [out_features, in_features] (the Linear layout), i.e. the
     ``trans_b`` operand form of ``kuiops_gemm``, so no transpose is ever materialised."""
@@ -69,9 +89,8 @@ class Decoder:
 
         # every rank draws the full-size tensors from the same seed and keeps its shard, so a
         # tensor-parallel run holds exactly the weights of the single-GPU run
-        def shard_rows(t, n_blocks_total, block):   # split output features in whole blocks
-            per = n_blocks_total // tp_size
-            return t[tp_rank * per * block:(tp_rank + 1) * per * block].contiguous()
+        def shard_rows(t, n_blocks_total, block):
+            return shard_out_features(t, n_blocks_total, block, tp_rank, tp_size)
 
         self.embed = w(cfg.vocab, d)
         self.layers = []
@@ -82,9 +101,9 @@ class Decoder:
             layer = dict(
                 wqkv=torch.cat([shard_rows(wq, cfg.n_heads, hd), shard_rows(wk, cfg.n_kv_heads, hd),
                                 shard_rows(wv, cfg.n_kv_heads, hd)], 0).contiguous(),
-                wo=wo[:, tp_rank * self.hq * hd:(tp_rank + 1) * self.hq * hd].contiguous(),
+                wo=shard_in_features(wo, self.hq * hd, tp_rank),
                 wgu=torch.cat([shard_rows(wg, cfg.d_ff, 1), shard_rows(wu, cfg.d_ff, 1)], 0).contiguous(),
-                wd=wd[:, tp_rank * self.ff:(tp_rank + 1) * self.ff].contiguous(),
+                wd=shard_in_features(wd, self.ff, tp_rank),
                 n1=torch.ones(d, device=self.device, dtype=dt), n2=torch.ones(d, device=self.device, dtype=dt))
             del wq, wk, wv, wo, wg, wu, wd
             self.layers.append(layer)

@@ -32,17 +32,51 @@ def peaks():
         return 6650.0, 1590.0, "fallback"
 
 
+_side = None
+EAGER = False        # --eager: plain launches timed with events (what a profiler capture needs)
+MATCH = ""           # --match: only time cases whose "op shape" contains this text
+
+
+def wanted(op, shape):
+    return MATCH in f"{op} {shape}"
+
+
 def time_us(fn, n_variants, iters):
-    """Average device time of fn(i % n_variants) over `iters` launches."""
-    for i in range(min(3, n_variants) + 2):
-        fn(i % n_variants)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        fn(i % n_variants)
-    e1.record()
-    torch.cuda.synchronize()
+    """Average device time of fn(i % n_variants) over `iters` launches.  The launches are captured
+    in a CUDA graph and the replay is timed, so host-side launch cost (tens of microseconds per call
+    through Python) does not hide kernels that run for a few microseconds."""
+    global _side
+    if EAGER:
+        for i in range(2):
+            fn(i % n_variants)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i % n_variants)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / iters
+    if _side is None:
+        _side = torch.cuda.Stream()
+    _side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(_side):
+        for i in range(min(3, n_variants) + 2):
+            fn(i % n_variants)
+        _side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=_side):
+            for i in range(iters):
+                fn(i % n_variants)
+        graph.replay()
+        _side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(_side)
+        graph.replay()
+        e1.record(_side)
+        _side.synchronize()
+    torch.cuda.current_stream().wait_stream(_side)
+    del graph
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
@@ -56,6 +90,10 @@ class Table:
         self.rows, self.out = [], out
 
     def add(self, op, shape, us, bytes_=None, flops=None, bound="hbm", note=""):
+        if callable(us):
+            if not wanted(op, shape):
+                return
+            us = us()
         row = {"op": op, "shape": shape, "us": round(us, 2), "bound": bound, "peak_kind": self.kind}
         if bytes_ is not None:
             row["alg_bytes"] = int(bytes_)
@@ -76,28 +114,34 @@ class Table:
 def bench_stream(T, iters):
     dev = "cuda"
     m, n = 64, 128256
-    nv = variants_for(m * n * 4)
-    xs = [torch.randn(m, n, device=dev) * 3 for _ in range(nv)]
-    y = torch.empty_like(xs[0])
-    T.add("softmax_f32", f"{m}x{n}", time_us(lambda i: _ffi.softmax(xs[i], out=y), nv, iters), bytes_=2 * m * n * 4)
-    ps = [_ffi.softmax(x) for x in xs]
-    T.add("topk_f32_k50", f"{m}x{n}", time_us(lambda i: _ffi.topk(ps[i], 50), nv, iters), bytes_=m * n * 4 + m * 50 * 12)
-    T.add("argmax_f32", f"{m}x{n}", time_us(lambda i: _ffi.argmax_lastdim(xs[i]), nv, iters), bytes_=m * n * 4)
-    del xs, ps
+    if any(wanted(o, f"{m}x{n}") for o in ("softmax_f32", "topk_f32_k50", "argmax_f32")):
+        nv = variants_for(m * n * 4)
+        xs = [torch.randn(m, n, device=dev) * 3 for _ in range(nv)]
+        y = torch.empty_like(xs[0])
+        T.add("softmax_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.softmax(xs[i], out=y), nv, iters)), bytes_=2 * m * n * 4)
+        if wanted("topk_f32_k50", f"{m}x{n}"):
+            ps = [_ffi.softmax(x) for x in xs]
+            T.add("topk_f32_k50", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.topk(ps[i], 50), nv, iters)), bytes_=m * n * 4 + m * 50 * 12)
+            del ps
+        T.add("argmax_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.argmax_lastdim(xs[i]), nv, iters)), bytes_=m * n * 4)
+        del xs
     rows, d = 32 * 2048, 4096
-    nv = variants_for(rows * d * 4)
-    hs = [torch.randn(rows, d, device=dev) for _ in range(nv)]
-    T.add("mean_f32_lastdim", f"{rows}x{d}", time_us(lambda i: _ffi.mean_lastdim(hs[i]), nv, iters), bytes_=rows * d * 4)
-    T.add("reduce_max_f32", f"{rows * d}", time_us(lambda i: _ffi.reduce("max", hs[i]), nv, iters), bytes_=rows * d * 4)
-    hb = [h.bfloat16() for h in hs[:max(2, nv // 2)]]
-    w = torch.ones(d, device=dev, dtype=torch.bfloat16)
-    yb = torch.empty_like(hb[0])
-    T.add("rmsnorm_bf16", f"{rows}x{d}", time_us(lambda i: _ffi.rmsnorm(hb[i % len(hb)], w, 1e-5, out=yb), len(hb), iters),
-          bytes_=2 * rows * d * 2)
-    T.add("map_silu_bf16", f"{rows * d}", time_us(lambda i: _ffi.map1("silu", hb[i % len(hb)], out=yb), len(hb), iters),
-          bytes_=2 * rows * d * 2)
-    T.add("map2_add_bf16", f"{rows * d}", time_us(lambda i: _ffi.map2("add", hb[i % len(hb)], hb[(i + 1) % len(hb)], out=yb), len(hb), iters),
-          bytes_=3 * rows * d * 2)
+    if any(wanted(o, f"{rows}x{d}") or wanted(o, f"{rows * d}") for o in ("mean_f32_lastdim", "reduce_max_f32")):
+        nv = variants_for(rows * d * 4)
+        hs = [torch.randn(rows, d, device=dev) for _ in range(nv)]
+        T.add("mean_f32_lastdim", f"{rows}x{d}", (lambda: time_us(lambda i: _ffi.mean_lastdim(hs[i]), nv, iters)), bytes_=rows * d * 4)
+        T.add("reduce_max_f32", f"{rows * d}", (lambda: time_us(lambda i: _ffi.reduce("max", hs[i]), nv, iters)), bytes_=rows * d * 4)
+        del hs
+    if any(wanted(o, f"{rows}x{d}") or wanted(o, f"{rows * d}") for o in ("rmsnorm_bf16", "map_silu_bf16", "map2_add_bf16")):
+        hb = [torch.randn(rows, d, device=dev).bfloat16() for _ in range(2)]
+        w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        yb = torch.empty_like(hb[0])
+        T.add("rmsnorm_bf16", f"{rows}x{d}", (lambda: time_us(lambda i: _ffi.rmsnorm(hb[i % 2], w, 1e-5, out=yb), 2, iters)),
+              bytes_=2 * rows * d * 2)
+        T.add("map_silu_bf16", f"{rows * d}", (lambda: time_us(lambda i: _ffi.map1("silu", hb[i % 2], out=yb), 2, iters)),
+              bytes_=2 * rows * d * 2)
+        T.add("map2_add_bf16", f"{rows * d}", (lambda: time_us(lambda i: _ffi.map2("add", hb[i % 2], hb[(i + 1) % 2], out=yb), 2, iters)),
+              bytes_=3 * rows * d * 2)
 
 
 def bench_index(T, iters):
@@ -109,17 +153,17 @@ def bench_index(T, iters):
         ids = [torch.randint(0, 128256, (r, c), device=dev, generator=g) for _ in range(nv)]
         idx = torch.randint(0, c, (r, c), device=dev, generator=g)
         perm = torch.argsort(torch.rand(r, c, device=dev, generator=g), dim=1)
-        T.add("gather_i64_dim1", f"{r}x{c}", time_us(lambda i: _ffi.gather(ids[i], 1, idx), nv, iters), bytes_=3 * nb,
+        T.add("gather_i64_dim1", f"{r}x{c}", (lambda: time_us(lambda i: _ffi.gather(ids[i], 1, idx), nv, iters)), bytes_=3 * nb,
               note="payload in + index in + out")
-        T.add("scatter_i64_dim1", f"{r}x{c}", time_us(lambda i: _ffi.scatter(ids[i], 1, perm, ids[(i + 1) % nv]), nv, iters),
+        T.add("scatter_i64_dim1", f"{r}x{c}", (lambda: time_us(lambda i: _ffi.scatter(ids[i], 1, perm, ids[(i + 1) % nv]), nv, iters)),
               bytes_=5 * nb, note="self copy (r+w) + src + index + scattered write")
         pos = torch.randint(0, c, (c // 4,), device=dev, generator=g)
-        T.add("index_i64_dim1", f"{r}x{c}[:, {c // 4}]", time_us(lambda i: _ffi.index(ids[i], 1, [pos]), nv, iters),
+        T.add("index_i64_dim1", f"{r}x{c}[:, {c // 4}]", (lambda: time_us(lambda i: _ffi.index(ids[i], 1, [pos]), nv, iters)),
               bytes_=2 * r * (c // 4) * 8)
         stop = torch.randint(0, 128256, (1024,), device=dev, generator=g)
-        T.add("isin_i64_vs_1024", f"{r}x{c}", time_us(lambda i: _ffi.isin(ids[i], stop), nv, iters), bytes_=nb + r * c)
+        T.add("isin_i64_vs_1024", f"{r}x{c}", (lambda: time_us(lambda i: _ffi.isin(ids[i], stop), nv, iters)), bytes_=nb + r * c)
         parts = [[t[:, k * (c // 8):(k + 1) * (c // 8)].contiguous() for k in range(8)] for t in ids[:max(2, nv // 2)]]
-        T.add("cat_8_slices_dim1", f"8 x {r}x{c // 8}", time_us(lambda i: _ffi.cat(parts[i % len(parts)], 1), len(parts), iters),
+        T.add("cat_8_slices_dim1", f"8 x {r}x{c // 8}", (lambda: time_us(lambda i: _ffi.cat(parts[i % len(parts)], 1), len(parts), iters)),
               bytes_=2 * nb)
         del ids, parts
 
@@ -127,6 +171,8 @@ def bench_index(T, iters):
 def bench_gemm(T, iters):
     dev = "cuda"
     for (N, K) in ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)):
+        if MATCH and not any(wanted(o, f"M{M} N{N} K{K}") for o in ("gemm_bf16_tn", "addmm_bias_bf16_tn") for M in (1, 8, 16, 32, 128, 4096)):
+            continue
         nv = variants_for(N * K * 2)
         Ws = [(torch.randn(N, K, device=dev) / K ** 0.5).bfloat16() for _ in range(min(nv, 6 if N > 100000 else nv))]
         bias = torch.zeros(N, device=dev, dtype=torch.bfloat16)
@@ -135,28 +181,30 @@ def bench_gemm(T, iters):
                 continue
             A = torch.randn(M, K, device=dev).bfloat16()
             C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            us = time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, out=C), len(Ws), iters)
+            us = (lambda: time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, out=C), len(Ws), iters))
             by, fl = 2 * (M * K + N * K + M * N), 2 * M * N * K
             if M >= 4096:
                 T.add("gemm_bf16_tn", f"M{M} N{N} K{K}", us, bytes_=by, flops=fl, bound="tensor")
             else:
                 T.add("gemm_bf16_tn", f"M{M} N{N} K{K}", us, bytes_=by, flops=fl, bound="hbm")
             if M in (16, 4096) and N == 4096 and K == 4096:
-                us = time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, Cin=bias, out=C), len(Ws), iters)
+                us = (lambda: time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, Cin=bias, out=C), len(Ws), iters))
                 T.add("addmm_bias_bf16_tn", f"M{M} N{N} K{K}", us, bytes_=by, flops=fl, bound="tensor" if M >= 4096 else "hbm")
         del Ws
+    if MATCH and not any(wanted(o, "") for o in ("mm_bf16_nn", "bmm_bf16", "mm_f32_simt")):
+        return
     # row-major B (MN-major tiles), the aten.mm operand form
     A = torch.randn(4096, 4096, device=dev).bfloat16()
     Bs = [(torch.randn(4096, 4096, device=dev) / 64).bfloat16() for _ in range(8)]
-    T.add("mm_bf16_nn", "M4096 N4096 K4096", time_us(lambda i: _ffi.mm(A, Bs[i % 8]), 8, iters), flops=2 * 4096 ** 3,
+    T.add("mm_bf16_nn", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A, Bs[i % 8]), 8, iters)), flops=2 * 4096 ** 3,
           bytes_=3 * 2 * 4096 ** 2, bound="tensor")
     A3 = [torch.randn(32, 4096, 128, device=dev).bfloat16() for _ in range(4)]
     B3 = [(torch.randn(32, 128, 4096, device=dev) / 11.3).bfloat16() for _ in range(4)]
-    T.add("bmm_bf16", "32 x 4096x128x4096", time_us(lambda i: _ffi.bmm(A3[i % 4], B3[i % 4]), 4, iters),
+    T.add("bmm_bf16", "32 x 4096x128x4096", (lambda: time_us(lambda i: _ffi.bmm(A3[i % 4], B3[i % 4]), 4, iters)),
           bytes_=2 * 32 * (2 * 4096 * 128 + 4096 * 4096), flops=2 * 32 * 4096 * 128 * 4096, bound="hbm")
     A32 = torch.randn(4096, 4096, device=dev)
     B32 = torch.randn(4096, 4096, device=dev) / 64
-    T.add("mm_f32_simt", "M4096 N4096 K4096", time_us(lambda i: _ffi.mm(A32, B32), 1, max(3, iters // 4)), flops=2 * 4096 ** 3,
+    T.add("mm_f32_simt", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A32, B32), 1, max(3, iters // 4))), flops=2 * 4096 ** 3,
           bytes_=3 * 4 * 4096 ** 2, bound="tensor", note="SIMT fp32 path; fraction is against the bf16 tensor peak")
 
 
@@ -166,17 +214,21 @@ def bench_sdpa(T, iters):
     for hkv in (32, 8):
         for S in (1024, 4096, 16384):
             B, H = 8, 32
+            if not wanted("sdpa_prefill_causal_bf16", f"B{B} Hq{H} Hkv{hkv} S{S} D{D}"):
+                continue
             Q = torch.randn(B, H, S, D, device=dev).bfloat16()
             K = torch.randn(B, hkv, S, D, device=dev).bfloat16()
             V = torch.randn(B, hkv, S, D, device=dev).bfloat16()
             O = torch.empty_like(Q)
             it = max(2, iters // (4 if S >= 16384 else 1))
-            us = time_us(lambda i: _ffi.sdpa(Q, K, V, is_causal=True, need_lse=False, out=O), 1, it)
+            us = (lambda: time_us(lambda i: _ffi.sdpa(Q, K, V, is_causal=True, need_lse=False, out=O), 1, it))
             T.add("sdpa_prefill_causal_bf16", f"B{B} Hq{H} Hkv{hkv} S{S} D{D}", us, flops=2 * B * H * S * S * D,
                   bytes_=2 * (2 * B * H * S * D + 2 * B * hkv * S * D), bound="tensor")
             del Q, K, V, O
         for S in (4096, 32768):
             B, H = 64, 32
+            if not wanted("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}"):
+                continue
             kv_bytes = 2 * B * hkv * S * D * 2
             nv = variants_for(kv_bytes) if kv_bytes < (8 << 30) else 1
             nv = min(nv, 2)
@@ -184,7 +236,7 @@ def bench_sdpa(T, iters):
             Ks = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
             Vs = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
             O = torch.empty_like(Q)
-            us = time_us(lambda i: _ffi.sdpa(Q, Ks[i], Vs[i], is_causal=True, need_lse=False, out=O), nv, max(3, iters // 2))
+            us = (lambda: time_us(lambda i: _ffi.sdpa(Q, Ks[i], Vs[i], is_causal=True, need_lse=False, out=O), nv, max(3, iters // 2)))
             T.add("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}", us, bytes_=kv_bytes + 2 * B * H * D * 2 * 2,
                   flops=4 * B * H * S * D, bound="hbm")
             del Ks, Vs
@@ -195,9 +247,13 @@ def main():
     ap.add_argument("--only", default="stream,index,gemm,sdpa")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
+    ap.add_argument("--match", default="", help='only cases whose "op shape" text contains this')
+    ap.add_argument("--eager", action="store_true", help="time plain launches instead of a CUDA-graph replay")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("opbench needs a CUDA device")
+    global EAGER, MATCH
+    EAGER, MATCH = a.eager, a.match
     if a.out:
         Path(a.out).write_text("")
     T = Table(a.out)

@@ -1,0 +1,81 @@
+"""Tensor-parallel and data-parallel decoder on two GPUs (skipped with fewer): the TP logits must
+match the single-GPU logits of the same weights within the bf16 bar, with exactly two all-reduces
+per layer; DP ranks reproduce their slice of the single-GPU result bit for bit."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tp_worker(rank, size, port, q):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    for p in (root, root / "kuillm_b200"):
+        sys.path.insert(0, str(p))
+    import torch.distributed as dist
+    from kuillm_b200.decoder import Decoder, DecoderConfig, dp_slice
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=size, device_id=torch.device("cuda", rank))
+    cfg = DecoderConfig.tiny(n_heads=4, n_kv_heads=2)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (4, 16), generator=g).cuda()
+    # reference: the whole model on this rank's GPU
+    full = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05)
+    full.alloc_cache(4, 24)
+    ref = full.prefill(ids)
+    ref_tok = ref.argmax(-1)
+    ref2 = full.decode_step(ref_tok)
+    # tensor parallel over the two ranks
+    calls = [0]
+    real = dist.all_reduce
+
+    def counted(t, *a, **k):
+        calls[0] += 1
+        return real(t, *a, **k)
+    dist.all_reduce = counted
+    tp = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
+    tp.alloc_cache(4, 24)
+    out = tp.prefill(ids)
+    n_calls = calls[0]
+    out2 = tp.decode_step(ref_tok)
+    dist.all_reduce = real
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    ok_tp = rel(out, ref) < 3e-2 and rel(out2, ref2) < 3e-2 and n_calls == 2 * cfg.n_layers
+    # data parallel: this rank's slice of the batch, no collective
+    lo, hi = dp_slice(4, rank, size)
+    dp = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05)
+    dp.alloc_cache(hi - lo, 24)
+    ok_dp = torch.equal(dp.prefill(ids[lo:hi]), ref[lo:hi])
+    flag = torch.tensor([1 if (ok_tp and ok_dp) else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        q.put((int(flag.item()), rel(out, ref), rel(out2, ref2), n_calls))
+    dist.destroy_process_group()
+
+
+def test_tp2_and_dp2_match_single_gpu():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    ok, r1, r2, n = q.get(timeout=10)
+    assert ok == 1, (r1, r2, n)

@@ -312,8 +312,14 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc}
         print(json.dumps(line))
     if world > 1:
+        # a captured graph may hold NCCL work: drop it and drain the device before the ranks part,
+        # then leave without tearing the communicator down (teardown after graph capture can block)
         import torch.distributed as dist
-        dist.destroy_process_group()
+        dec._graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():

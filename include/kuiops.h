@@ -65,6 +65,12 @@ KUIOPS_API const char* kuiops_strerror(int code);
  * device-side error word to *host_out (0 = no wait ever ran out; otherwise the code of the
  * wait that gave up) and optionally clears it.  Synchronises the device. */
 KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
+/* Programmatic dependent launch for the short kernels of a decode step (GEMM, attention,
+ * RMSNorm, RoPE, SwiGLU, embedding, arg-max): when enabled (default; KUIOPS_PDL=0 in the
+ * environment or a 0 here turns it off) they are launched so that their set-up overlaps the
+ * tail of the previous kernel in the stream; each waits for that kernel's completion before
+ * touching memory, so results do not change.  Returns the previous setting. */
+KUIOPS_API int kuiops_set_pdl(int enabled);
 /* Number of kernels this library has enqueued since load (all threads). */
 KUIOPS_API uint64_t    kuiops_launch_count(void);
 
@@ -101,6 +107,16 @@ KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
                 void* C, int64_t ldc, int64_t stride_c,
                 void* workspace, size_t workspace_bytes,
                 kuiops_stream_t stream);
+
+/* Fused MLP front half: Y[m, j] = silu(A w_gate_j) * (A w_up_j), one tensor-core GEMM whose
+ * epilogue applies the activation, so the [M, 2N] gate|up product never reaches memory.
+ * W is [2N, K] (leading dimension ldw) with gate and up rows interleaved: row 2j = w_gate_j,
+ * row 2j + 1 = w_up_j.  bf16 / f16 operands that meet the tensor-core alignment rules only
+ * (KUIOPS_EUNSUPPORTED otherwise: run kuiops_gemm then kuiops_swiglu).  The dispatcher sees this
+ * as mm, mm, silu, mul (kuipy/kuiops.py:158,166 of the reference); no reference counterpart. */
+KUIOPS_API int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, const void* W, int64_t ldw, void* Y, int64_t ldy,
+                void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
 
 /* aten.mm: C[M,N] = A[M,K] x B[K,N], all dense row-major.
  * Reference launcher: (u32 M, u32 N, u32 K, in* A, in* B, out* C), kuiops/mm/wrapper_mm.cu.j2:15-19.

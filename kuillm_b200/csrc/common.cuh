@@ -21,6 +21,35 @@ inline int check_launch() {
 
 inline cudaStream_t as_stream(kuiops_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Kernels on the decode path are a few microseconds long, so launch latency and prologue are a
+// large share of a step.  A kernel launched with the programmatic-serialisation attribute may
+// begin (block scheduling, barrier / TMEM set-up) while its predecessor in the stream is still
+// running; it must execute pdl_wait() before it touches global memory, which blocks until the
+// predecessor grid has completed and its writes are visible.  pdl_trigger() tells the scheduler
+// that this block no longer minds dependents being scheduled next to it; it is called after the
+// block has claimed everything it will ever allocate (shared memory, TMEM), so a dependent that
+// parks on an SM can never starve the grid it is waiting for.  Without the launch attribute both
+// are no-ops.
+extern std::atomic<int> g_pdl_enabled;
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch `kern` (which calls pdl_wait() first thing) with the attribute when enabled.
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled.load(std::memory_order_relaxed) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+}
+
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {
   static __device__ __forceinline__ float to_f(float v) { return v; }
@@ -34,6 +63,17 @@ template <> struct ElemTraits<__half> {
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
 };
+
+// Two floats rounded and packed into one 32-bit word of 16-bit elements (first value in the low half).
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 // 16-byte vector of T, the unit of every coalesced HBM access here.
 template <typename T> struct alignas(16) Vec16 {

@@ -158,6 +158,8 @@ template <typename T, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residual, const T* __restrict__ w,
                float eps, T* __restrict__ y, T* residual_out) {
+  pdl_wait();
+  pdl_trigger();
   // WPR warps share a row (1, 2, 4 or 8), each thread keeps at most 4 vectors of it in registers
   constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
   __shared__ float red[8];
@@ -217,6 +219,8 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(uint64_t m, uint32_t n, const T* __restrict__ gu, T* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int VN = Vec16<T>::N;
   const uint32_t nvec = n / VN;
   const uint64_t total = m * nvec;
@@ -241,6 +245,8 @@ __global__ void __launch_bounds__(256)
 rope_qkv_kernel(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, T* qkv, int64_t row_stride,
                 const int64_t* __restrict__ positions, float log2_theta, T* k_cache, T* v_cache,
                 uint64_t cache_cap, uint32_t rows_per_seq) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int VN = Vec16<T>::N;
   const uint32_t half = d / 2, vec_per_half = half / VN;
   const uint32_t heads = hq + 2 * hk;                 // q heads, k heads, v heads
@@ -298,6 +304,8 @@ template <typename P>
 __global__ void __launch_bounds__(256)
 embedding_kernel(uint64_t rows, uint64_t width_p, uint64_t vocab, const P* __restrict__ table,
                  const int64_t* __restrict__ ids, P* __restrict__ out, int32_t* status) {
+  pdl_wait();
+  pdl_trigger();
   const uint64_t total = rows * width_p;
   const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
   for (uint64_t t = gt; t < total; t += gs) {
@@ -314,6 +322,8 @@ embedding_kernel(uint64_t rows, uint64_t width_p, uint64_t vocab, const P* __res
 // x[i] += delta over int64 (position counters kept on the device between captured decode steps)
 __global__ void __launch_bounds__(256)
 add_i64_kernel(uint64_t len, long long* x, long long delta) {
+  pdl_wait();
+  pdl_trigger();
   const uint64_t gs = uint64_t(gridDim.x) * blockDim.x;
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < len; i += gs) x[i] += delta;
 }
@@ -335,8 +345,7 @@ int kuiops_map(int dtype, int op, uint64_t len, const void* X, void* Y, double c
 
 int kuiops_add_i64(uint64_t len, int64_t* x, int64_t delta, kuiops_stream_t s) {
   if (len == 0 || !x) return KUIOPS_EINVAL;
-  add_i64_kernel<<<stream_grid(len, 256, 8), 256, 0, as_stream(s)>>>(len, reinterpret_cast<long long*>(x), delta);
-  return check_launch();
+  return launch_pdl(add_i64_kernel, dim3(stream_grid(len, 256, 8)), dim3(256), 0, as_stream(s), len, reinterpret_cast<long long*>(x), (long long)delta);
 }
 
 int kuiops_map2(int dtype, int op, uint64_t len, const void* X, const void* B, void* Y, double c1, kuiops_stream_t s) {
@@ -403,12 +412,11 @@ static int rmsnorm_launch(uint64_t m, uint32_t n, const void* x, const void* res
   auto X = static_cast<const T*>(x); auto R = static_cast<const T*>(res); auto W = static_cast<const T*>(w);
   auto Y = static_cast<T*>(y); auto RO = static_cast<T*>(res_out);
   // warps per row so that a thread holds at most 4 vectors
-  if (nvec <= 128) rmsnorm_kernel<T, 1><<<stream_grid(m, 8, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else if (nvec <= 256) rmsnorm_kernel<T, 2><<<stream_grid(m, 4, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else if (nvec <= 512) rmsnorm_kernel<T, 4><<<stream_grid(m, 2, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else if (nvec <= 1024) rmsnorm_kernel<T, 8><<<stream_grid(m, 1, 16), 256, 0, st>>>(m, n, X, R, W, eps, Y, RO);
-  else return KUIOPS_EUNSUPPORTED;
-  return check_launch();
+  if (nvec <= 128) return launch_pdl(rmsnorm_kernel<T, 1>, dim3(stream_grid(m, 8, 16)), dim3(256), 0, st, m, n, X, R, W, eps, Y, RO);
+  if (nvec <= 256) return launch_pdl(rmsnorm_kernel<T, 2>, dim3(stream_grid(m, 4, 16)), dim3(256), 0, st, m, n, X, R, W, eps, Y, RO);
+  if (nvec <= 512) return launch_pdl(rmsnorm_kernel<T, 4>, dim3(stream_grid(m, 2, 16)), dim3(256), 0, st, m, n, X, R, W, eps, Y, RO);
+  if (nvec <= 1024) return launch_pdl(rmsnorm_kernel<T, 8>, dim3(stream_grid(m, 1, 16)), dim3(256), 0, st, m, n, X, R, W, eps, Y, RO);
+  return KUIOPS_EUNSUPPORTED;
 }
 
 extern "C" {
@@ -429,8 +437,7 @@ static int swiglu_launch(uint64_t m, uint32_t n, const void* gu, void* y, cudaSt
   if (m == 0 || n == 0 || !gu || !y) return KUIOPS_EINVAL;
   if (n % VN || !aligned16(gu) || !aligned16(y)) return KUIOPS_EUNSUPPORTED;
   unsigned grid = stream_grid(m * (n / VN), 256 * 2, 16);
-  swiglu_kernel<T><<<grid, 256, 0, st>>>(m, n, static_cast<const T*>(gu), static_cast<T*>(y));
-  return check_launch();
+  return launch_pdl(swiglu_kernel<T>, dim3(grid), dim3(256), 0, st, m, n, static_cast<const T*>(gu), static_cast<T*>(y));
 }
 
 extern "C" {
@@ -457,10 +464,8 @@ static int rope_launch(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, void
     return KUIOPS_EUNSUPPORTED;
   const uint64_t total = rows * (hq + 2 * hk) * (d / 2 / VN);
   unsigned grid = stream_grid(total, 256, 16);
-  rope_qkv_kernel<T><<<grid, 256, 0, st>>>(rows, hq, hk, d, static_cast<T*>(qkv), row_stride, positions,
-                                           log2f(theta), static_cast<T*>(kc), static_cast<T*>(vc), cap,
-                                           rps ? rps : 1);
-  return check_launch();
+  return launch_pdl(rope_qkv_kernel<T>, dim3(grid), dim3(256), 0, st, rows, hq, hk, d, static_cast<T*>(qkv), row_stride,
+                    positions, log2f(theta), static_cast<T*>(kc), static_cast<T*>(vc), cap, rps ? rps : 1u);
 }
 
 extern "C" {
@@ -484,12 +489,11 @@ int kuiops_embedding(uint32_t elem_bytes, uint64_t rows, uint64_t width, uint64_
   if (row_bytes % 16 == 0 && aligned16(table) && aligned16(out)) {
     const uint64_t wp = row_bytes / 16;
     unsigned grid = stream_grid(rows * wp, 256, 16);
-    embedding_kernel<int4><<<grid, 256, 0, st>>>(rows, wp, vocab, (const int4*)table, ids, (int4*)out, status);
+    return launch_pdl(embedding_kernel<int4>, dim3(grid), dim3(256), 0, st, rows, wp, vocab, (const int4*)table, ids, (int4*)out, status);
   } else {
     unsigned grid = stream_grid(rows * row_bytes, 256, 16);
-    embedding_kernel<uint8_t><<<grid, 256, 0, st>>>(rows, row_bytes, vocab, (const uint8_t*)table, ids, (uint8_t*)out, status);
+    return launch_pdl(embedding_kernel<uint8_t>, dim3(grid), dim3(256), 0, st, rows, row_bytes, vocab, (const uint8_t*)table, ids, (uint8_t*)out, status);
   }
-  return check_launch();
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@ struct GemmArgs {
   const void* Cin; int64_t ldcin, stride_cin;
   float alpha, beta;
   void* C; int64_t ldc, stride_c;
+  int epilogue;   // 0: C = alpha*acc + beta*Cin;  1: C[m, j] = silu(acc[m, 2j]) * acc[m, 2j+1] (gate/up rows interleaved in B)
 };
 
 // SIMT kernel: any dtype / shape / stride.

@@ -1,15 +1,25 @@
 // C-ABI entry points of the GEMM family and the library-wide helpers.
 #include "gemm.cuh"
 #include "tc_ptx.cuh"
+#include <cstdlib>
 
 namespace kuiops {
 std::atomic<uint64_t> g_launches{0};
+static int pdl_default() {
+  const char* e = getenv("KUIOPS_PDL");
+  return (e && e[0] == '0') ? 0 : 1;
+}
+std::atomic<int> g_pdl_enabled{pdl_default()};
 }
 using namespace kuiops;
 
 extern "C" {
 
 int kuiops_abi_version(void) { return KUIOPS_ABI_VERSION; }
+
+int kuiops_set_pdl(int enabled) {
+  return g_pdl_enabled.exchange(enabled ? 1 : 0);
+}
 
 uint64_t kuiops_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -62,10 +72,24 @@ int kuiops_gemm(int dtype, int out_dtype, uint32_t batch, uint32_t M, uint32_t N
   a.B = B; a.ldb = ldb; a.stride_b = stride_b; a.trans_b = trans_b ? 1 : 0;
   a.Cin = Cin; a.ldcin = ldcin; a.stride_cin = stride_cin;
   a.alpha = alpha; a.beta = Cin ? beta : 0.f;
-  a.C = C; a.ldc = ldc; a.stride_c = stride_c;
+  a.C = C; a.ldc = ldc; a.stride_c = stride_c; a.epilogue = 0;
   cudaStream_t st = as_stream(stream);
   if (gemm_tc_eligible(a)) return gemm_tc(a, workspace, workspace_bytes, st);
   return gemm_simt(a, st);
+}
+
+int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
+                       const void* W, int64_t ldw, void* Y, int64_t ldy,
+                       void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || N == 0 || K == 0 || !A || !W || !Y) return KUIOPS_EINVAL;
+  if (lda < int64_t(K) || ldw < int64_t(K) || ldy < int64_t(N) || N > 0x7FFFFFFFu) return KUIOPS_EINVAL;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = 2 * N; a.K = K;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
+  a.alpha = 1.f; a.beta = 0.f; a.C = Y; a.ldc = ldy; a.epilogue = 1;
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  return gemm_tc(a, workspace, workspace_bytes, as_stream(stream));
 }
 
 #define KUIOPS_GEMM_ENTRIES(SUFFIX, DT)                                                                             \

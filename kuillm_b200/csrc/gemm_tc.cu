@@ -31,7 +31,7 @@ constexpr int kTcThreads = 192;
 struct TcParams {
   uint32_t rowsP, rowsQ, K, batch;
   uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split;
-  int swapped, out_f32;
+  int swapped, out_f32, epi;
   uint32_t M, N;
   float alpha, beta;
   const void* Cin; int64_t ldcin, stride_cin;
@@ -67,6 +67,21 @@ __device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32
     v += p.beta * ElemTraits<TIN>::to_f(cin[size_t(m) * p.ldcin + n]);
   }
   const size_t off = size_t(b) * p.stride_c + size_t(m) * p.ldc + n;
+  if (p.out_f32) static_cast<float*>(p.C)[off] = v;
+  else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+
+// SwiGLU epilogue, swapped placement: lane n holds column n of the fused gate|up product for row
+// `col`; gate and up of one output sit in neighbouring lanes (rows 2j, 2j+1 of the weight).
+// Warp-collective: every lane of the warp must call it.
+template <typename TIN>
+__device__ __forceinline__ void store_swiglu_swapped(const TcParams& p, uint32_t lane_row, uint32_t col, float acc) {
+  const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+  if ((lane_row & 1u) || col >= p.M || lane_row >= p.N) return;
+  const float v = silu_mul(acc, other);
+  const size_t off = size_t(col) * p.ldc + (lane_row >> 1);
   if (p.out_f32) static_cast<float*>(p.C)[off] = v;
   else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
 }
@@ -108,6 +123,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared memory, TMEM and the kernel parameters; the
+  // operands may still be being written by the previous kernel in the stream
+  pdl_wait();
+  pdl_trigger();
 
   const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
   const uint32_t units = tiles_per_batch * p.batch * p.splits;
@@ -211,7 +230,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         for (uint32_t c = 0; c < ncols; c += 16) {
           tc::tmem_ld16(taddr + c, v);
           tc::tmem_ld_wait();
-          if (c_vec && cin_vec && row < p.M && col0 + c + 16 <= p.N) {
+          if (p.epi == 1) {
+            if (p.swapped) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) store_swiglu_swapped<TIN>(p, row, col0 + c + j, v[j]);
+            } else if (row < p.M) {
+              // 16 consecutive columns = 8 (gate, up) pairs of one row -> 8 outputs
+              const uint32_t oc = (col0 + c) >> 1;
+              if (!p.out_f32 && (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && col0 + c + 16 <= p.N) {
+                Vec16<TIN> o;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o.v[j] = ElemTraits<TIN>::from_f(silu_mul(v[2 * j], v[2 * j + 1]));
+                st16(static_cast<TIN*>(p.C) + size_t(row) * p.ldc + oc, o);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (col0 + c + 2 * j + 1 < p.N) {
+                    const float r = silu_mul(v[2 * j], v[2 * j + 1]);
+                    const size_t off = size_t(row) * p.ldc + oc + j;
+                    if (p.out_f32) static_cast<float*>(p.C)[off] = r;
+                    else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(r);
+                  }
+                }
+              }
+            }
+          } else if (c_vec && cin_vec && row < p.M && col0 + c + 16 <= p.N) {
             // 16 consecutive outputs of one row: two 16-byte stores, addend fetched the same way
             float add[16];
 #pragma unroll
@@ -281,7 +324,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         float sum = part[0];
 #pragma unroll
         for (int s2 = 1; s2 < 8; ++s2) sum += part[s2];
-        store_elem<TIN>(p, b, row, col0 + c, sum);
+        if (p.epi == 1) store_swiglu_swapped<TIN>(p, row, col0 + c, sum);
+        else store_elem<TIN>(p, b, row, col0 + c, sum);
       }
     }
     __syncwarp();
@@ -412,11 +456,13 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = p.splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_pdl_enabled.load(std::memory_order_relaxed) ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mp, mq, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
@@ -452,7 +498,7 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   TcParams p = {};
   p.K = a.K; p.batch = a.batch;
   p.tilesP = pl.tilesP; p.tilesQ = pl.tilesQ; p.splits = pl.splits; p.kblocks = pl.kblocks; p.kb_per_split = pl.kb_per_split;
-  p.swapped = pl.swapped ? 1 : 0; p.out_f32 = a.out_dtype == KUIOPS_F32 ? 1 : 0;
+  p.swapped = pl.swapped ? 1 : 0; p.out_f32 = a.out_dtype == KUIOPS_F32 ? 1 : 0; p.epi = a.epilogue;
   p.M = a.M; p.N = a.N;
   p.rowsP = pl.swapped ? a.N : a.M; p.rowsQ = pl.swapped ? a.M : a.N;
   p.alpha = a.alpha; p.beta = a.beta;

@@ -14,6 +14,7 @@
 #include "sdpa.cuh"
 #include "tc_ptx.cuh"
 #include <type_traits>
+#include <cstdlib>
 
 namespace kuiops {
 
@@ -55,7 +56,11 @@ __device__ __forceinline__ bool dec_wait(uint64_t* bar, uint32_t parity) {
   return true;
 }
 
-template <typename T>
+// SMALL (at most 8 query rows, e.g. 4 GQA heads x 1 token): the Q and P operands keep a single
+// 8-row core-matrix group in shared memory and their descriptors use a zero stride between row
+// groups, so all 16 groups of the 128-row UMMA tile read the same 1 KB (TMEM lanes 8..127 then
+// hold copies of lanes 0..7 and are ignored).  The 46 KB this frees go to a third K/V ring slot.
+template <typename T, bool SMALL>
 __global__ void __launch_bounds__(kDecThreads, 2)
 sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const DecParams p) {
@@ -67,18 +72,23 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (threadIdx.x == 0) atomicExch(p.err, 10u);
     return;
   }
+  constexpr uint32_t NSLOT = SMALL ? 3 : 2;                    // K/V ring depth
+  constexpr uint32_t Q_HALF = SMALL ? 1024u : uint32_t(DBM) * 128u;   // bytes of one 64-column half of Q
+  constexpr uint32_t Q_BYTES = 2 * Q_HALF;
+  constexpr uint32_t P_BYTES = SMALL ? 1024u : D_P_BYTES;
+  constexpr uint32_t ROW_GROUP_STRIDE = SMALL ? 0u : 1024u;      // SBO of the Q and P descriptors
   unsigned char* q_s = smem;
-  unsigned char* kv_s = q_s + D_Q_BYTES;                       // slot i: K at kv_s + i*32K, V right after K
-  unsigned char* p_s = kv_s + 2 * (D_K_BYTES + D_V_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + D_P_BYTES);
+  unsigned char* kv_s = q_s + Q_BYTES;                         // slot i: K at kv_s + i*32K, V right after K
+  unsigned char* p_s = kv_s + NSLOT * (D_K_BYTES + D_V_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
   uint64_t* q_full = bars;          // 1
-  uint64_t* k_full = bars + 1;      // 2
-  uint64_t* v_full = bars + 3;      // 2
-  uint64_t* kv_empty = bars + 5;    // 2
-  uint64_t* s_full = bars + 7;      // 1
-  uint64_t* p_ready = bars + 8;     // 1
-  uint64_t* o_done = bars + 9;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* k_full = bars + 1;      // NSLOT (room for 3)
+  uint64_t* v_full = bars + 4;      // NSLOT
+  uint64_t* kv_empty = bars + 7;    // NSLOT
+  uint64_t* s_full = bars + 10;     // 2: S is double buffered so that Q K^T of the next tile overlaps this tile's softmax
+  uint64_t* p_ready = bars + 12;    // 1
+  uint64_t* o_done = bars + 13;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,27 +97,15 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t unit = blockIdx.x / p.splits;
   const uint32_t kvh = unit % p.h_kv;
   const uint32_t b = unit / p.h_kv;
-  // keys of this batch entry, optionally counted on the device
-  uint32_t S = p.s;
-  if (p.kv_lens) {
-    const long long kl = p.kv_lens[b];
-    S = kl < 0 ? 0u : (kl < (long long)p.s ? uint32_t(kl) : p.s);
-  }
-  // this CTA's slice of the keys, in whole tiles
-  const uint32_t tiles_total = (S + DBN - 1) / DBN;
-  const uint32_t tiles_per = (tiles_total + p.splits - 1) / p.splits;
-  const uint32_t s_lo = min(split * tiles_per * DBN, S);
-  const uint32_t s_hi = min(s_lo + tiles_per * DBN, S);
-  const uint32_t n_tiles = (s_hi - s_lo + DBN - 1) / DBN;
-
   // rows of the tile that carry no query must not feed NaN bit patterns into the MMA
-  for (uint32_t i = threadIdx.x; i < D_Q_BYTES / 16; i += blockDim.x) reinterpret_cast<int4*>(q_s)[i] = make_int4(0, 0, 0, 0);
+  for (uint32_t i = threadIdx.x; i < Q_BYTES / 16; i += blockDim.x) reinterpret_cast<int4*>(q_s)[i] = make_int4(0, 0, 0, 0);
   tc::fence_proxy_async();
 
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
-    tc::mbar_init(s_full, 1);
+    for (uint32_t i = 0; i < NSLOT; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
+    tc::mbar_init(&s_full[0], 1);
+    tc::mbar_init(&s_full[1], 1);
     tc::mbar_init(p_ready, 4);
     tc::mbar_init(o_done, 1);
     tc::fence_barrier_init();
@@ -122,15 +120,30 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+  pdl_wait();          // Q, the cache and the key counts may still be being written by earlier kernels
+  pdl_trigger();
+  // keys of this batch entry, optionally counted on the device
+  uint32_t S = p.s;
+  if (p.kv_lens) {
+    const long long kl = p.kv_lens[b];
+    S = kl < 0 ? 0u : (kl < (long long)p.s ? uint32_t(kl) : p.s);
+  }
+  // this CTA's slice of the keys, in whole tiles
+  const uint32_t tiles_total = (S + DBN - 1) / DBN;
+  const uint32_t tiles_per = (tiles_total + p.splits - 1) / p.splits;
+  const uint32_t s_lo = min(split * tiles_per * DBN, S);
+  const uint32_t s_hi = min(s_lo + tiles_per * DBN, S);
+  const uint32_t n_tiles = (s_hi - s_lo + DBN - 1) / DBN;
+
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
     if (lane == 0) {
       tc::mbar_expect_tx(q_full, 2u * p.rows * 128u);
       tc::tma_load_4d(q_s, &tmQ, q_full, 0, 0, int(kvh * p.G), int(b));
-      tc::tma_load_4d(q_s + DBM * 128, &tmQ, q_full, 64, 0, int(kvh * p.G), int(b));
+      tc::tma_load_4d(q_s + Q_HALF, &tmQ, q_full, 64, 0, int(kvh * p.G), int(b));
       for (uint32_t j = 0; j < n_tiles; ++j) {
-        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        const uint32_t slot = j % NSLOT, ph = (j / NSLOT) & 1;
         if (!dec_wait(&kv_empty[slot], ph ^ 1)) { atomicExch(p.err, 11u); break; }
         unsigned char* ks = kv_s + slot * (D_K_BYTES + D_V_BYTES);
         unsigned char* vs = ks + D_K_BYTES;
@@ -152,29 +165,37 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool ok = dec_wait(q_full, 0);
       if (!ok) atomicExch(p.err, 12u);
       const uint32_t qa = tc::smem_u32(q_s), pa = tc::smem_u32(p_s);
-      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+      // S = Q K^T of tile j into S buffer j & 1: two 64-wide halves of the head dim x four 16-wide steps
+      auto issue_qk = [&](uint32_t j) -> bool {
+        const uint32_t slot = j % NSLOT, ph = (j / NSLOT) & 1, sbuf = j & 1;
         const uint32_t ka = tc::smem_u32(kv_s + slot * (D_K_BYTES + D_V_BYTES));
-        const uint32_t va = ka + D_K_BYTES;
-        if (!dec_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); ok = false; break; }
+        if (!dec_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); return false; }
         tc::tc_fence_after();
-        // S = Q K^T over the 128 head-dim elements: two 64-wide halves x four 16-wide steps
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = tc::make_smem_desc(qa + hh * (DBM * 128) + kk * 32, 16, 1024);
+            const uint64_t da = tc::make_smem_desc(qa + hh * Q_HALF + kk * 32, 16, ROW_GROUP_STRIDE);
             const uint64_t db = tc::make_smem_desc(ka + hh * (DBN * 128) + kk * 32, 16, 1024);
-            tc::umma_f16(tmem_S, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
+            tc::umma_f16(tmem_S + sbuf * DBN, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
           }
-        tc::umma_commit(s_full);
+        tc::umma_commit(&s_full[sbuf]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t slot = j % NSLOT, ph = (j / NSLOT) & 1;
+        const uint32_t va = tc::smem_u32(kv_s + slot * (D_K_BYTES + D_V_BYTES)) + D_K_BYTES;
+        // the next tile's scores are computed while the softmax warps work on this one; their S
+        // buffer was released when p_ready of tile j - 1 arrived
+        if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
         if (!dec_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
         if (!dec_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
         tc::tc_fence_after();
         // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, 1024);
+          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, ROW_GROUP_STRIDE);
           const uint64_t db = tc::make_smem_desc(va + kk * 2048, DBN * 128, 1024);
           tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
@@ -199,24 +220,23 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (uint32_t j = 0; j < n_tiles && ok; ++j) {
-      if (!dec_wait(s_full, j & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      if (!dec_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(p.err, 16u); ok = false; break; }
       tc::tc_fence_after();
       float sv[DBN];
       float corr = 1.f;
       if (warp_active) {
-        tc::tmem_ld32(tmem_S + lane_addr, sv);
-        tc::tmem_ld32(tmem_S + lane_addr + 32, sv + 32);
+        tc::tmem_ld32(tmem_S + (j & 1) * DBN + lane_addr, sv);
+        tc::tmem_ld32(tmem_S + (j & 1) * DBN + lane_addr + 32, sv + 32);
         tc::tmem_ld_wait();
         const int64_t key0 = int64_t(s_lo) + int64_t(j) * DBN;
         const bool edge = key0 + DBN - 1 > row_lim;
         float mx = -INFINITY;
 #pragma unroll
         for (int c = 0; c < DBN; ++c) {
-          float v = sv[c] * p.scale_log2;
-          if (edge && key0 + c > row_lim) v = -INFINITY;
-          sv[c] = v;
-          mx = fmaxf(mx, v);
+          if (edge && key0 + c > row_lim) sv[c] = -INFINITY;
+          mx = fmaxf(mx, sv[c]);
         }
+        mx *= p.scale_log2;                       // scale > 0: the max commutes with the scaling
         if (mx > m_used + kDecRescale || m_used == -INFINITY) {
           const float m_new = fmaxf(mx, m_used);
           corr = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
@@ -225,7 +245,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const float mm = (m_used == -INFINITY) ? 0.f : m_used;
         float rs = 0.f;
 #pragma unroll
-        for (int c = 0; c < DBN; ++c) { sv[c] = exp2f(sv[c] - mm); rs += sv[c]; }
+        for (int c = 0; c < DBN; ++c) { sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -mm)); rs += sv[c]; }
         l_run = l_run * corr + rs;
       }
       if (j > 0) {
@@ -245,16 +265,18 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tc::tmem_st_wait();
         }
       }
-      if (warp_active) {
-        unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+      if (warp_active && (!SMALL || r < 8)) {
+        unsigned char* prow = p_s + (SMALL ? 0u : (r >> 3) * 1024) + (r & 7) * 128;
 #pragma unroll
         for (int c = 0; c < DBN / 8; ++c) {
-          Vec16<T> pk;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) pk.v[e] = ElemTraits<T>::from_f(row_valid ? sv[c * 8 + e] : 0.f);
-          *reinterpret_cast<Vec16<T>*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+          uint4 pk;
+          pk.x = row_valid ? pack2<T>(sv[c * 8 + 0], sv[c * 8 + 1]) : 0u;
+          pk.y = row_valid ? pack2<T>(sv[c * 8 + 2], sv[c * 8 + 3]) : 0u;
+          pk.z = row_valid ? pack2<T>(sv[c * 8 + 4], sv[c * 8 + 5]) : 0u;
+          pk.w = row_valid ? pack2<T>(sv[c * 8 + 6], sv[c * 8 + 7]) : 0u;
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
         }
-      } else if (j == 0) {
+      } else if (j == 0 && !SMALL) {
         // rows that never carry a query: one zero fill keeps the P operand free of stale bit patterns
         unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
@@ -362,6 +384,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 bool sdpa_decode_tc_eligible(const SdpaArgs& a) {
   if (a.dtype != KUIOPS_BF16 && a.dtype != KUIOPS_F16) return false;
+  if (!(a.scale > 0.f)) return false;               // the softmax takes the row max before scaling
   if (a.e != DD || a.ev != DD || a.bias != nullptr) return false;
   const uint32_t G = a.h / a.h_kv;
   if (a.l > 16 || uint64_t(G) * a.l > uint64_t(DBM) || G > 128) return false;
@@ -379,7 +402,7 @@ static uint32_t decode_tc_splits(const SdpaArgs& a) {
   const uint64_t units = uint64_t(a.n) * a.h_kv;
   const uint64_t resident = 2 * uint64_t(kNumSMs);          // two CTAs per SM
   if (units >= resident) return 1;
-  uint32_t want = uint32_t((resident + units - 1) / units);
+  uint32_t want = uint32_t(resident / units);               // whole waves only: a partial second wave costs a full one
   uint32_t cap = a.s / (4 * DBN);                           // at least four key tiles per slice
   if (cap < 1) cap = 1;
   uint32_t splits = want < cap ? want : cap;
@@ -396,6 +419,21 @@ size_t sdpa_decode_tc_workspace_bytes(const SdpaArgs& a) {
 
 size_t sdpa_decode_tc_counter_bytes(const SdpaArgs& a) {
   return decode_tc_splits(a) == 1 ? 0 : ((uint64_t(a.n) * a.h_kv * 4 + 255) & ~size_t(255));
+}
+
+template <typename T, bool SMALL>
+static int decode_tc_launch_variant(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p,
+                                    unsigned grid, size_t smem, cudaStream_t st) {
+  auto kern = sdpa_decode_tc_kernel<T, SMALL>;
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return KUIOPS_ELAUNCH;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  return launch_pdl(kern, dim3(grid), dim3(kDecThreads), smem, st, mq, mk, mv, p);
 }
 
 template <typename T>
@@ -438,19 +476,11 @@ static int decode_tc_launch(const SdpaArgs& a, void* workspace, size_t workspace
   p.out = a.out; p.o_sn = a.o_sn; p.o_sh = a.o_sh; p.o_sl = a.o_sl; p.lse = a.lse;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
-  constexpr size_t smem = D_SMEM + 128;
-  auto kern = sdpa_decode_tc_kernel<T>;
-  static std::atomic<uint64_t> configured{0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
-  const uint64_t bit = 1ull << (dev & 63);
-  if (!(configured.load(std::memory_order_acquire) & bit)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return KUIOPS_ELAUNCH;
-    configured.fetch_or(bit, std::memory_order_release);
-  }
   const unsigned grid = unsigned(uint64_t(a.n) * a.h_kv * p.splits);
-  kern<<<grid, kDecThreads, smem, st>>>(mq, mk, mv, p);
-  return check_launch();
+  static const bool small_ok = [] { const char* e = getenv("KUIOPS_DECODE_SMALL"); return !(e && e[0] == '0'); }();
+  if (p.rows <= 8 && small_ok)
+    return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 1024 + 128, st);
+  return decode_tc_launch_variant<T, false>(mq, mk, mv, p, grid, D_SMEM + 128, st);
 }
 
 int sdpa_decode_tc(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {

@@ -30,7 +30,7 @@ constexpr uint32_t F_K_BYTES = FBN * FD * 2;        // 16 KB: two halves of 8 KB
 constexpr uint32_t F_V_BYTES = FBN * FD * 2;        // 16 KB: two 64-column boxes of 8 KB
 constexpr uint32_t F_P_BYTES = FBM * FBN * 2;       // 16 KB
 constexpr uint32_t F_SMEM = F_Q_BYTES + 2 * (F_K_BYTES + F_V_BYTES) + F_P_BYTES;   // 112 KB
-constexpr uint32_t F_TMEM_COLS = 256;               // S at column 0 (64 used), O at column 128
+constexpr uint32_t F_TMEM_COLS = 256;               // two S buffers at columns 0 and 64, O at column 128
 constexpr float kRescaleThreshold = 8.0f;           // log2 units
 
 struct FlashParams {
@@ -76,10 +76,10 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
   uint64_t* kv_empty = bars + 5;    // 2
-  uint64_t* s_full = bars + 7;      // 1
-  uint64_t* p_ready = bars + 8;     // 1
-  uint64_t* o_done = bars + 9;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* s_full = bars + 7;      // 2: S is double buffered so that Q K^T of the next tile overlaps this tile's softmax
+  uint64_t* p_ready = bars + 9;     // 1
+  uint64_t* o_done = bars + 10;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heaviest query tiles (most visible keys under the causal mask) are scheduled first
@@ -100,7 +100,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
-    tc::mbar_init(s_full, 1);
+    tc::mbar_init(&s_full[0], 1);
+    tc::mbar_init(&s_full[1], 1);
     tc::mbar_init(p_ready, 4);
     tc::mbar_init(o_done, 1);
     tc::fence_barrier_init();
@@ -115,6 +116,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+  pdl_wait();          // Q, K, V may still be being written by the previous kernel in the stream
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -145,22 +148,30 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       bool ok = flash_wait(q_full, 0);
       if (!ok) atomicExch(p.err, 12u);
       const uint32_t qa = tc::smem_u32(q_s), pa = tc::smem_u32(p_s);
-      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+      // S = Q K^T of tile j into S buffer j & 1: two 64-wide halves of the head dim x four 16-wide steps
+      auto issue_qk = [&](uint32_t j) -> bool {
         const uint32_t slot = j & 1, ph = (j >> 1) & 1;
         const uint32_t ka = tc::smem_u32(kv_s + slot * (F_K_BYTES + F_V_BYTES));
-        const uint32_t va = ka + F_K_BYTES;
-        if (!flash_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); ok = false; break; }
+        if (!flash_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); return false; }
         tc::tc_fence_after();
-        // S = Q K^T over the 128 head-dim elements: two 64-wide halves x four 16-wide steps
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t da = tc::make_smem_desc(qa + hh * (FBM * 128) + kk * 32, 16, 1024);
             const uint64_t db = tc::make_smem_desc(ka + hh * (FBN * 128) + kk * 32, 16, 1024);
-            tc::umma_f16(tmem_S, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
+            tc::umma_f16(tmem_S + slot * FBN, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
           }
-        tc::umma_commit(s_full);
+        tc::umma_commit(&s_full[slot]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t slot = j & 1, ph = (j >> 1) & 1;
+        const uint32_t va = tc::smem_u32(kv_s + slot * (F_K_BYTES + F_V_BYTES)) + F_K_BYTES;
+        // the next tile's scores are computed while the softmax warps work on this one; their S
+        // buffer was released when p_ready of tile j - 1 arrived
+        if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
         if (!flash_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
         if (!flash_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
         tc::tc_fence_after();
@@ -186,22 +197,21 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (uint32_t j = 0; j < n_tiles && ok; ++j) {
-      if (!flash_wait(s_full, j & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      if (!flash_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(p.err, 16u); ok = false; break; }
       tc::tc_fence_after();
       float sv[FBN];
-      tc::tmem_ld32(tmem_S + lane_addr, sv);
-      tc::tmem_ld32(tmem_S + lane_addr + 32, sv + 32);
+      tc::tmem_ld32(tmem_S + (j & 1) * FBN + lane_addr, sv);
+      tc::tmem_ld32(tmem_S + (j & 1) * FBN + lane_addr + 32, sv + 32);
       tc::tmem_ld_wait();
       const int64_t key0 = int64_t(j) * FBN;
       const bool edge = key0 + FBN - 1 > row_lim;          // tile crosses this row's limit (or the end of the keys)
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < FBN; ++c) {
-        float v = sv[c] * p.scale_log2;
-        if (edge && key0 + c > row_lim) v = -INFINITY;
-        sv[c] = v;
-        mx = fmaxf(mx, v);
+        if (edge && key0 + c > row_lim) sv[c] = -INFINITY;
+        mx = fmaxf(mx, sv[c]);
       }
+      mx *= p.scale_log2;                       // scale > 0: the max commutes with the scaling
       float corr = 1.f;
       if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
         const float m_new = fmaxf(mx, m_used);
@@ -211,7 +221,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float mm = (m_used == -INFINITY) ? 0.f : m_used;   // a fully masked row keeps p = 0
       float rs = 0.f;
 #pragma unroll
-      for (int c = 0; c < FBN; ++c) { sv[c] = exp2f(sv[c] - mm); rs += sv[c]; }
+      for (int c = 0; c < FBN; ++c) { sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -mm)); rs += sv[c]; }
       l_run = l_run * corr + rs;
       if (j > 0) {
         // the previous P V must be done before P's buffer is overwritten or O is touched
@@ -235,10 +245,12 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
       for (int c = 0; c < FBN / 8; ++c) {
-        Vec16<T> pk;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) pk.v[e] = ElemTraits<T>::from_f(sv[c * 8 + e]);
-        *reinterpret_cast<Vec16<T>*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+        uint4 pk;
+        pk.x = pack2<T>(sv[c * 8 + 0], sv[c * 8 + 1]);
+        pk.y = pack2<T>(sv[c * 8 + 2], sv[c * 8 + 3]);
+        pk.z = pack2<T>(sv[c * 8 + 4], sv[c * 8 + 5]);
+        pk.w = pack2<T>(sv[c * 8 + 6], sv[c * 8 + 7]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
       }
       tc::fence_proxy_async();          // make the generic-proxy writes visible to the UMMA (async proxy)
       tc::tc_fence_before();
@@ -287,6 +299,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 bool sdpa_flash_eligible(const SdpaArgs& a) {
   if (a.dtype != KUIOPS_BF16 && a.dtype != KUIOPS_F16) return false;
+  if (!(a.scale > 0.f)) return false;               // the softmax takes the row max before scaling
   if (a.e != FD || a.ev != FD || a.bias != nullptr || a.kv_lens != nullptr) return false;
   if (a.l < 64) return false;                       // short query blocks belong to the split-KV kernel
   if (a.is_causal && a.l > a.s) return false;       // rows without any visible key
@@ -332,8 +345,7 @@ static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
     configured.fetch_or(bit, std::memory_order_release);
   }
   const unsigned grid = unsigned(uint64_t(a.n) * a.h * ((a.l + FBM - 1) / FBM));
-  kern<<<grid, kFlashThreads, smem, st>>>(mq, mk, mv, p);
-  return check_launch();
+  return launch_pdl(kern, dim3(grid), dim3(kFlashThreads), smem, st, mq, mk, mv, p);
 }
 
 int sdpa_flash(const SdpaArgs& a, cudaStream_t st) {

@@ -10,12 +10,12 @@ namespace kuiops {
 // --------------------------------------------------------------------------------------
 // Row softmax.
 // A row is split over the CTAs of one thread-block cluster (1, 2, 4 or 8 CTAs) so that a
-// handful of very long rows (64 x 128256 logits) still covers every SM.  Each CTA makes one
-// pass over its slice keeping an online (max, sum-of-exp) pair, the pairs are exchanged
-// through distributed shared memory, and a second pass writes exp(x - M) / S.  The slice is
-// held in registers between the passes when it fits (CACHE_VECS 16-byte vectors per thread),
-// so HBM sees one read and one write; longer slices are re-read (served by L2 when the
-// matrix fits there).
+// handful of very long rows (64 x 128256 logits) still covers every SM.  Each CTA finds the max
+// of its slice, then the sum of exp(x - max); every CTA pushes its (max, sum) pair into the shared
+// memory of all its peers (distributed shared memory), one cluster barrier later each CTA combines
+// the pairs locally and writes exp(x - M) / S.  The slice is held in registers between the passes
+// when it fits (CACHE_VECS 16-byte vectors per thread), so HBM sees one read and one write; longer
+// slices are re-read (served by L2 when the matrix fits there).
 // Replaces Klas.RowSoftmax.inst_gpu, one block per row, in place
 // (kuiops/softmax/Kuiops.Softmax.Inst.fst.j2:10-11).
 // --------------------------------------------------------------------------------------
@@ -23,23 +23,50 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct MaxSum { float m, s; };
 
-__device__ __forceinline__ void online_add(MaxSum& a, float x) {
-  // fold one value into (m, s) with s = sum exp(x_i - m)
-  if (x > a.m) {
-    a.s = a.s * exp2f((a.m - x) * kLog2e) + 1.f;
-    a.m = x;
-  } else {
-    a.s += exp2f((x - a.m) * kLog2e);
-  }
+// Every thread gets the block-wide max (or sum) of v; `red` is a 32-float shared scratch.
+__device__ __forceinline__ float block_allreduce_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  __syncthreads();
+  return t;
 }
-__device__ __forceinline__ MaxSum online_merge(MaxSum a, MaxSum b) {
-  if (b.m == -INFINITY) return a;
-  if (a.m == -INFINITY) return b;
-  float m = fmaxf(a.m, b.m);
-  MaxSum r;
-  r.m = m;
-  r.s = a.s * exp2f((a.m - m) * kLog2e) + b.s * exp2f((b.m - m) * kLog2e);
-  return r;
+__device__ __forceinline__ float block_allreduce_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// Apply f to every element of the slice [lo, hi) of row x, four 16-byte loads in flight per thread.
+template <typename T, typename F>
+__device__ __forceinline__ void for_slice(const T* x, uint32_t lo, uint32_t hi, int vec_ok, F f) {
+  constexpr int VN = Vec16<T>::N;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  if (vec_ok) {
+    const uint32_t nvec = (hi - lo) / VN;
+    for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
+      Vec16<T> t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * nt < nvec) {
+#pragma unroll
+          for (int e = 0; e < VN; ++e) f(ElemTraits<T>::to_f(t[u].v[e]), lo + (v0 + u * nt) * VN + e);
+        }
+    }
+    for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt) f(ElemTraits<T>::to_f(x[i]), i);
+  } else {
+    for (uint32_t i = lo + tid; i < hi; i += nt) f(ElemTraits<T>::to_f(x[i]), i);
+  }
 }
 
 template <typename T, int CACHE_VECS>
@@ -47,12 +74,14 @@ __global__ void __launch_bounds__(1024)
 softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
                     uint32_t cluster_ctas, int vec_ok) {
   constexpr int VN = Vec16<T>::N;
-  __shared__ float red_m[32], red_s[32];
-  __shared__ MaxSum cta_pair;
+  __shared__ float red[32];
+  __shared__ MaxSum pairs[8];        // (max, sum of exp) of every CTA of the cluster, pushed by its owner
 
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
   const uint32_t row = blockIdx.x / cluster_ctas;
+  // peers must be running before their shared memory is written; arrive now, wait just before the push
+  if (cluster_ctas > 1) cluster.barrier_arrive();
   // slice boundaries in elements, multiples of VN so vector accesses stay aligned
   const uint32_t nv_total = (n + VN - 1) / VN;
   const uint32_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
@@ -60,95 +89,81 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
   const uint32_t hi = min(lo + nv_per * VN, n);
   const T* x = X + size_t(row) * n;
   T* y = Y + size_t(row) * n;
-  const int tid = threadIdx.x, nt = blockDim.x;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  const uint32_t nvec = (hi - lo) / VN;
 
+  // ---- pass 1: slice max (the slice stays in registers when it fits) ------------------------
   Vec16<T> cache[CACHE_VECS > 0 ? CACHE_VECS : 1];
-  MaxSum acc{-INFINITY, 0.f};
-
-  if (row < m) {
-    if (vec_ok) {
-      const uint32_t nvec = (hi - lo) / VN;           // full vectors in the slice
-      if (CACHE_VECS > 0) {
+  float mx = -INFINITY;
+  if (CACHE_VECS > 0) {
 #pragma unroll
-        for (int c = 0; c < CACHE_VECS; ++c) {
-          uint32_t v = tid + c * nt;
-          if (v < nvec) {
-            cache[c] = ld16_stream(x + lo + size_t(v) * VN);
+    for (int c = 0; c < CACHE_VECS; ++c)
+      if (tid + c * nt < nvec) cache[c] = ld16_stream(x + lo + size_t(tid + c * nt) * VN);
 #pragma unroll
-            for (int e = 0; e < VN; ++e) online_add(acc, ElemTraits<T>::to_f(cache[c].v[e]));
-          }
-        }
-      } else {
-        for (uint32_t v = tid; v < nvec; v += nt) {
-          Vec16<T> t = ld16(x + lo + size_t(v) * VN);
+    for (int c = 0; c < CACHE_VECS; ++c)
+      if (tid + c * nt < nvec) {
 #pragma unroll
-          for (int e = 0; e < VN; ++e) online_add(acc, ElemTraits<T>::to_f(t.v[e]));
-        }
+        for (int e = 0; e < VN; ++e) mx = fmaxf(mx, ElemTraits<T>::to_f(cache[c].v[e]));
       }
-      for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt)
-        online_add(acc, ElemTraits<T>::to_f(x[i]));
-    } else {
-      for (uint32_t i = lo + tid; i < hi; i += nt) online_add(acc, ElemTraits<T>::to_f(x[i]));
-    }
-  }
-  // block merge
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    MaxSum b{__shfl_xor_sync(0xffffffffu, acc.m, o), __shfl_xor_sync(0xffffffffu, acc.s, o)};
-    acc = online_merge(acc, b);
-  }
-  const int lane = tid & 31, w = tid >> 5, nw = (nt + 31) >> 5;
-  if (lane == 0) { red_m[w] = acc.m; red_s[w] = acc.s; }
-  __syncthreads();
-  if (w == 0) {
-    MaxSum t = lane < nw ? MaxSum{red_m[lane], red_s[lane]} : MaxSum{-INFINITY, 0.f};
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      MaxSum b{__shfl_xor_sync(0xffffffffu, t.m, o), __shfl_xor_sync(0xffffffffu, t.s, o)};
-      t = online_merge(t, b);
-    }
-    if (lane == 0) cta_pair = t;
-  }
-  MaxSum tot;
-  if (cluster_ctas > 1) {
-    cluster.sync();
-    tot = MaxSum{-INFINITY, 0.f};
-    for (uint32_t r = 0; r < cluster_ctas; ++r) {
-      const MaxSum* remote = cluster.map_shared_rank(&cta_pair, r);
-      tot = online_merge(tot, *remote);
-    }
-    cluster.sync();   // nobody leaves while a peer may still read its pair
   } else {
-    __syncthreads();
-    tot = cta_pair;
+    for_slice(x, lo, hi, vec_ok, [&](float v, uint32_t) { mx = fmaxf(mx, v); });
   }
-  if (row >= m) return;
-  const float M = tot.m;
-  const float inv = 1.f / tot.s;
-  const float mb = -M * kLog2e;
-  if (vec_ok) {
-    const uint32_t nvec = (hi - lo) / VN;
-    if (CACHE_VECS > 0) {
+  const float bm = block_allreduce_max(mx, red);
+  // ---- pass 2: sum of exp(x - slice max) ------------------------------------------------------
+  const float nb = (bm == -INFINITY) ? 0.f : -bm * kLog2e;
+  float sm = 0.f;
+  if (CACHE_VECS > 0) {
 #pragma unroll
-      for (int c = 0; c < CACHE_VECS; ++c) {
-        uint32_t v = tid + c * nt;
-        if (v < nvec) {
-          Vec16<T> o;
+    for (int c = 0; c < CACHE_VECS; ++c)
+      if (tid + c * nt < nvec) {
 #pragma unroll
-          for (int e = 0; e < VN; ++e)
-            o.v[e] = ElemTraits<T>::from_f(
-                exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, mb)) * inv);
-          st16(y + lo + size_t(v) * VN, o);
-        }
+        for (int e = 0; e < VN; ++e) sm += exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, nb));
       }
-    } else {
-      for (uint32_t v = tid; v < nvec; v += nt) {
-        Vec16<T> t = ld16(x + lo + size_t(v) * VN), o;
+  } else {
+    for_slice(x, lo, hi, vec_ok, [&](float v, uint32_t) { sm += exp2f(fmaf(v, kLog2e, nb)); });
+  }
+  const float bs = block_allreduce_sum(sm, red);
+  // ---- exchange: push this CTA's pair into every peer, one cluster barrier, read locally ------
+  float M = bm, S = bs;
+  if (cluster_ctas > 1) {
+    cluster.barrier_wait();
+    if (tid < cluster_ctas) {
+      MaxSum* dst = cluster.map_shared_rank(pairs, tid);
+      dst[part] = MaxSum{bm, bs};
+    }
+    cluster.sync();
+    M = -INFINITY;
+    for (uint32_t r = 0; r < cluster_ctas; ++r) M = fmaxf(M, pairs[r].m);
+    S = 0.f;
+    for (uint32_t r = 0; r < cluster_ctas; ++r)
+      if (pairs[r].m != -INFINITY) S += pairs[r].s * exp2f((pairs[r].m - M) * kLog2e);
+  }
+  // ---- pass 3: write exp(x - M) / S -------------------------------------------------------------
+  const float inv = 1.f / S;
+  const float mb = -M * kLog2e;
+  if (CACHE_VECS > 0) {
+#pragma unroll
+    for (int c = 0; c < CACHE_VECS; ++c)
+      if (tid + c * nt < nvec) {
+        Vec16<T> o;
 #pragma unroll
         for (int e = 0; e < VN; ++e)
-          o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(t.v[e]), kLog2e, mb)) * inv);
-        st16(y + lo + size_t(v) * VN, o);
+          o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, mb)) * inv);
+        st16(y + lo + size_t(tid + c * nt) * VN, o);
       }
+  } else if (vec_ok) {
+    for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
+      Vec16<T> t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * nt < nvec) {
+          Vec16<T> o;
+#pragma unroll
+          for (int e = 0; e < VN; ++e) o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(t[u].v[e]), kLog2e, mb)) * inv);
+          st16(y + lo + size_t(v0 + u * nt) * VN, o);
+        }
     }
     for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt)
       y[i] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
@@ -385,6 +400,8 @@ static int fold_launch(uint64_t n, const void* in, void* out, void* ws, size_t w
 template <typename T>
 __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __restrict__ out, int vec_ok) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sv[32];
   __shared__ long long si[32];
   constexpr int VN = Vec16<T>::N;
@@ -404,10 +421,17 @@ argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __r
     };
     if (vec_ok) {
       const uint64_t nvec = n / VN;
-      for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
-        Vec16<T> t = ld16_stream(x + v * VN);
+      const uint64_t nt = blockDim.x;
+      for (uint64_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * nt) {      // four loads in flight per thread
+        Vec16<T> t[4];
 #pragma unroll
-        for (int e = 0; e < VN; ++e) consider(ElemTraits<T>::to_f(t.v[e]), (long long)(v * VN + e));
+        for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16_stream(x + (v0 + u * nt) * VN);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * nt < nvec) {
+#pragma unroll
+            for (int e = 0; e < VN; ++e) consider(ElemTraits<T>::to_f(t[u].v[e]), (long long)((v0 + u * nt) * VN + e));
+          }
       }
       for (uint64_t i = nvec * VN + threadIdx.x; i < n; i += blockDim.x)
         consider(ElemTraits<T>::to_f(x[i]), (long long)i);
@@ -449,8 +473,7 @@ static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cu
   const int vec_ok = aligned16(X) && (n % VN == 0);
   unsigned threads = n >= 32768 ? 1024 : (n >= 2048 ? 256 : 64);
   unsigned grid = unsigned(m < uint64_t(kNumSMs) * 8 ? m : uint64_t(kNumSMs) * 8);
-  argmax_rows_kernel<T><<<grid, threads, 0, st>>>(m, n, static_cast<const T*>(X), out, vec_ok);
-  return check_launch();
+  return launch_pdl(argmax_rows_kernel<T>, dim3(grid), dim3(threads), 0, st, m, n, static_cast<const T*>(X), out, vec_ok);
 }
 
 }  // namespace kuiops

@@ -102,7 +102,9 @@ class Decoder:
                 wqkv=torch.cat([shard_rows(wq, cfg.n_heads, hd), shard_rows(wk, cfg.n_kv_heads, hd),
                                 shard_rows(wv, cfg.n_kv_heads, hd)], 0).contiguous(),
                 wo=shard_in_features(wo, self.hq * hd, tp_rank),
-                wgu=torch.cat([shard_rows(wg, cfg.d_ff, 1), shard_rows(wu, cfg.d_ff, 1)], 0).contiguous(),
+                # gate and up rows interleaved (2j = gate_j, 2j + 1 = up_j): the layout of the fused
+                # GEMM + SwiGLU epilogue
+                wgu=torch.stack([shard_rows(wg, cfg.d_ff, 1), shard_rows(wu, cfg.d_ff, 1)], 1).reshape(2 * self.ff, d).contiguous(),
                 wd=shard_in_features(wd, self.ff, tp_rank),
                 n1=torch.ones(d, device=self.device, dtype=dt), n2=torch.ones(d, device=self.device, dtype=dt))
             del wq, wk, wv, wo, wg, wu, wd
@@ -160,7 +162,7 @@ class Decoder:
             _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4, kv_lens=kv_lens)
             o = self._allreduce(_ffi.gemm(attn, L["wo"], trans_b=True))
             h2 = _ffi.rmsnorm(o, L["n2"], cfg.eps, residual=resid)
-            act = _ffi.swiglu(_ffi.gemm(h2, L["wgu"], trans_b=True))
+            act = _ffi.gemm_swiglu(h2, L["wgu"])
             x = self._allreduce(_ffi.gemm(act, L["wd"], trans_b=True))
         self.length = end
         if last_only and seq > 1:

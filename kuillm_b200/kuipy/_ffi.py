@@ -50,11 +50,14 @@ SIGNATURES = {
     "kuiops_strerror": (ctypes.c_char_p, [c_int]),
     "kuiops_debug_tc_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
     "kuiops_launch_count": (c_u64, []),
+    "kuiops_set_pdl": (c_int, [c_int]),
     "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),
     "kuiops_gemm": (c_int, [c_int, c_int, c_u32, c_u32, c_u32, c_u32,
                             c_void_p, c_i64, c_i64, c_void_p, c_i64, c_i64, c_int,
                             c_void_p, c_i64, c_i64, c_float, c_float,
                             c_void_p, c_i64, c_i64, c_void_p, c_size_t, c_void_p]),
+    "kuiops_gemm_swiglu": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
+                                   c_void_p, c_size_t, c_void_p]),
     "kuiops_sdpa_workspace_bytes": (c_size_t, [c_int] + [c_u32] * 7),
     "kuiops_sdpa": (c_int, [c_int] + [c_u32] * 7 +
                     [c_void_p, c_i64, c_i64, c_i64] * 3 +
@@ -139,6 +142,11 @@ def strerror(code: int) -> str:
         return lib().kuiops_strerror(code).decode()
     except RuntimeError:
         return f"kuiops error {code}"
+
+
+def set_pdl(enabled: bool) -> bool:
+    """Turn programmatic dependent launch of the decode-path kernels on or off; returns the old setting."""
+    return bool(lib().kuiops_set_pdl(1 if enabled else 0))
 
 
 def launch_count() -> int:
@@ -244,6 +252,25 @@ def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dt
                          A.data_ptr(), lda, sa, B.data_ptr(), ldb, sb, 1 if trans_b else 0,
                          cin_p, ldcin, scin, float(alpha), float(beta),
                          out.data_ptr(), ldc, sc, ws.data_ptr(), ws.numel(), _stream()), "gemm")
+    return out
+
+
+def gemm_swiglu(A, W_interleaved, out=None):
+    """silu(A Wg^T) * (A Wu^T) with gate / up rows interleaved in W ([2N, K]); falls back to the
+    unfused pair of kernels where the tensor-core path does not apply."""
+    M, K = A.shape
+    N = W_interleaved.shape[0] // 2
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    L = lib()
+    rc = L.kuiops_gemm_swiglu(dtype_code(A.dtype), M, N, K, A.data_ptr(), max(A.stride(0), K), W_interleaved.data_ptr(),
+                              W_interleaved.stride(0), out.data_ptr(), max(out.stride(0), N), None, 0, _stream()) \
+        if A.dtype in (torch.bfloat16, torch.float16) and A.stride(1) == 1 and W_interleaved.stride(1) == 1 else EUNSUPPORTED
+    if rc == EUNSUPPORTED:
+        gu = gemm(A, W_interleaved, trans_b=True)                      # interleaved columns
+        g, u = gu[:, 0::2].contiguous(), gu[:, 1::2].contiguous()
+        return swiglu(torch.cat([g, u], 1), out=out)
+    _check(rc, "gemm_swiglu")
     return out
 
 

@@ -29,8 +29,8 @@ def _hf_twin(dec):
             H.self_attn.k_proj.weight.copy_(L["wqkv"][hq:hq + hk])
             H.self_attn.v_proj.weight.copy_(L["wqkv"][hq + hk:])
             H.self_attn.o_proj.weight.copy_(L["wo"])
-            H.mlp.gate_proj.weight.copy_(L["wgu"][:c.d_ff])
-            H.mlp.up_proj.weight.copy_(L["wgu"][c.d_ff:])
+            H.mlp.gate_proj.weight.copy_(L["wgu"][0::2])      # rows are interleaved gate, up, gate, up ...
+            H.mlp.up_proj.weight.copy_(L["wgu"][1::2])
             H.mlp.down_proj.weight.copy_(L["wd"])
             H.input_layernorm.weight.copy_(L["n1"])
             H.post_attention_layernorm.weight.copy_(L["n2"])

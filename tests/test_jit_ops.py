@@ -84,6 +84,22 @@ def test_mm_transposed_weight_view_is_used_in_place(cuda, gates, dtype):
     assert_close_ref_bar(out, O.mm(to_np(A), to_np(W).T), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 7, 32, 100, 300])
+def test_gemm_swiglu_fused_epilogue(cuda, dtype, M):
+    from kuipy import _ffi
+    N, K = 200, 136
+    A = randn(M, K, dtype=dtype)
+    Wg, Wu = (randn(N, K, dtype=dtype, seed=1) / K ** 0.5).to(dtype), (randn(N, K, dtype=dtype, seed=2) / K ** 0.5).to(dtype)
+    W = torch.stack([Wg, Wu], 1).reshape(2 * N, K).contiguous()
+    out = _ffi.gemm_swiglu(A, W)
+    g, u = O.mm(to_np(A), to_np(Wg).T), O.mm(to_np(A), to_np(Wu).T)
+    ref = g / (1.0 + np.exp(-g)) * u
+    assert out.shape == (M, N) and out.dtype == dtype
+    assert_close_ref_bar(out, ref, dtype)
+    assert _ffi.tc_error() == 0
+
+
 # ---- softmax / mean / folds / topk -----------------------------------------------------------------
 @pytest.mark.parametrize("dtype", FLOATS)
 @pytest.mark.parametrize("shape", [(128, 64), (8, 5, 33), (3, 4100), (2, 40000)])

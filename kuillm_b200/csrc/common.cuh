@@ -50,6 +50,31 @@ inline int launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
   return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
 }
 
+// Same, for a kernel whose CTAs form clusters of `cluster` along x (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+inline int launch_cluster_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              unsigned cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled.load(std::memory_order_relaxed) ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+}
+
+// 2^x by the special-function unit (relative error about 2^-22; results below 2^-126 become 0).
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {
   static __device__ __forceinline__ float to_f(float v) { return v; }

@@ -105,6 +105,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+  // normal placement only: 4 KB per epilogue warp to turn row-per-thread results into row-contiguous stores
+  unsigned char* epi_stage = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -227,7 +229,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
       float v[16];
       if (p.splits == 1) {
-        for (uint32_t c = 0; c < ncols; c += 16) {
+        uint32_t c = 0;
+        if (ACC_STAGES == 2 && p.epi == 0 && c_vec && (!p.Cin || (p.ldcin == 0 && cin_vec))) {
+          // 64 columns at a time: a thread owns one row of the accumulator, so direct stores would
+          // touch 32 rows per instruction.  The warp's 32 x 64 block goes through shared memory
+          // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and leaves as 128-byte
+          // row segments, four rows per store instruction.
+          unsigned char* stg = epi_stage + quarter * 4096;
+          TIN* cbase = static_cast<TIN*>(p.C) + size_t(b) * p.stride_c + col0;
+          for (; c + 64 <= ncols; c += 64) {
+            float w[64];
+            tc::tmem_ld32(taddr + c, w);
+            tc::tmem_ld32(taddr + c + 32, w + 32);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float add[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) add[e] = 0.f;
+              if (p.Cin) {
+                const Vec16<TIN> bv = ld16(static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin + col0 + c + j * 8);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) add[e] = p.beta * ElemTraits<TIN>::to_f(bv.v[e]);
+              }
+              Vec16<TIN> o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o.v[e] = ElemTraits<TIN>::from_f(fmaf(p.alpha, w[j * 8 + e], add[e]));
+              *reinterpret_cast<Vec16<TIN>*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t r = i * 4 + (lane >> 3), ch = lane & 7;
+              const Vec16<TIN> o = *reinterpret_cast<const Vec16<TIN>*>(stg + r * 128 + ((ch ^ (r & 7)) << 4));
+              const uint32_t grow = tp * TBM + quarter * 32 + r;
+              if (grow < p.M) st16(cbase + size_t(grow) * p.ldc + c + ch * 8, o);
+            }
+            __syncwarp();
+          }
+        }
+        for (; c < ncols; c += 16) {
           tc::tmem_ld16(taddr + c, v);
           tc::tmem_ld_wait();
           if (p.epi == 1) {
@@ -439,7 +480,9 @@ template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParams& p, unsigned grid, cudaStream_t st) {
   static_assert(size_t(BN) * TBM * sizeof(float) <= size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2),
                 "the split-K partial is parked in the pipeline buffers");
-  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256;
+  // pipeline stages + alignment slack + barriers + (normal placement) the epilogue's staging blocks
+  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256 + (ACC_STAGES == 2 ? 16384 : 0);
+  static_assert(smem <= 227 * 1024, "shared memory budget of one CTA");
   auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
   // the opt-in for large dynamic shared memory is per device: do it once per (kernel, device)
   static std::atomic<uint64_t> configured{0};

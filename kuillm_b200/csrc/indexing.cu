@@ -98,6 +98,152 @@ scatter_kernel(const __grid_constant__ CoordMap cm, const W* __restrict__ src, c
   }
 }
 
+// ---- row-local gather / scatter ---------------------------------------------------------
+// When the indexed axis is the innermost one, every cell that one row of the index addresses
+// lies in one dense row of the addressed tensor.  A CTA stages that row in shared memory, so the
+// random accesses never leave the SM and global memory only sees coalesced 16-byte traffic:
+// gather reads input row + index row and writes the output row; scatter reads self row + src row
+// + index row and writes the output row once (the separate clone of self disappears).
+// The staging buffer is shifted by the row's misalignment so that global and shared addresses
+// agree modulo 16 and the body of the row moves as 16-byte vectors.
+template <typename W>
+__device__ __forceinline__ W* stage_row_in(unsigned char* raw, const W* g, uint64_t count) {
+  const uint32_t shift = uint32_t(reinterpret_cast<uintptr_t>(g) & 15u);      // multiple of sizeof(W)
+  W* stage = reinterpret_cast<W*>(raw + shift);
+  constexpr uint32_t PER = 16 / sizeof(W);
+  const uint64_t head = shift ? min(uint64_t((16 - shift) / sizeof(W)), count) : 0;
+  const uint64_t nvec = (count - head) / PER;
+  for (uint64_t i = threadIdx.x; i < head; i += blockDim.x) stage[i] = g[i];
+  const int4* gv = reinterpret_cast<const int4*>(g + head);
+  int4* sv = reinterpret_cast<int4*>(stage + head);
+  for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) sv[v] = __ldcs(gv + v);
+  for (uint64_t i = head + nvec * PER + threadIdx.x; i < count; i += blockDim.x) stage[i] = g[i];
+  return stage;
+}
+template <typename W>
+__device__ __forceinline__ void stage_row_out(const W* stage, W* g, uint64_t count) {
+  // `stage` carries the misalignment of the row it was loaded from; vectors need the same one here
+  const uint32_t shift_g = uint32_t(reinterpret_cast<uintptr_t>(g) & 15u);
+  const uint32_t shift_s = uint32_t(__cvta_generic_to_shared(stage) & 15u);
+  if (shift_g != shift_s) {
+    for (uint64_t i = threadIdx.x; i < count; i += blockDim.x) g[i] = stage[i];
+    return;
+  }
+  constexpr uint32_t PER = 16 / sizeof(W);
+  const uint64_t head = shift_g ? min(uint64_t((16 - shift_g) / sizeof(W)), count) : 0;
+  const uint64_t nvec = (count - head) / PER;
+  for (uint64_t i = threadIdx.x; i < head; i += blockDim.x) g[i] = stage[i];
+  const int4* sv = reinterpret_cast<const int4*>(stage + head);
+  int4* gv = reinterpret_cast<int4*>(g + head);
+  for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) gv[v] = sv[v];
+  for (uint64_t i = head + nvec * PER + threadIdx.x; i < count; i += blockDim.x) g[i] = stage[i];
+}
+
+template <typename W>
+__global__ void __launch_bounds__(1024)
+gather_rows_kernel(uint64_t rows_w, uint64_t cols_w, uint64_t cols_f, const W* __restrict__ inp,
+                   const int64_t* __restrict__ idx, W* __restrict__ out, int32_t* status) {
+  extern __shared__ __align__(16) unsigned char stage_raw[];
+  for (uint64_t row = blockIdx.x; row < rows_w; row += gridDim.x) {
+    __syncthreads();                                   // the previous row's readers are done
+    const W* stage = stage_row_in(stage_raw, inp + row * cols_f, cols_f);
+    const int64_t* irow = idx + row * cols_w;
+    W* orow = out + row * cols_w;
+    __syncthreads();
+    const bool pairs = (reinterpret_cast<uintptr_t>(irow) & 15u) == 0;
+    const uint64_t npair = pairs ? cols_w / 2 : 0;
+    for (uint64_t q0 = threadIdx.x; q0 < npair; q0 += 4ull * blockDim.x) {       // four index loads in flight
+      int4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (q0 + u * blockDim.x < npair) raw[u] = __ldcs(reinterpret_cast<const int4*>(irow) + q0 + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint64_t q = q0 + u * blockDim.x;
+        if (q < npair) {
+          const long long* jj = reinterpret_cast<const long long*>(&raw[u]);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const long long j = jj[e];
+            if (j < 0 || uint64_t(j) >= cols_f) { if (status) atomicExch(status, 1); continue; }
+            orow[2 * q + e] = stage[j];
+          }
+        }
+      }
+    }
+    for (uint64_t c = npair * 2 + threadIdx.x; c < cols_w; c += blockDim.x) {
+      const int64_t j = irow[c];
+      if (j < 0 || uint64_t(j) >= cols_f) { if (status) atomicExch(status, 1); continue; }
+      orow[c] = stage[j];
+    }
+  }
+}
+
+template <typename W>
+__global__ void __launch_bounds__(1024)
+scatter_rows_kernel(uint64_t rows_f, uint64_t rows_w, uint64_t cols_w, uint64_t cols_f, const W* self_,
+                    const W* __restrict__ src, const int64_t* __restrict__ idx, W* out, int32_t* status) {
+  extern __shared__ __align__(16) unsigned char stage_raw[];
+  for (uint64_t row = blockIdx.x; row < rows_f; row += gridDim.x) {
+    __syncthreads();                                   // the previous row has been written out
+    W* stage = stage_row_in(stage_raw, self_ + row * cols_f, cols_f);
+    __syncthreads();
+    if (row < rows_w) {
+      const int64_t* irow = idx + row * cols_w;
+      const W* srow = src + row * cols_w;
+      for (uint64_t c0 = threadIdx.x; c0 < cols_w; c0 += 4ull * blockDim.x) {    // four loads of each in flight
+        int64_t j[4];
+        W v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint64_t c = c0 + u * blockDim.x;
+          if (c < cols_w) { j[u] = __ldcs(irow + c); v[u] = __ldcs(srow + c); }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint64_t c = c0 + u * blockDim.x;
+          if (c < cols_w) {
+            if (j[u] < 0 || uint64_t(j[u]) >= cols_f) { if (status) atomicExch(status, 1); continue; }
+            stage[j[u]] = v[u];
+          }
+        }
+      }
+      __syncthreads();
+    }
+    stage_row_out(stage, out + row * cols_f, cols_f);
+  }
+}
+
+// Launch geometry of the row-local kernels: as many CTAs per SM as shared memory and threads allow.
+struct RowsLaunch { unsigned grid, threads; size_t smem; bool ok; };
+static RowsLaunch rows_launch(uint64_t rows, uint64_t cols_f, uint32_t word) {
+  RowsLaunch r = {};
+  const uint64_t bytes = cols_f * word + 16;
+  r.ok = bytes <= 200 * 1024;
+  if (!r.ok) return r;
+  r.smem = size_t(bytes);
+  r.threads = bytes >= 64 * 1024 ? 1024 : (bytes >= 16 * 1024 ? 512 : 256);
+  uint64_t per_sm = (220 * 1024) / (bytes + 1024);
+  if (per_sm > 2048 / r.threads) per_sm = 2048 / r.threads;
+  if (per_sm < 1) per_sm = 1;
+  const uint64_t cap = uint64_t(kNumSMs) * per_sm;
+  r.grid = unsigned(rows < cap ? rows : cap);
+  return r;
+}
+// Dynamic shared memory above 48 KB needs an opt-in per kernel and device.
+template <typename K>
+static bool allow_smem(K kern, size_t bytes) {
+  static std::atomic<uint64_t> done{0};               // one per kernel type
+  if (bytes <= 48 * 1024) return true;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024 + 16) != cudaSuccess) return false;
+  done.fetch_or(bit, std::memory_order_release);
+  return true;
+}
+
 __global__ void __launch_bounds__(256)
 copy_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t bytes, int vec_ok) {
   const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
@@ -243,52 +389,84 @@ index_kernel(const __grid_constant__ IndexParams p, const W* __restrict__ self_,
 }
 
 // ---- isin -------------------------------------------------------------------------------
-// The test set is sorted in shared memory one tile at a time (bitonic, kIsinTile entries) and
-// every element does a binary search per tile.  A 1024-entry stop-id set is one tile.
-constexpr int kIsinTile = 4096;
+// The test set goes into an open-addressing hash table in shared memory (kIsinTile entries per
+// pass at load factor 1/2; a 1024-entry stop-id set is one pass) and every element probes it.
+// Elements are read two per 16-byte load and results written eight per store.
+constexpr int kIsinTile = 2048;
+constexpr int kIsinSlots = 2 * kIsinTile;
+constexpr unsigned long long kIsinEmpty = 0x8000000000000000ull;    // INT64_MIN marks a free slot
+
+__device__ __forceinline__ uint32_t isin_hash(unsigned long long v) {
+  return uint32_t((v * 0x9E3779B97F4A7C15ull) >> 52);               // 12 bits = kIsinSlots
+}
+__device__ __forceinline__ bool isin_probe(const unsigned long long* slots, bool has_empty_key, long long v) {
+  const unsigned long long u = static_cast<unsigned long long>(v);
+  if (u == kIsinEmpty) return has_empty_key;
+  uint32_t h = isin_hash(u);
+  for (int probes = 0; probes < kIsinSlots; ++probes) {             // ends at the first free slot
+    const unsigned long long sl = slots[h];
+    if (sl == u) return true;
+    if (sl == kIsinEmpty) return false;
+    h = (h + 1) & (kIsinSlots - 1);
+  }
+  return false;
+}
 
 __global__ void __launch_bounds__(512)
 isin_kernel(uint64_t n, const int64_t* __restrict__ elems, uint64_t m, const int64_t* __restrict__ tests, int invert,
-            uint8_t* __restrict__ out, uint64_t per_block) {
-  __shared__ long long tile[kIsinTile];
-  const uint64_t lo = uint64_t(blockIdx.x) * per_block;
+            uint8_t* __restrict__ out, uint64_t per_block, int vec_ok) {
+  __shared__ unsigned long long slots[kIsinSlots];
+  __shared__ int has_empty_key;
+  const uint64_t lo = uint64_t(blockIdx.x) * per_block;      // per_block is a multiple of 8
   const uint64_t hi = lo + per_block < n ? lo + per_block : n;
   if (lo >= n) return;
+  const uint8_t inv = invert ? 1 : 0;
   for (uint64_t t0 = 0; t0 < m; t0 += kIsinTile) {
     const uint32_t cnt = uint32_t(m - t0 < uint64_t(kIsinTile) ? m - t0 : uint64_t(kIsinTile));
-    uint32_t pow2 = 1;
-    while (pow2 < cnt) pow2 <<= 1;
+    const bool first = t0 == 0, last = t0 + kIsinTile >= m;
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < pow2; i += blockDim.x) tile[i] = i < cnt ? tests[t0 + i] : LLONG_MAX;
+    for (uint32_t i = threadIdx.x; i < uint32_t(kIsinSlots); i += blockDim.x) slots[i] = kIsinEmpty;
+    if (threadIdx.x == 0) has_empty_key = 0;
     __syncthreads();
-    for (uint32_t k = 2; k <= pow2; k <<= 1) {
-      for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-        for (uint32_t i = threadIdx.x; i < pow2; i += blockDim.x) {
-          const uint32_t l = i ^ j;
-          if (l > i) {
-            const long long a = tile[i], b = tile[l];
-            const bool up = (i & k) == 0;
-            if ((a > b) == up) { tile[i] = b; tile[l] = a; }
-          }
-        }
-        __syncthreads();
+    for (uint32_t i = threadIdx.x; i < cnt; i += blockDim.x) {
+      const unsigned long long u = static_cast<unsigned long long>(tests[t0 + i]);
+      if (u == kIsinEmpty) { has_empty_key = 1; continue; }
+      uint32_t h = isin_hash(u);
+      for (int probes = 0; probes < kIsinSlots; ++probes) {
+        const unsigned long long prev = atomicCAS(&slots[h], kIsinEmpty, u);
+        if (prev == kIsinEmpty || prev == u) break;
+        h = (h + 1) & (kIsinSlots - 1);
       }
     }
-    for (uint64_t e = lo + threadIdx.x; e < hi; e += blockDim.x) {
-      const long long v = elems[e];
-      uint32_t a = 0, b = cnt;       // first position with tile[pos] >= v
-      while (a < b) {
-        const uint32_t mid = (a + b) >> 1;
-        if (tile[mid] < v) a = mid + 1; else b = mid;
-      }
-      const bool hit = a < cnt && tile[a] == v;
-      if (t0 == 0) out[e] = hit ? 1 : 0;
-      else if (hit) out[e] = 1;
-    }
-  }
-  if (invert) {
     __syncthreads();
-    for (uint64_t e = lo + threadIdx.x; e < hi; e += blockDim.x) out[e] = out[e] ? 0 : 1;
+    const bool hek = has_empty_key != 0;
+    // out holds the running "found in an earlier pass" flag between passes; the last pass applies invert
+    auto finish = [&](bool hit, uint8_t prev) -> uint8_t {
+      const uint8_t f = (hit || (!first && prev)) ? 1 : 0;
+      return last ? uint8_t(f ^ inv) : f;
+    };
+    uint64_t e0 = lo;
+    if (vec_ok) {
+      const uint64_t groups = (hi - lo) / 8;
+      for (uint64_t g = threadIdx.x; g < groups; g += blockDim.x) {
+        const uint64_t e = lo + g * 8;
+        int4 raw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) raw[q] = __ldcs(reinterpret_cast<const int4*>(elems + e) + q);
+        const long long* v = reinterpret_cast<const long long*>(raw);
+        uint2 prev = make_uint2(0u, 0u);
+        if (!first) prev = *reinterpret_cast<const uint2*>(out + e);
+        const uint8_t* pb = reinterpret_cast<const uint8_t*>(&prev);
+        uint2 res;
+        uint8_t* rb = reinterpret_cast<uint8_t*>(&res);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) rb[q] = finish(isin_probe(slots, hek, v[q]), pb[q]);
+        *reinterpret_cast<uint2*>(out + e) = res;
+      }
+      e0 = lo + groups * 8;
+    }
+    for (uint64_t e = e0 + threadIdx.x; e < hi; e += blockDim.x)
+      out[e] = finish(isin_probe(slots, hek, elems[e]), first ? uint8_t(0) : out[e]);
   }
 }
 
@@ -315,6 +493,20 @@ int kuiops_gather(uint32_t elem_bytes, uint32_t rank, uint32_t dim, const uint64
   CoordMap cm;
   build_coord_map(rank, dim, idx_shape, inp_shape, cm);
   cudaStream_t st = as_stream(s);
+  // innermost-axis gather that takes a fair share of each input row: stage the row on chip
+  if (cm.dim_stride == 1 && (cm.rank == 1 || (cm.rank == 2 && cm.stride[0] == cm.dim_size))) {
+    const uint64_t rows_w = cm.rank == 2 ? cm.shape[0] : 1, cols_w = cm.shape[cm.rank - 1], cols_f = cm.dim_size;
+    const RowsLaunch rl = rows_launch(rows_w, cols_f, elem_bytes);
+    if (rl.ok && cols_w * 4 >= cols_f) {
+#define RCASE(B, WT)                                                                                          \
+  case B: if (!allow_smem(gather_rows_kernel<WT>, rl.smem)) return KUIOPS_ELAUNCH;                             \
+    gather_rows_kernel<WT><<<rl.grid, rl.threads, rl.smem, st>>>(rows_w, cols_w, cols_f, static_cast<const WT*>(inp), idx, \
+                                                                  static_cast<WT*>(out), status); break;
+      switch (elem_bytes) { RCASE(1, uint8_t) RCASE(2, uint16_t) RCASE(4, uint32_t) RCASE(8, uint64_t) }
+#undef RCASE
+      return check_launch();
+    }
+  }
   unsigned grid = stream_grid(n, 256 * 2, 16);
 #define ARGS cm, static_cast<const W*>(inp), idx, static_cast<W*>(out), n, status
   {
@@ -346,12 +538,27 @@ int kuiops_scatter(uint32_t elem_bytes, uint32_t rank, uint32_t dim, const uint6
   }
   if (numel == 0 || n != numel || total_addr == 0) return KUIOPS_EINVAL;
   cudaStream_t st = as_stream(s);
+  CoordMap cm;
+  build_coord_map(rank, dim, src_shape, self_shape, cm);
+  // innermost-axis scatter: clone and scatter row by row through shared memory, one pass
+  if (cm.dim_stride == 1 && (cm.rank == 1 || (cm.rank == 2 && cm.stride[0] == cm.dim_size))) {
+    const uint64_t rows_w = cm.rank == 2 ? cm.shape[0] : 1, cols_w = cm.shape[cm.rank - 1], cols_f = cm.dim_size;
+    const uint64_t rows_f = total_addr / cols_f;
+    const RowsLaunch rl = rows_launch(rows_f, cols_f, elem_bytes);
+    if (rl.ok) {
+#define RCASE(B, WT)                                                                                          \
+  case B: if (!allow_smem(scatter_rows_kernel<WT>, rl.smem)) return KUIOPS_ELAUNCH;                            \
+    scatter_rows_kernel<WT><<<rl.grid, rl.threads, rl.smem, st>>>(rows_f, rows_w, cols_w, cols_f,              \
+        static_cast<const WT*>(self_), static_cast<const WT*>(src), idx, static_cast<WT*>(out), status); break;
+      switch (elem_bytes) { RCASE(1, uint8_t) RCASE(2, uint16_t) RCASE(4, uint32_t) RCASE(8, uint64_t) }
+#undef RCASE
+      return check_launch();
+    }
+  }
   if (self_ != out) {
     int rc = copy_bytes(self_, out, total_addr * elem_bytes, st);
     if (rc != KUIOPS_OK) return rc;
   }
-  CoordMap cm;
-  build_coord_map(rank, dim, src_shape, self_shape, cm);
   unsigned grid = stream_grid(n, 256 * 2, 16);
 #define ARGS cm, static_cast<const W*>(src), idx, static_cast<W*>(out), n, status
   {
@@ -434,16 +641,21 @@ int kuiops_isin_i64(uint64_t n, const int64_t* elements, uint64_t m, const int64
                     void* out, kuiops_stream_t s) {
   if (n == 0 || !elements || !out) return KUIOPS_EINVAL;
   if (m > 0 && !test_elements) return KUIOPS_EINVAL;
-  // each block re-sorts the test set, so give a block enough elements to amortise that
-  uint64_t per_block = 2048;
+  // each block rebuilds the hash table, so give a block enough elements to amortise that
+  uint64_t per_block = 4096;
   uint64_t blocks = (n + per_block - 1) / per_block;
-  if (blocks > uint64_t(kNumSMs) * 4) { blocks = uint64_t(kNumSMs) * 4; per_block = (n + blocks - 1) / blocks; }
+  if (blocks > uint64_t(kNumSMs) * 8) {
+    blocks = uint64_t(kNumSMs) * 8;
+    per_block = ((n + blocks - 1) / blocks + 7) / 8 * 8;
+    blocks = (n + per_block - 1) / per_block;
+  }
   if (m == 0) {
     // empty test set: everything is "not in"
     return cudaMemsetAsync(out, invert ? 1 : 0, n, as_stream(s)) == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
   }
+  const int vec_ok = aligned16(elements) && (reinterpret_cast<uintptr_t>(out) % 8 == 0);
   isin_kernel<<<unsigned(blocks), 512, 0, as_stream(s)>>>(n, elements, m, test_elements, invert,
-                                                          static_cast<uint8_t*>(out), per_block);
+                                                          static_cast<uint8_t*>(out), per_block, vec_ok);
   return check_launch();
 }
 

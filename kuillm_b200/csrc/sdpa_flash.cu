@@ -5,11 +5,15 @@
 // two-slot TMA ring.  Per tile:
 //     S = Q K^T        UMMA 128 x 64 x 128, both operands K-major in shared memory, S in TMEM
 //     softmax          4 warps, one query row per thread: tcgen05.ld S, online max / sum in the
-//                      log2 domain in registers, P = exp2(S - m) written as bf16 into a K-major
-//                      128-byte-swizzled shared tile; the O accumulator in TMEM is rescaled only
-//                      when a row's running max grew by more than 2^8 (the stale max stays exact
-//                      because the final normalisation uses the same max)
-//     O += P V         UMMA 128 x 128 x 64, P K-major from shared memory, V MN-major as loaded
+//                      log2 domain in registers (3-input max, packed f32x2 FMA / add, ex2.approx,
+//                      four independent chains so the two resident warps per scheduler hide each
+//                      other's latencies); the O accumulator in TMEM is rescaled only when a row's
+//                      running max grew by more than 2^8 (the stale max stays exact because the
+//                      final normalisation uses the same max)
+//     P                bf16, either stored back into TMEM over the S buffer it came from (the
+//                      A operand of the next UMMA is then read from TMEM; no shared-memory round
+//                      trip, no proxy fence) or written into a K-major 128-byte-swizzled shared tile
+//     O += P V         UMMA 128 x 128 x 64, V MN-major as loaded
 // The CTA is small enough (112 KB of shared memory, 256 TMEM columns) for two CTAs per SM, so one
 // CTA's softmax overlaps the other's MMAs.  Epilogue: O / l to global, natural-log LSE.
 // This is the causal / grouped-query attention the dispatcher reaches as
@@ -18,6 +22,7 @@
 #include "sdpa.cuh"
 #include "tc_ptx.cuh"
 #include <type_traits>
+#include <cstdlib>
 
 namespace kuiops {
 
@@ -56,7 +61,29 @@ __device__ __forceinline__ bool flash_wait(uint64_t* bar, uint32_t parity) {
   return true;
 }
 
-template <typename T>
+__device__ __forceinline__ float f_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float f_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// (a0, a1) = (a0, a1) * s + c as one packed instruction
+__device__ __forceinline__ void f_fma2(float& a0, float& a1, float s, float c) {
+  asm("{.reg .b64 ra, rb, rc;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %2};\n mov.b64 rc, {%3, %3};\n"
+      " fma.rn.f32x2 ra, ra, rb, rc;\n mov.b64 {%0, %1}, ra;}"
+      : "+f"(a0), "+f"(a1) : "f"(s), "f"(c));
+}
+__device__ __forceinline__ void f_add2(float& a0, float& a1, float b0, float b1) {
+  asm("{.reg .b64 ra, rb;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n add.rn.f32x2 ra, ra, rb;\n mov.b64 {%0, %1}, ra;}"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+
+// PT: P is handed to the second UMMA through TMEM (over its own S buffer) instead of shared memory.
+template <typename T, bool PT>
 __global__ void __launch_bounds__(kFlashThreads, 2)
 sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
@@ -71,7 +98,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + F_Q_BYTES;                       // slot i: K at kv_s + i*32K, V right after K
   unsigned char* p_s = kv_s + 2 * (F_K_BYTES + F_V_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + F_P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + (PT ? 0u : F_P_BYTES));
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
@@ -170,7 +197,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t slot = j & 1, ph = (j >> 1) & 1;
         const uint32_t va = tc::smem_u32(kv_s + slot * (F_K_BYTES + F_V_BYTES)) + F_K_BYTES;
         // the next tile's scores are computed while the softmax warps work on this one; their S
-        // buffer was released when p_ready of tile j - 1 arrived
+        // buffer was released when p_ready of tile j - 1 arrived (and, when it holds P, the UMMA
+        // that reads P of tile j - 1 was issued before this one and the pipe runs in order)
         if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
         if (!flash_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
         if (!flash_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
@@ -178,9 +206,14 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, 1024);
           const uint64_t db = tc::make_smem_desc(va + kk * 2048, FBN * 128, 1024);
-          tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          if (PT) {
+            // 16 keys of bf16 P = 8 TMEM columns of the S buffer the softmax overwrote
+            tc::umma_f16_ts(tmem_O, tmem_S + slot * FBN + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, 1024);
+            tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         tc::umma_commit(&kv_empty[slot]);
         tc::umma_commit(o_done);
@@ -204,55 +237,89 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc::tmem_ld32(tmem_S + (j & 1) * FBN + lane_addr + 32, sv + 32);
       tc::tmem_ld_wait();
       const int64_t key0 = int64_t(j) * FBN;
-      const bool edge = key0 + FBN - 1 > row_lim;          // tile crosses this row's limit (or the end of the keys)
-      float mx = -INFINITY;
+      // tile crosses this row's limit (or the end of the keys): only the diagonal and last tiles
+      if (__any_sync(0xffffffffu, key0 + FBN - 1 > row_lim)) {
 #pragma unroll
-      for (int c = 0; c < FBN; ++c) {
-        if (edge && key0 + c > row_lim) sv[c] = -INFINITY;
-        mx = fmaxf(mx, sv[c]);
+        for (int c = 0; c < FBN; ++c)
+          if (key0 + c > row_lim) sv[c] = -INFINITY;
       }
-      mx *= p.scale_log2;                       // scale > 0: the max commutes with the scaling
+      float m0 = f_max3(sv[0], sv[1], sv[2]), m1 = f_max3(sv[3], sv[4], sv[5]);
+      float m2 = f_max3(sv[6], sv[7], sv[8]), m3 = f_max3(sv[9], sv[10], sv[11]);
+#pragma unroll
+      for (int c = 12; c + 8 <= FBN; c += 8) {
+        m0 = f_max3(m0, sv[c], sv[c + 1]);
+        m1 = f_max3(m1, sv[c + 2], sv[c + 3]);
+        m2 = f_max3(m2, sv[c + 4], sv[c + 5]);
+        m3 = f_max3(m3, sv[c + 6], sv[c + 7]);
+      }
+      // 12 + 8 * 6 = 60: the last four columns
+      m0 = f_max3(m0, sv[FBN - 4], sv[FBN - 3]);
+      m1 = f_max3(m1, sv[FBN - 2], sv[FBN - 1]);
+      float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;   // scale > 0: the max commutes with the scaling
       float corr = 1.f;
       if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
         const float m_new = fmaxf(mx, m_used);
         corr = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
         m_used = m_new;
       }
-      const float mm = (m_used == -INFINITY) ? 0.f : m_used;   // a fully masked row keeps p = 0
-      float rs = 0.f;
+      const float nmm = (m_used == -INFINITY) ? 0.f : -m_used;   // a fully masked row keeps p = 0
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < FBN; ++c) { sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -mm)); rs += sv[c]; }
-      l_run = l_run * corr + rs;
+      for (int c = 0; c < FBN; c += 4) {
+        f_fma2(sv[c], sv[c + 1], p.scale_log2, nmm);
+        f_fma2(sv[c + 2], sv[c + 3], p.scale_log2, nmm);
+        sv[c] = f_ex2(sv[c]);
+        sv[c + 1] = f_ex2(sv[c + 1]);
+        sv[c + 2] = f_ex2(sv[c + 2]);
+        sv[c + 3] = f_ex2(sv[c + 3]);
+        f_add2(r0, r1, sv[c], sv[c + 1]);
+        f_add2(r2, r3, sv[c + 2], sv[c + 3]);
+      }
+      l_run = l_run * corr + ((r0 + r1) + (r2 + r3));
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, corr != 1.f);
       if (j > 0) {
-        // the previous P V must be done before P's buffer is overwritten or O is touched
+        // The previous P V must be done before O is touched and, with P in shared memory, before
+        // P's buffer is overwritten.  It is waited for in every tile, also when nothing depends on
+        // it: a parity wait only tells the current phase of the barrier from the one before, so
+        // every phase has to be observed in turn.  The wait sits after this tile's exponentials,
+        // by which time that UMMA has normally completed.
         if (!flash_wait(o_done, (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
         tc::tc_fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
+      }
+      if (rescale) {
 #pragma unroll
-          for (int c0 = 0; c0 < FD; c0 += 32) {
-            float ov[32];
-            tc::tmem_ld32(tmem_O + lane_addr + c0, ov);
-            tc::tmem_ld_wait();
-            uint32_t ou[32];
+        for (int c0 = 0; c0 < FD; c0 += 16) {
+          float ov[16];
+          tc::tmem_ld16(tmem_O + lane_addr + c0, ov);
+          tc::tmem_ld_wait();
+          uint32_t ou[16];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) ou[c] = __float_as_uint(ov[c] * corr);
-            tc::tmem_st32(tmem_O + lane_addr + c0, ou);
-          }
-          tc::tmem_st_wait();
+          for (int c = 0; c < 16; ++c) ou[c] = __float_as_uint(ov[c] * corr);
+          tc::tmem_st16(tmem_O + lane_addr + c0, ou);
         }
+        tc::tmem_st_wait();
       }
-      // P row -> K-major 128-byte-swizzled tile: 16-byte chunk c of row r sits at chunk (c ^ (r & 7))
-      unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+      if (PT) {
+        // row r of P: bf16 pairs (key 2c, key 2c + 1) in column c of the S buffer this tile came from
+        uint32_t pk[FBN / 2];
 #pragma unroll
-      for (int c = 0; c < FBN / 8; ++c) {
-        uint4 pk;
-        pk.x = pack2<T>(sv[c * 8 + 0], sv[c * 8 + 1]);
-        pk.y = pack2<T>(sv[c * 8 + 2], sv[c * 8 + 3]);
-        pk.z = pack2<T>(sv[c * 8 + 4], sv[c * 8 + 5]);
-        pk.w = pack2<T>(sv[c * 8 + 6], sv[c * 8 + 7]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+        for (int c = 0; c < FBN / 2; ++c) pk[c] = pack2<T>(sv[2 * c], sv[2 * c + 1]);
+        tc::tmem_st32(tmem_S + (j & 1) * FBN + lane_addr, pk);
+        tc::tmem_st_wait();
+      } else {
+        // P row -> K-major 128-byte-swizzled tile: 16-byte chunk c of row r sits at chunk (c ^ (r & 7))
+        unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < FBN / 8; ++c) {
+          uint4 pk;
+          pk.x = pack2<T>(sv[c * 8 + 0], sv[c * 8 + 1]);
+          pk.y = pack2<T>(sv[c * 8 + 2], sv[c * 8 + 3]);
+          pk.z = pack2<T>(sv[c * 8 + 4], sv[c * 8 + 5]);
+          pk.w = pack2<T>(sv[c * 8 + 6], sv[c * 8 + 7]);
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+        }
+        tc::fence_proxy_async();          // make the generic-proxy writes visible to the UMMA (async proxy)
       }
-      tc::fence_proxy_async();          // make the generic-proxy writes visible to the UMMA (async proxy)
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(p_ready);
@@ -312,7 +379,7 @@ bool sdpa_flash_eligible(const SdpaArgs& a) {
   return ctas < (1ull << 31);
 }
 
-template <typename T>
+template <typename T, bool PT>
 static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   auto enc = [](CUtensorMap* m, const void* base, uint32_t rows, uint32_t heads, uint32_t n, int64_t s_row,
@@ -334,8 +401,8 @@ static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
   p.out = a.out; p.o_sn = a.o_sn; p.o_sh = a.o_sh; p.o_sl = a.o_sl; p.lse = a.lse;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
-  constexpr size_t smem = F_SMEM + 128;
-  auto kern = sdpa_flash_kernel<T>;
+  constexpr size_t smem = F_SMEM - (PT ? F_P_BYTES : 0u) + 128;
+  auto kern = sdpa_flash_kernel<T, PT>;
   static std::atomic<uint64_t> configured{0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
@@ -348,9 +415,22 @@ static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
   return launch_pdl(kern, dim3(grid), dim3(kFlashThreads), smem, st, mq, mk, mv, p);
 }
 
+// KUIOPS_FLASH_PTMEM=0 selects the variant that hands P to the tensor core through shared memory.
+static bool flash_p_in_tmem() {
+  static const bool v = [] {
+    const char* e = getenv("KUIOPS_FLASH_PTMEM");
+    return !(e && e[0] == '0');
+  }();
+  return v;
+}
+
 int sdpa_flash(const SdpaArgs& a, cudaStream_t st) {
-  if (a.dtype == KUIOPS_BF16) return flash_launch<__nv_bfloat16>(a, st);
-  return flash_launch<__half>(a, st);
+  if (flash_p_in_tmem()) {
+    if (a.dtype == KUIOPS_BF16) return flash_launch<__nv_bfloat16, true>(a, st);
+    return flash_launch<__half, true>(a, st);
+  }
+  if (a.dtype == KUIOPS_BF16) return flash_launch<__nv_bfloat16, false>(a, st);
+  return flash_launch<__half, false>(a, st);
 }
 
 }  // namespace kuiops

@@ -13,9 +13,10 @@ namespace kuiops {
 // handful of very long rows (64 x 128256 logits) still covers every SM.  Each CTA finds the max
 // of its slice, then the sum of exp(x - max); every CTA pushes its (max, sum) pair into the shared
 // memory of all its peers (distributed shared memory), one cluster barrier later each CTA combines
-// the pairs locally and writes exp(x - M) / S.  The slice is held in registers between the passes
-// when it fits (CACHE_VECS 16-byte vectors per thread), so HBM sees one read and one write; longer
-// slices are re-read (served by L2 when the matrix fits there).
+// the pairs locally and writes exp(x - M) / S.  A short slice is held in registers between the
+// passes (CACHE_VECS 16-byte vectors per thread), so HBM sees one read and one write; a long slice
+// is streamed once with a running (max, sum) per thread and read again for the write pass (served
+// by L2 when the matrix fits there).
 // Replaces Klas.RowSoftmax.inst_gpu, one block per row, in place
 // (kuiops/softmax/Kuiops.Softmax.Inst.fst.j2:10-11).
 // --------------------------------------------------------------------------------------
@@ -45,32 +46,30 @@ __device__ __forceinline__ float block_allreduce_sum(float v, float* red) {
   return t;
 }
 
-// Apply f to every element of the slice [lo, hi) of row x, four 16-byte loads in flight per thread.
-template <typename T, typename F>
-__device__ __forceinline__ void for_slice(const T* x, uint32_t lo, uint32_t hi, int vec_ok, F f) {
-  constexpr int VN = Vec16<T>::N;
-  const uint32_t tid = threadIdx.x, nt = blockDim.x;
-  if (vec_ok) {
-    const uint32_t nvec = (hi - lo) / VN;
-    for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
-      Vec16<T> t[4];
+// Running (max, sum of 2^((x - max) log2 e)) of one thread; merging a vector costs one extra ex2.
+struct OnlineMaxSum {
+  float m = -INFINITY, s = 0.f;
+  template <int VN>
+  __device__ __forceinline__ void add(const float (&v)[VN]) {
+    float vm = v[0];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+    for (int e = 1; e < VN; ++e) vm = fmaxf(vm, v[e]);
+    const float mn = fmaxf(m, vm);
+    const float nb = (mn == -INFINITY) ? 0.f : -mn * kLog2e;
+    float acc = s * fast_ex2(fmaf(m, kLog2e, nb));        // m = -inf: s is 0 and stays 0
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * nt < nvec) {
-#pragma unroll
-          for (int e = 0; e < VN; ++e) f(ElemTraits<T>::to_f(t[u].v[e]), lo + (v0 + u * nt) * VN + e);
-        }
-    }
-    for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt) f(ElemTraits<T>::to_f(x[i]), i);
-  } else {
-    for (uint32_t i = lo + tid; i < hi; i += nt) f(ElemTraits<T>::to_f(x[i]), i);
+    for (int e = 0; e < VN; ++e) acc += fast_ex2(fmaf(v[e], kLog2e, nb));
+    s = acc;
+    m = mn;
   }
-}
+  __device__ __forceinline__ void add1(float v) {
+    const float one[1] = {v};
+    add<1>(one);
+  }
+};
 
 template <typename T, int CACHE_VECS>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
                     uint32_t cluster_ctas, int vec_ok) {
   constexpr int VN = Vec16<T>::N;
@@ -82,6 +81,8 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
   const uint32_t row = blockIdx.x / cluster_ctas;
   // peers must be running before their shared memory is written; arrive now, wait just before the push
   if (cluster_ctas > 1) cluster.barrier_arrive();
+  pdl_wait();
+  pdl_trigger();
   // slice boundaries in elements, multiples of VN so vector accesses stay aligned
   const uint32_t nv_total = (n + VN - 1) / VN;
   const uint32_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
@@ -92,10 +93,12 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
   const uint32_t tid = threadIdx.x, nt = blockDim.x;
   const uint32_t nvec = (hi - lo) / VN;
 
-  // ---- pass 1: slice max (the slice stays in registers when it fits) ------------------------
+  // ---- slice statistics: (max, sum of exp(x - max)) ------------------------------------------
   Vec16<T> cache[CACHE_VECS > 0 ? CACHE_VECS : 1];
-  float mx = -INFINITY;
+  float bm, bs;
   if (CACHE_VECS > 0) {
+    // short slice: it stays in registers, so the max and the sum are two passes over registers
+    float mx = -INFINITY;
 #pragma unroll
     for (int c = 0; c < CACHE_VECS; ++c)
       if (tid + c * nt < nvec) cache[c] = ld16_stream(x + lo + size_t(tid + c * nt) * VN);
@@ -105,24 +108,42 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
 #pragma unroll
         for (int e = 0; e < VN; ++e) mx = fmaxf(mx, ElemTraits<T>::to_f(cache[c].v[e]));
       }
-  } else {
-    for_slice(x, lo, hi, vec_ok, [&](float v, uint32_t) { mx = fmaxf(mx, v); });
-  }
-  const float bm = block_allreduce_max(mx, red);
-  // ---- pass 2: sum of exp(x - slice max) ------------------------------------------------------
-  const float nb = (bm == -INFINITY) ? 0.f : -bm * kLog2e;
-  float sm = 0.f;
-  if (CACHE_VECS > 0) {
+    bm = block_allreduce_max(mx, red);
+    const float nb = (bm == -INFINITY) ? 0.f : -bm * kLog2e;
+    float sm = 0.f;
 #pragma unroll
     for (int c = 0; c < CACHE_VECS; ++c)
       if (tid + c * nt < nvec) {
 #pragma unroll
-        for (int e = 0; e < VN; ++e) sm += exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, nb));
+        for (int e = 0; e < VN; ++e) sm += fast_ex2(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, nb));
       }
+    bs = block_allreduce_sum(sm, red);
   } else {
-    for_slice(x, lo, hi, vec_ok, [&](float v, uint32_t) { sm += exp2f(fmaf(v, kLog2e, nb)); });
+    // long slice: one streaming pass with a running (max, sum) per thread; the write pass below
+    // reads the slice again (from L2 when the matrix fits there)
+    OnlineMaxSum st;
+    if (vec_ok) {
+      for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
+        Vec16<T> t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * nt < nvec) {
+            float f[VN];
+#pragma unroll
+            for (int e = 0; e < VN; ++e) f[e] = ElemTraits<T>::to_f(t[u].v[e]);
+            st.add<VN>(f);
+          }
+      }
+      for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt) st.add1(ElemTraits<T>::to_f(x[i]));
+    } else {
+      for (uint32_t i = lo + tid; i < hi; i += nt) st.add1(ElemTraits<T>::to_f(x[i]));
+    }
+    bm = block_allreduce_max(st.m, red);
+    const float nb = (bm == -INFINITY) ? 0.f : -bm * kLog2e;
+    bs = block_allreduce_sum(st.s * fast_ex2(fmaf(st.m, kLog2e, nb)), red);
   }
-  const float bs = block_allreduce_sum(sm, red);
   // ---- exchange: push this CTA's pair into every peer, one cluster barrier, read locally ------
   float M = bm, S = bs;
   if (cluster_ctas > 1) {
@@ -138,7 +159,7 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
     for (uint32_t r = 0; r < cluster_ctas; ++r)
       if (pairs[r].m != -INFINITY) S += pairs[r].s * exp2f((pairs[r].m - M) * kLog2e);
   }
-  // ---- pass 3: write exp(x - M) / S -------------------------------------------------------------
+  // ---- write exp(x - M) / S -------------------------------------------------------------------
   const float inv = 1.f / S;
   const float mb = -M * kLog2e;
   if (CACHE_VECS > 0) {
@@ -148,7 +169,7 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
         Vec16<T> o;
 #pragma unroll
         for (int e = 0; e < VN; ++e)
-          o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, mb)) * inv);
+          o.v[e] = ElemTraits<T>::from_f(fast_ex2(fmaf(ElemTraits<T>::to_f(cache[c].v[e]), kLog2e, mb)) * inv);
         st16(y + lo + size_t(tid + c * nt) * VN, o);
       }
   } else if (vec_ok) {
@@ -161,15 +182,15 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
         if (v0 + u * nt < nvec) {
           Vec16<T> o;
 #pragma unroll
-          for (int e = 0; e < VN; ++e) o.v[e] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(t[u].v[e]), kLog2e, mb)) * inv);
+          for (int e = 0; e < VN; ++e) o.v[e] = ElemTraits<T>::from_f(fast_ex2(fmaf(ElemTraits<T>::to_f(t[u].v[e]), kLog2e, mb)) * inv);
           st16(y + lo + size_t(v0 + u * nt) * VN, o);
         }
     }
     for (uint32_t i = lo + nvec * VN + tid; i < hi; i += nt)
-      y[i] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
+      y[i] = ElemTraits<T>::from_f(fast_ex2(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
   } else {
     for (uint32_t i = lo + tid; i < hi; i += nt)
-      y[i] = ElemTraits<T>::from_f(exp2f(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
+      y[i] = ElemTraits<T>::from_f(fast_ex2(fmaf(ElemTraits<T>::to_f(x[i]), kLog2e, mb)) * inv);
   }
 }
 
@@ -183,29 +204,20 @@ static int softmax_launch(uint32_t m, uint32_t n, const void* X, void* Y, cudaSt
   // cluster width: enough CTAs to cover the SMs when rows are few and long
   uint32_t c = 1;
   while (c < 8 && uint64_t(m) * c < 2 * kNumSMs && n / (c * 2) >= 8192) c *= 2;
-  const uint32_t slice = (n + c - 1) / c;
-  uint32_t threads = (slice / VN + 3) / 4;             // ~4 vectors per thread
-  threads = ((threads + 31) / 32) * 32;
-  if (threads < 32) threads = 32;
-  if (threads > 1024) threads = 1024;
   const uint32_t nv_per = ((n + VN - 1) / VN + c - 1) / c;   // vectors per CTA slice
-  const bool cached = vec_ok && nv_per <= threads * 4;
-
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(m * c);
-  cfg.blockDim = dim3(threads);
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = c; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  // A slice of up to 4 vectors per thread of a 256-thread CTA is kept in registers.  Longer slices
+  // are streamed twice by 256-thread CTAs: small CTAs with few registers are all resident at once
+  // (a 64 x 128256 matrix is 512 CTAs, three or four per SM), where 1024-thread CTAs that cache
+  // their slice would run in several waves.
+  uint32_t threads = ((nv_per + 3) / 4 + 31) / 32 * 32;
+  if (threads < 32) threads = 32;
+  const bool cached = vec_ok && threads <= 256;
+  if (!cached) threads = 256;
   const T* x = static_cast<const T*>(X);
   T* y = static_cast<T*>(Y);
-  cudaError_t e = cached
-      ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<T, 4>, m, n, x, y, c, vec_ok)
-      : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<T, 0>, m, n, x, y, c, vec_ok);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+  return cached
+      ? launch_cluster_pdl(softmax_rows_kernel<T, 4>, dim3(m * c), dim3(threads), 0, st, c, m, n, x, y, c, vec_ok)
+      : launch_cluster_pdl(softmax_rows_kernel<T, 0>, dim3(m * c), dim3(threads), 0, st, c, m, n, x, y, c, vec_ok);
 }
 
 // --------------------------------------------------------------------------------------
@@ -397,83 +409,115 @@ static int fold_launch(uint64_t n, const void* in, void* out, void* ws, size_t w
 // --------------------------------------------------------------------------------------
 // Row arg-max (greedy sampling over the vocabulary), ties to the lowest index.
 // --------------------------------------------------------------------------------------
+// Candidate of one thread / warp / CTA: the value and its index inside the row.
+struct ArgBest {
+  float v;
+  long long i;     // LLONG_MAX: nothing seen yet
+};
+// NaN counts as the maximum, as in torch.argmax; equal values (and -0 / +0) keep the lowest index.
+__device__ __forceinline__ void arg_consider(ArgBest& b, float v, long long i) {
+  if (i == LLONG_MAX) return;
+  const bool vnan = v != v, bnan = b.v != b.v;
+  bool better;
+  if (b.i == LLONG_MAX) better = true;
+  else if (vnan != bnan) better = vnan;
+  else if (vnan) better = i < b.i;
+  else better = v > b.v || (v == b.v && i < b.i);
+  if (better) { b.v = v; b.i = i; }
+}
+
+// A row is split over the CTAs of a cluster (1..8) so that a few long rows still cover the SMs;
+// every CTA pushes its candidate into the leader's shared memory and the leader picks.
 template <typename T>
-__global__ void __launch_bounds__(1024)
-argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __restrict__ out, int vec_ok) {
-  pdl_wait();
-  pdl_trigger();
+__global__ void __launch_bounds__(512)
+argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __restrict__ out, int vec_ok,
+                   uint32_t cluster_ctas) {
   __shared__ float sv[32];
   __shared__ long long si[32];
+  __shared__ ArgBest parts[8];
   constexpr int VN = Vec16<T>::N;
-  for (uint64_t row = blockIdx.x; row < m; row += gridDim.x) {
-    const T* x = X + row * n;
-    float bv = -INFINITY;
-    long long bi = LLONG_MAX;
-    auto consider = [&](float v, long long i) {
-      // NaN counts as the maximum, as in torch.argmax; equal keys keep the lowest index
-      const bool vnan = v != v, bnan = bv != bv;
-      bool better;
-      if (bi == LLONG_MAX) better = true;
-      else if (vnan != bnan) better = vnan;
-      else if (vnan) better = i < bi;
-      else better = v > bv || (v == bv && i < bi);
-      if (better) { bv = v; bi = i; }
-    };
-    if (vec_ok) {
-      const uint64_t nvec = n / VN;
-      const uint64_t nt = blockDim.x;
-      for (uint64_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * nt) {      // four loads in flight per thread
-        Vec16<T> t[4];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
+  if (cluster_ctas > 1) cluster.barrier_arrive();      // peers are running before their memory is written
+  pdl_wait();
+  pdl_trigger();
+  const uint64_t row = blockIdx.x / cluster_ctas;      // grid = m * cluster_ctas
+  const T* x = X + row * n;
+  // slice of this CTA in whole vectors
+  const uint64_t nv_total = (n + VN - 1) / VN;
+  const uint64_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
+  const uint64_t lo = min(uint64_t(part) * nv_per * VN, n), hi = min(lo + nv_per * VN, n);
+  ArgBest best{-INFINITY, LLONG_MAX};
+  // The hot loop only asks "is v above the running value, or is either a NaN"; the full rule runs
+  // on the few elements that pass.  A thread meets its elements in index order, so a later equal
+  // value never replaces an earlier one.
+  auto scan = [&](float v, long long i) {
+    if (!(v <= best.v) || best.i == LLONG_MAX) arg_consider(best, v, i);
+  };
+  if (vec_ok) {
+    const uint64_t nvec = (hi - lo) / VN;
+    const uint64_t nt = blockDim.x;
+    for (uint64_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * nt) {      // four loads in flight per thread
+      Vec16<T> t[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16_stream(x + (v0 + u * nt) * VN);
+      for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16_stream(x + lo + (v0 + u * nt) * VN);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (v0 + u * nt < nvec) {
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * nt < nvec) {
 #pragma unroll
-            for (int e = 0; e < VN; ++e) consider(ElemTraits<T>::to_f(t[u].v[e]), (long long)((v0 + u * nt) * VN + e));
-          }
-      }
-      for (uint64_t i = nvec * VN + threadIdx.x; i < n; i += blockDim.x)
-        consider(ElemTraits<T>::to_f(x[i]), (long long)i);
-    } else {
-      for (uint64_t i = threadIdx.x; i < n; i += blockDim.x) consider(ElemTraits<T>::to_f(x[i]), (long long)i);
+          for (int e = 0; e < VN; ++e) scan(ElemTraits<T>::to_f(t[u].v[e]), (long long)(lo + (v0 + u * nt) * VN + e));
+        }
     }
-    auto merge = [&](float ov, long long oi) {
-      if (oi == LLONG_MAX) return;
-      consider(ov, oi);
-    };
+    for (uint64_t i = lo + nvec * VN + threadIdx.x; i < hi; i += blockDim.x)
+      arg_consider(best, ElemTraits<T>::to_f(x[i]), (long long)i);
+  } else {
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) arg_consider(best, ElemTraits<T>::to_f(x[i]), (long long)i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
+    const long long oi = __shfl_xor_sync(0xffffffffu, best.i, o);
+    arg_consider(best, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) { sv[w] = best.v; si[w] = best.i; }
+  __syncthreads();
+  if (w == 0) {
+    best.v = lane < nw ? sv[lane] : -INFINITY;
+    best.i = lane < nw ? si[lane] : LLONG_MAX;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      merge(ov, oi);
+      const float ov = __shfl_xor_sync(0xffffffffu, best.v, o);
+      const long long oi = __shfl_xor_sync(0xffffffffu, best.i, o);
+      arg_consider(best, ov, oi);
     }
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (lane == 0) { sv[w] = bv; si[w] = bi; }
-    __syncthreads();
-    if (w == 0) {
-      bv = lane < nw ? sv[lane] : -INFINITY;
-      bi = lane < nw ? si[lane] : LLONG_MAX;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        merge(ov, oi);
-      }
-      if (lane == 0) out[row] = bi;
-    }
+  }
+  if (cluster_ctas == 1) {
+    if (threadIdx.x == 0) out[row] = best.i;
+    return;
+  }
+  cluster.barrier_wait();
+  if (threadIdx.x == 0) cluster.map_shared_rank(parts, 0)[part] = best;
+  cluster.sync();
+  if (part == 0 && threadIdx.x == 0) {
+    ArgBest b = parts[0];
+    for (uint32_t r = 1; r < cluster_ctas; ++r) arg_consider(b, parts[r].v, parts[r].i);
+    out[row] = b.i;
   }
 }
 
 template <typename T>
 static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cudaStream_t st) {
   if (m == 0 || n == 0 || !X || !out) return KUIOPS_EINVAL;
+  if (m > 0x7FFFFFFFull / 8) return KUIOPS_ELIMIT;
   constexpr int VN = Vec16<T>::N;
   const int vec_ok = aligned16(X) && (n % VN == 0);
-  unsigned threads = n >= 32768 ? 1024 : (n >= 2048 ? 256 : 64);
-  unsigned grid = unsigned(m < uint64_t(kNumSMs) * 8 ? m : uint64_t(kNumSMs) * 8);
-  return launch_pdl(argmax_rows_kernel<T>, dim3(grid), dim3(threads), 0, st, m, n, static_cast<const T*>(X), out, vec_ok);
+  unsigned threads = n >= 16384 ? 512 : (n >= 2048 ? 256 : 64);
+  // cluster width: enough CTAs to give every SM two when rows are few and long
+  uint32_t c = 1;
+  while (c < 8 && m * c < 2 * uint64_t(kNumSMs) && n / (c * 2) >= 8192) c *= 2;
+  return launch_cluster_pdl(argmax_rows_kernel<T>, dim3(unsigned(m * c)), dim3(threads), 0, st, c, m, n,
+                            static_cast<const T*>(X), out, vec_ok, c);
 }
 
 }  // namespace kuiops

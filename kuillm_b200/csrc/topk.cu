@@ -10,6 +10,14 @@
 // among equal values) and writes it.  HBM sees the row once; the second pass is served by L2.
 // When the threshold bin holds more than kCandMax elements (for example a constant row) the
 // leader finishes the row alone with two more radix passes and an index-ordered tie pick.
+//
+// Small k (the sampling case, k = 50 of 128256) takes a cheaper first pass, topk_sel_kernel:
+// the histogram is built from one key per thread, the largest of the elements the thread read.
+// The k-th largest of those thread maxima is a lower bound of the k-th largest element (they are
+// k distinct elements), so every element of the answer lies in a bin at or above the bin of that
+// bound; the second pass collects exactly those elements (a few more than k) and the leader sorts
+// them.  This keeps the radix-select structure but takes the shared-memory atomics, which
+// serialise when most keys fall into a handful of exponent bins, out of the streaming pass.
 #include "common.cuh"
 #include <cooperative_groups.h>
 
@@ -23,7 +31,7 @@ constexpr int kTopkMaxK = 2048;
 
 __device__ __forceinline__ uint32_t key_of(float v) {
   if (v != v) return 0xFFFFFFFFu;
-  uint32_t u = __float_as_uint(v);
+  uint32_t u = __float_as_uint(v + 0.f);       // -0 and +0 compare equal: both take the key of +0
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 // (key, index) packed so that a descending sort yields value-descending, index-ascending
@@ -192,6 +200,8 @@ topk_rows_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X
   for (int i = tid; i < kBins; i += blockDim.x) sh.hist[i] = 0;
   if (tid == 0) { sh.sel_cnt = 0; sh.cand_cnt = 0; sh.bin = 0; sh.need = 0; sh.bin_cnt = 0; }
   __syncthreads();
+  pdl_wait();
+  pdl_trigger();
 
   // ---- pass 1: histogram of the top 11 key bits over the slice -------------------------
   // (uniform trip counts: hist_add is warp-collective; four 16-byte loads in flight per thread)
@@ -307,6 +317,141 @@ topk_rows_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X
   }
 }
 
+// Exact top-k of a whole row by one CTA (1024 threads), reading global memory: the fall-back of
+// topk_sel_kernel when its candidate list overflows.  Leaves the unsorted answer in sh.sel.
+__device__ void topk_row_single_cta(TopkShared& sh, const float* __restrict__ x, uint32_t n, uint32_t k) {
+  const int tid = threadIdx.x;
+  for (int i = tid; i < kBins; i += blockDim.x) sh.hist[i] = 0;
+  if (tid == 0) { sh.sel_cnt = 0; sh.cand_cnt = 0; sh.bin = 0; sh.need = 0; sh.bin_cnt = 0; }
+  __syncthreads();
+  for (uint32_t i = tid; i < n; i += blockDim.x) atomicAdd(&sh.hist[key_of(x[i]) >> 21], 1u);
+  __syncthreads();
+  find_threshold_bin(sh, k);
+  const uint32_t bin = sh.bin;
+  const bool fits = sh.bin_cnt <= uint32_t(kCandMax);
+  for (uint32_t i = tid; i < n; i += blockDim.x) {
+    const uint32_t key = key_of(x[i]), b = key >> 21;
+    if (b > bin) {
+      const uint32_t pos = atomicAdd(&sh.sel_cnt, 1u);
+      if (pos < k) sh.sel[pos] = pack(key, i);
+    } else if (fits && b == bin) {
+      const uint32_t pos = atomicAdd(&sh.cand_cnt, 1u);
+      if (pos < uint32_t(kCandMax)) sh.cand[pos] = pack(key, i);
+    }
+  }
+  __syncthreads();
+  if (fits) {
+    const uint32_t need = sh.need, base = sh.sel_cnt;
+    sort_desc(sh.cand, min(sh.cand_cnt, uint32_t(kCandMax)));
+    for (uint32_t i = tid; i < need; i += blockDim.x)
+      if (base + i < k) sh.sel[base + i] = sh.cand[i];
+    __syncthreads();
+  } else {
+    finish_row_slow(sh, x, n, k);
+  }
+}
+
+__global__ void __launch_bounds__(kTopkThreads)
+topk_sel_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X, float* __restrict__ values,
+                int64_t* __restrict__ indices, uint32_t cluster_ctas) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  TopkShared& sh = *reinterpret_cast<TopkShared*>(smem_raw);
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
+  const uint32_t row = blockIdx.x / cluster_ctas;
+  const bool leader = part == 0;
+  TopkShared* lead = cluster_ctas > 1 ? cluster.map_shared_rank(&sh, 0) : &sh;
+  const int tid = threadIdx.x;
+  const float* x = X + size_t(row) * n;
+  const uint32_t nv_total = (n + 3) / 4;
+  const uint32_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
+  const uint32_t lo = min(part * nv_per * 4, n), hi = min(lo + nv_per * 4, n);
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  const uint32_t nvec = vec_ok ? (hi - lo) / 4 : 0;
+  const uint32_t nt = blockDim.x;
+
+  for (int i = tid; i < kBins; i += blockDim.x) sh.hist[i] = 0;
+  if (tid == 0) { sh.sel_cnt = 0; sh.cand_cnt = 0; sh.bin = 0; sh.need = 0; sh.bin_cnt = 0; }
+  __syncthreads();
+  pdl_wait();
+  pdl_trigger();
+
+  // ---- pass 1: the largest key each thread meets (no atomics in the stream) -------------------
+  uint32_t kmax = 0;                          // 0 is the key of no value: "this thread saw nothing"
+  for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
+    float4 f[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      f[u] = (v0 + u * nt < nvec) ? __ldcs(reinterpret_cast<const float4*>(x + lo + size_t(v0 + u * nt) * 4))
+                                  : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (v0 + u * nt < nvec)
+        kmax = max(max(kmax, max(key_of(f[u].x), key_of(f[u].y))), max(key_of(f[u].z), key_of(f[u].w)));
+  }
+  for (uint32_t i = lo + nvec * 4 + tid; i < hi; i += nt) kmax = max(kmax, key_of(x[i]));
+  {
+    // one histogram entry per thread, duplicates inside a warp combined first
+    const uint32_t b = kmax >> 21;
+    const uint32_t peers = __match_any_sync(0xffffffffu, kmax ? b : 0xFFFFFFFFu);
+    if (kmax && (tid & 31) == __ffs(peers) - 1) atomicAdd(&sh.hist[b], uint32_t(__popc(peers)));
+  }
+  __syncthreads();
+  if (cluster_ctas > 1) {
+    cluster.sync();                        // the leader's histogram is initialised and filled
+    if (!leader) {
+      for (int i = tid; i < kBins; i += blockDim.x) {
+        const uint32_t c = sh.hist[i];
+        if (c) atomicAdd(&lead->hist[i], c);
+      }
+    }
+    cluster.sync();
+  }
+  if (leader) find_threshold_bin(sh, k);   // fewer than k thread maxima: bin stays 0, everything is a candidate
+  if (cluster_ctas > 1) cluster.sync();
+  const uint32_t bin = lead->bin;
+
+  // ---- pass 2 (served by L2): every element at or above the bound's bin goes to the leader ----
+  auto route = [&](float v, uint32_t i) {
+    const uint32_t key = key_of(v);
+    if ((key >> 21) >= bin) {
+      const uint32_t pos = atomicAdd(&lead->cand_cnt, 1u);
+      if (pos < uint32_t(kCandMax)) lead->cand[pos] = pack(key, i);
+    }
+  };
+  for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
+    float4 f[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (v0 + u * nt < nvec) f[u] = *reinterpret_cast<const float4*>(x + lo + size_t(v0 + u * nt) * 4);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (v0 + u * nt < nvec) {
+        const uint32_t i0 = lo + (v0 + u * nt) * 4;
+        route(f[u].x, i0); route(f[u].y, i0 + 1); route(f[u].z, i0 + 2); route(f[u].w, i0 + 3);
+      }
+  }
+  for (uint32_t i = lo + nvec * 4 + tid; i < hi; i += nt) route(x[i], i);
+  if (cluster_ctas > 1) cluster.sync();    // all remote writes landed; followers may leave
+  if (!leader) return;
+  __syncthreads();
+
+  const uint32_t cnt = sh.cand_cnt;
+  const unsigned long long* res = sh.cand;
+  if (cnt <= uint32_t(kCandMax) && cnt >= k) {
+    sort_desc(sh.cand, cnt);               // key descending, index ascending among equal keys
+  } else {
+    topk_row_single_cta(sh, x, n, k);
+    sort_desc(sh.sel, k);
+    res = sh.sel;
+  }
+  for (uint32_t i = tid; i < k; i += blockDim.x) {
+    const uint32_t idx = ~uint32_t(res[i] & 0xFFFFFFFFull);
+    values[size_t(row) * k + i] = x[idx];
+    indices[size_t(row) * k + i] = int64_t(idx);
+  }
+}
+
 }  // namespace kuiops
 
 using namespace kuiops;
@@ -320,17 +465,10 @@ extern "C" int kuiops_topk_f32(uint32_t m, uint32_t n, uint32_t k, const void* X
   uint32_t c = 1;
   while (c < 4 && uint64_t(m) * c * 2 <= uint64_t(kNumSMs) && n / (c * 2) >= 16384) c *= 2;
   const size_t smem = sizeof(TopkShared);   // ~41 KB, below the 48 KB that needs no opt-in
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(m * c);
-  cfg.blockDim = dim3(kTopkThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = as_stream(s);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = c; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_rows_kernel, m, n, k, static_cast<const float*>(X),
-                                     static_cast<float*>(values), indices, c);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return e == cudaSuccess ? KUIOPS_OK : KUIOPS_ELAUNCH;
+  // few results per row: the thread-maxima bound is tight (the row has 1024 c thread maxima)
+  if (k * 8 <= 1024 * c)
+    return launch_cluster_pdl(topk_sel_kernel, dim3(m * c), dim3(kTopkThreads), smem, as_stream(s), c, m, n, k,
+                              static_cast<const float*>(X), static_cast<float*>(values), indices, c);
+  return launch_cluster_pdl(topk_rows_kernel, dim3(m * c), dim3(kTopkThreads), smem, as_stream(s), c, m, n, k,
+                            static_cast<const float*>(X), static_cast<float*>(values), indices, c);
 }

@@ -1,6 +1,6 @@
 """Per-operator roofline table at the benchmark configurations.
 
-    python -m kuillm_b200.opbench [--only gemm,sdpa,stream,index] [--iters 20] [--out file.jsonl]
+    python -m kuillm_b200.opbench [--only gemm,sdpa,stream,index,decode] [--iters 20] [--out file.jsonl]
 
 Each line: op, shape, microseconds per launch (CUDA events on the launching stream, after
 warm-up), the algorithmic bytes or flops of one launch, the achieved rate and its fraction of
@@ -125,6 +125,16 @@ def bench_stream(T, iters):
             del ps
         T.add("argmax_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.argmax_lastdim(xs[i]), nv, iters)), bytes_=m * n * 4)
         del xs
+    if wanted("argmax_bf16", "32x128256"):
+        nv = variants_for(32 * n * 2)
+        lb = [torch.randn(32, n, device=dev).bfloat16() for _ in range(nv)]
+        T.add("argmax_bf16", f"32x{n}", (lambda: time_us(lambda i: _ffi.argmax_lastdim(lb[i]), nv, iters)), bytes_=32 * n * 2)
+        del lb
+    if wanted("softmax_f32", "4096x32768"):
+        big = [torch.randn(4096, 32768, device=dev) for _ in range(2)]
+        yb2 = torch.empty_like(big[0])
+        T.add("softmax_f32", "4096x32768", (lambda: time_us(lambda i: _ffi.softmax(big[i % 2], out=yb2), 2, iters)), bytes_=2 * 4096 * 32768 * 4)
+        del big, yb2
     rows, d = 32 * 2048, 4096
     if any(wanted(o, f"{rows}x{d}") or wanted(o, f"{rows * d}") for o in ("mean_f32_lastdim", "reduce_max_f32")):
         nv = variants_for(rows * d * 4)
@@ -170,7 +180,7 @@ def bench_index(T, iters):
 
 def bench_gemm(T, iters):
     dev = "cuda"
-    for (N, K) in ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)):
+    for (N, K) in ((4096, 4096), (6144, 4096), (14336, 4096), (28672, 4096), (4096, 14336), (128256, 4096)):
         if MATCH and not any(wanted(o, f"M{M} N{N} K{K}") for o in ("gemm_bf16_tn", "addmm_bias_bf16_tn") for M in (1, 8, 16, 32, 128, 4096)):
             continue
         nv = variants_for(N * K * 2)
@@ -242,6 +252,75 @@ def bench_sdpa(T, iters):
             del Ks, Vs
 
 
+def bench_decode_breakdown(T, iters):
+    """Where one decode step of the Llama-3-8B shape (batch 32, context 2176) spends its time:
+    the step's kernels are replayed group by group from CUDA graphs (same weights, caches and
+    launch arguments as the real step), next to the whole captured step."""
+    from kuillm_b200.decoder import Decoder, DecoderConfig
+    cfg = DecoderConfig.llama3_8b()
+    B, cap, ctx = 32, 2304, 2176
+    dec = Decoder(cfg)
+    dec.alloc_cache(B, cap)
+    dev = dec.device
+    hd, hq, hk, d = cfg.head_dim, dec.hq, dec.hk, cfg.d_model
+    W = (hq + 2 * hk) * hd
+    x = torch.randn(B, d, device=dev).bfloat16()
+    resid = torch.randn(B, d, device=dev).bfloat16()
+    qkv = torch.randn(B, W, device=dev).bfloat16()
+    attn = torch.randn(B, hq * hd, device=dev).bfloat16()
+    act = torch.randn(B, dec.ff, device=dev).bfloat16()
+    pos = torch.full((B,), ctx - 1, device=dev, dtype=torch.int64)
+    kvlen = torch.full((B,), ctx, device=dev, dtype=torch.int64)
+    q4 = qkv.as_strided((B, hq, 1, hd), (W, hd, W, 1))
+    o4 = attn.as_strided((B, hq, 1, hd), (hq * hd, hd, hq * hd, 1))
+    tok = torch.zeros(B, dtype=torch.int64, device=dev)
+
+    def gemms():
+        for L in dec.layers:
+            _ffi.gemm(x, L["wqkv"], trans_b=True)
+            _ffi.gemm(attn, L["wo"], trans_b=True)
+            _ffi.gemm_swiglu(x, L["wgu"])
+            _ffi.gemm(act, L["wd"], trans_b=True)
+
+    def attention():
+        for li in range(cfg.n_layers):
+            _ffi.sdpa(q4, dec.k_cache[li], dec.v_cache[li], is_causal=True, need_lse=False, out=o4, kv_lens=kvlen)
+
+    def small():
+        for li, L in enumerate(dec.layers):
+            _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)
+            _ffi.rope_qkv(qkv, hq, hk, hd, pos, cfg.rope_theta, dec.k_cache[li], dec.v_cache[li], rows_per_seq=1)
+            _ffi.rmsnorm(x, L["n2"], cfg.eps, residual=resid)
+
+    def head():
+        h = _ffi.embedding(dec.embed, tok)
+        hf = _ffi.rmsnorm(h, dec.norm_f, cfg.eps, residual=resid)
+        logits = _ffi.gemm(hf, dec.lm_head, trans_b=True)
+        _ffi.argmax_lastdim(logits)
+
+    def step():
+        dec.length = ctx - 1
+        dec._graph_step()
+
+    dec._tok = tok
+    dec._tok_out = torch.zeros_like(tok)
+    dec._pos = pos.clone()
+    dec._kvlen = kvlen.clone()
+    n_layer_launch = {"gemm": 4 * cfg.n_layers, "attention": cfg.n_layers, "norm_rope": 3 * cfg.n_layers, "embed_head_argmax": 4}
+    weights = cfg.n_layers * (W * d + hq * hd * d + 2 * dec.ff * d + dec.ff * d) * 2
+    kv = 2 * cfg.n_layers * B * hk * ctx * hd * 2
+    head_b = cfg.vocab * d * 2
+    small_b = cfg.n_layers * (2 * 4 * B * d * 2 + 2 * B * W * 2)
+    for name, fn, nbytes in (("gemm", gemms, weights), ("attention", attention, kv), ("norm_rope", small, small_b),
+                             ("embed_head_argmax", head, head_b), ("whole_step", step, weights + kv + head_b)):
+        if not wanted("decode_step_part", name):
+            continue
+        # few calls per graph: every whole step moves the device-side position / length counters on
+        us = time_us(lambda i: fn(), 1, min(max(2, iters // 4), 16))
+        launches = n_layer_launch.get(name, sum(n_layer_launch.values()) + 2)
+        T.add("decode_step_part", name, us, bytes_=nbytes, bound="hbm", note=f"{launches} launches per call")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="stream,index,gemm,sdpa")
@@ -258,7 +337,8 @@ def main():
         Path(a.out).write_text("")
     T = Table(a.out)
     for name in a.only.split(","):
-        {"stream": bench_stream, "index": bench_index, "gemm": bench_gemm, "sdpa": bench_sdpa}[name](T, a.iters)
+        {"stream": bench_stream, "index": bench_index, "gemm": bench_gemm, "sdpa": bench_sdpa,
+         "decode": bench_decode_breakdown}[name](T, a.iters)
         torch.cuda.empty_cache()
     if _ffi.tc_error() != 0:
         print(json.dumps({"error": "a tensor-core pipeline wait timed out"}))

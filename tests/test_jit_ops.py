@@ -184,6 +184,47 @@ def test_topk_ties_take_the_lowest_index(cuda, gates, case):
     assert np.array_equal(to_np(vals), rv, equal_nan=True)
 
 
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("shape", [(5, 100), (3, 70000), (32, 128256), (300, 4099)])
+def test_argmax_lowest_index_of_the_maximum(cuda, dtype, shape):
+    """Row arg-max over 1..8 CTAs per row: ties (the quantised dtypes repeat values), NaN first, -0 == +0."""
+    from kuipy import _ffi
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(*shape, generator=g).to(dtype)
+    X[0, 7], X[0, shape[1] - 1] = 9.0, 9.0             # a tie between both ends of the row
+    X[1, :] = 0.0
+    X[1, 3] = -0.0                                      # all equal, one negative zero: index 0 wins
+    X[2, shape[1] // 2] = float("nan")                  # NaN is the maximum
+    X[2, shape[1] // 2 + 9] = float("nan")
+    got = _ffi.argmax_lastdim(X.cuda())
+    ref = torch.argmax(X.float(), dim=-1)
+    assert got.dtype == torch.int64
+    assert torch.equal(got.cpu(), ref)
+
+
+def test_softmax_long_rows_in_clusters(cuda):
+    """64 rows of 128256 fp32: eight CTAs per row, streamed twice; and a row of -inf except one entry."""
+    X = randn(64, 128256) * 3
+    X[5, :] = float("-inf")
+    X[5, 77] = 1.0
+    out = run_family(kuiops.SoftmaxImpl({}), aten._softmax.default, (X, 1, False))
+    ref = O.softmax_lastdim(to_np(X))
+    assert_fp32_1e5(out, ref)
+    assert float(out[5, 77]) == 1.0 and float(out[5].sum()) == 1.0
+
+
+def test_topk_small_k_of_a_long_row_with_duplicates(cuda, gates):
+    """k = 50 of 128256 through the thread-maxima bound; bf16-quantised values give many exact ties."""
+    gates("wide")
+    g = torch.Generator().manual_seed(5)
+    X = (torch.randn(8, 128256, generator=g) * 3).bfloat16().float()
+    X[3, 1000:1100] = X[3].max() + 1                    # 100 copies of the maximum: lowest 50 indices
+    vals, idx = run_family(kuiops.TopkImpl({}), aten.topk.default, (X.cuda(), 50))
+    rv, ri = O.topk(X.numpy(), 50)
+    assert_bit_exact(idx, ri)
+    assert_bit_exact(vals, rv)
+
+
 # ---- attention --------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", FLOATS)
 def test_sdpa_biased(cuda, gates, dtype):
@@ -284,6 +325,28 @@ def test_scatter(cuda, dtype, shape, dim):
     assert out.data_ptr() != Self.data_ptr()
 
 
+@pytest.mark.parametrize("dtype", [torch.int64, torch.bfloat16, torch.bool])
+def test_gather_scatter_innermost_axis_rows_staged_on_chip(cuda, gates, dtype):
+    """Rows long enough for several vector chunks, odd lengths (rows start misaligned), an index block
+    smaller than the tensor on both axes, and a 3-d tensor whose outer axes merge."""
+    gates("wide")
+    g = torch.Generator().manual_seed(7)
+    as_np = (lambda t: t.view(torch.int16).cpu().numpy()) if dtype == torch.bfloat16 else to_np
+    view = (lambda t: t.view(torch.int16)) if dtype == torch.bfloat16 else (lambda t: t)
+    for shape, ishape in (((70, 5001), (70, 5001)), ((70, 5001), (33, 4000)), ((3, 5, 2049), (3, 5, 2049)), ((1, 20000), (1, 20000))):
+        Inp = payload(shape, dtype)
+        Idx = torch.randint(0, shape[-1], ishape, generator=g).cuda()
+        d = len(shape) - 1
+        out = run_family(kuiops.GatherImpl({}), aten.gather.default, (Inp, d, Idx))
+        assert_bit_exact(view(out), O.gather(as_np(Inp), d, to_np(Idx)))
+        # scatter: a permutation prefix per row keeps the index injective
+        rows = int(np.prod(ishape[:-1]))
+        perm = torch.stack([torch.randperm(shape[-1], generator=g)[:ishape[-1]] for _ in range(rows)]).reshape(ishape).cuda()
+        Src = payload(ishape, dtype, seed=9)
+        got = run_family(kuiops.ScatterImpl({}), aten.scatter.src, (Inp, d, perm, Src))
+        assert_bit_exact(view(got), O.scatter(as_np(Inp), d, to_np(perm), as_np(Src)))
+
+
 def test_scatter_unsupported(cuda):
     impl = kuiops.ScatterImpl({})
     Self, Src = randn(4, 4), randn(4, 4)
@@ -342,6 +405,24 @@ def test_index_and_isin(cuda, gates):
     assert_bit_exact(run_family(kuiops.IsinImpl({}), aten.isin.Tensor_Tensor, (ids * 997, big)), O.isin(to_np(ids) * 997, to_np(big)))
     scalar = torch.tensor(int(ids[0, 0]), device="cuda")
     assert_bit_exact(run_family(kuiops.IsinImpl({}), aten.isin.Tensor_Tensor, (ids, scalar)), O.isin(to_np(ids), to_np(scalar)))
+
+
+def test_isin_hash_table_edges(cuda, gates):
+    """INT64_MIN (the table's free-slot mark) as a test value and as an element, duplicates in the
+    test set, sizes that are not multiples of the 8-element store, several passes with invert."""
+    gates("wide")
+    g = torch.Generator().manual_seed(4)
+    lo = torch.iinfo(torch.int64).min
+    ids = torch.randint(-50, 50, (3, 1001), generator=g)
+    ids[0, 0], ids[2, 1000] = lo, lo
+    for stop in (torch.tensor([lo, 3, 3, 7, -4]), torch.tensor([3, 7, -4]), torch.randint(-10 ** 9, 10 ** 9, (4500,), generator=g)):
+        for inv in (False, True):
+            got = run_family(kuiops.IsinImpl({}), aten.isin.Tensor_Tensor, (ids.cuda(), stop.cuda()), {"invert": inv})
+            assert_bit_exact(got, O.isin(ids.numpy(), stop.numpy(), invert=inv))
+    wide = torch.randint(-10 ** 9, 10 ** 9, (4500,), generator=g)
+    pick = wide[torch.randint(0, 4500, (3, 1001), generator=g)]         # every element is in the set
+    got = run_family(kuiops.IsinImpl({}), aten.isin.Tensor_Tensor, (pick.cuda(), wide.cuda()))
+    assert bool(got.all())
 
 
 def test_out_of_range_indices_are_skipped_and_flagged(cuda):

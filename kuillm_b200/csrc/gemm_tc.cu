@@ -435,6 +435,11 @@ bool gemm_tc_eligible(const GemmArgs& a) {
 
 struct TcPlan { bool swapped; int bn; uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split; };
 
+// Pipeline depth of the swapped placement: chosen so that three CTAs (two for the 128-column
+// tile) fit one SM; what keeps HBM busy is the number of resident CTAs, each with a few tiles in
+// flight, not the depth of one CTA's ring.
+constexpr uint32_t swapped_stages(int bn) { return bn <= 16 ? 4u : 3u; }
+
 static TcPlan make_plan(const GemmArgs& a) {
   TcPlan pl = {};
   pl.kblocks = (a.K + TBK - 1) / TBK;
@@ -453,7 +458,7 @@ static TcPlan make_plan(const GemmArgs& a) {
   if (pl.swapped) {
     // Too few output tiles to occupy the machine: split K over the CTAs of a cluster (at most 8, the
     // portable cluster size).  Aim at as many CTAs as can be resident at once.
-    const uint32_t smem_cta = 4u * (TBM * TBK * 2 + uint32_t(pl.bn) * TBK * 2) + 2048;
+    const uint32_t smem_cta = swapped_stages(pl.bn) * (TBM * TBK * 2 + uint32_t(pl.bn) * TBK * 2) + 2048;
     uint32_t per_sm = (227u * 1024u) / smem_cta;
     if (per_sm > 3) per_sm = 3;
     if (per_sm < 1) per_sm = 1;
@@ -557,8 +562,8 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
     const unsigned grid = unsigned(units);
     const CUtensorMap& mp = mapB; const CUtensorMap& mq = mapA;
 #define KUIOPS_SW(BNV)                                                                             \
-  case BNV: return b_mn ? launch_tc<TIN, BNV, 4, 1, true, false>(mp, mq, p, grid, st)              \
-                        : launch_tc<TIN, BNV, 4, 1, false, false>(mp, mq, p, grid, st);
+  case BNV: return b_mn ? launch_tc<TIN, BNV, int(swapped_stages(BNV)), 1, true, false>(mp, mq, p, grid, st)   \
+                        : launch_tc<TIN, BNV, int(swapped_stages(BNV)), 1, false, false>(mp, mq, p, grid, st);
     switch (pl.bn) { KUIOPS_SW(16) KUIOPS_SW(32) KUIOPS_SW(64) KUIOPS_SW(128) }
 #undef KUIOPS_SW
     return KUIOPS_EUNSUPPORTED;

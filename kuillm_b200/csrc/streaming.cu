@@ -429,7 +429,7 @@ __device__ __forceinline__ void arg_consider(ArgBest& b, float v, long long i) {
 // A row is split over the CTAs of a cluster (1..8) so that a few long rows still cover the SMs;
 // every CTA pushes its candidate into the leader's shared memory and the leader picks.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256)
 argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __restrict__ out, int vec_ok,
                    uint32_t cluster_ctas) {
   __shared__ float sv[32];
@@ -512,7 +512,8 @@ static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cu
   if (m > 0x7FFFFFFFull / 8) return KUIOPS_ELIMIT;
   constexpr int VN = Vec16<T>::N;
   const int vec_ok = aligned16(X) && (n % VN == 0);
-  unsigned threads = n >= 16384 ? 512 : (n >= 2048 ? 256 : 64);
+  // small CTAs: with a cluster per row all of them must be resident at once to finish in one wave
+  unsigned threads = n >= 2048 ? 256 : 64;
   // cluster width: enough CTAs to give every SM two when rows are few and long
   uint32_t c = 1;
   while (c < 8 && m * c < 2 * uint64_t(kNumSMs) && n / (c * 2) >= 8192) c *= 2;

@@ -166,7 +166,7 @@ def bench_index(T, iters):
         T.add("gather_i64_dim1", f"{r}x{c}", (lambda: time_us(lambda i: _ffi.gather(ids[i], 1, idx), nv, iters)), bytes_=3 * nb,
               note="payload in + index in + out")
         T.add("scatter_i64_dim1", f"{r}x{c}", (lambda: time_us(lambda i: _ffi.scatter(ids[i], 1, perm, ids[(i + 1) % nv]), nv, iters)),
-              bytes_=5 * nb, note="self copy (r+w) + src + index + scattered write")
+              bytes_=4 * nb, note="self in + src + index + out")
         pos = torch.randint(0, c, (c // 4,), device=dev, generator=g)
         T.add("index_i64_dim1", f"{r}x{c}[:, {c // 4}]", (lambda: time_us(lambda i: _ffi.index(ids[i], 1, [pos]), nv, iters)),
               bytes_=2 * r * (c // 4) * 8)

@@ -11,7 +11,9 @@
 //     memory, each CTA finishing a share of the tile's columns (in-kernel reduction,
 //     deterministic, no global scratch).
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = TMEM allocator + UMMA issuer (one
-// lane), warps 2..5 = epilogue (TMEM -> registers -> alpha/beta/bias -> global).
+// lane), warps 2..5 = epilogue (TMEM -> registers -> alpha/beta/bias -> global); the normal
+// placement adds warps 6..9 as a second epilogue group, one group per accumulator stage, so that
+// short-K problems whose time is all epilogue (bmm with K = 128) drain two tiles at once.
 // Operands arrive through 3-D tensor maps (inner, rows, batch) with 128-byte swizzle; edges in
 // M, N and K rely on TMA zero fill, so no divisibility is required beyond the 16-byte stride
 // rule.  Replaces Klas.GEMM.TensorCore2D (wmma fragments, kuiops/mm/Kuiops.Mm.Inst.fst.j2:9-11).
@@ -26,7 +28,8 @@ namespace kuiops {
 
 constexpr int TBM = 128;   // TMEM lanes = rows of the P operand per tile
 constexpr int TBK = 64;    // K elements per pipeline stage (one 128-byte swizzle span)
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 192;        // swapped placement: one epilogue warpgroup
+constexpr int kTcThreadsWide = 320;    // normal placement: one epilogue warpgroup per accumulator stage
 
 struct TcParams {
   uint32_t rowsP, rowsQ, K, batch;
@@ -87,7 +90,7 @@ __device__ __forceinline__ void store_swiglu_swapped(const TcParams& p, uint32_t
 }
 
 template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(ACC_STAGES == 2 ? kTcThreadsWide : kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
                const TcParams p) {
   constexpr uint32_t P_BYTES = TBM * TBK * 2;
@@ -105,7 +108,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
-  // normal placement only: 4 KB per epilogue warp to turn row-per-thread results into row-contiguous stores
+  // normal placement only: 4 KB per epilogue warp (8 warps) to turn row-per-thread results into row-contiguous stores
   unsigned char* epi_stage = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -213,9 +216,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
                        ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
     const bool cin_vec = !p.Cin || (((reinterpret_cast<uintptr_t>(p.Cin) & 15u) == 0) && (p.ldcin % 8 == 0) &&
                                     (p.stride_cin % 8 == 0));
-    uint32_t acc_it = 0;
+    // epilogue group g owns accumulator stage g: it takes this CTA's tiles g, g + groups, ...
+    constexpr uint32_t kGroups = ACC_STAGES == 2 ? 2 : 1;
+    const uint32_t group = (warp - 2) >> 2;
+    uint32_t acc_it = group;
     bool ok = true;
-    for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++acc_it) {
+    for (uint32_t u = blockIdx.x + group * gridDim.x; u < units && ok; u += kGroups * gridDim.x, acc_it += kGroups) {
       const uint32_t tile = u / p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
       const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
@@ -235,7 +241,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
           // touch 32 rows per instruction.  The warp's 32 x 64 block goes through shared memory
           // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and leaves as 128-byte
           // row segments, four rows per store instruction.
-          unsigned char* stg = epi_stage + quarter * 4096;
+          unsigned char* stg = epi_stage + (warp - 2) * 4096;
           TIN* cbase = static_cast<TIN*>(p.C) + size_t(b) * p.stride_c + col0;
           for (; c + 64 <= ncols; c += 64) {
             float w[64];
@@ -347,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     // the cluster barrier instructions are warp-collective
     __syncwarp();
     cluster.sync();
-    if (warp >= 2 && blockIdx.x < units) {
+    if (warp >= 2 && warp < 6 && blockIdx.x < units) {
       const uint32_t quarter = warp & 3, lane_in_tile = quarter * 32 + lane;
       const uint32_t tile = blockIdx.x / p.splits, rank = blockIdx.x % p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
@@ -486,7 +492,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   static_assert(size_t(BN) * TBM * sizeof(float) <= size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2),
                 "the split-K partial is parked in the pipeline buffers");
   // pipeline stages + alignment slack + barriers + (normal placement) the epilogue's staging blocks
-  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256 + (ACC_STAGES == 2 ? 16384 : 0);
+  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256 + (ACC_STAGES == 2 ? 32768 : 0);
   static_assert(smem <= 227 * 1024, "shared memory budget of one CTA");
   auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
   // the opt-in for large dynamic shared memory is per device: do it once per (kernel, device)
@@ -501,7 +507,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(ACC_STAGES == 2 ? kTcThreadsWide : kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];

@@ -459,21 +459,8 @@ isin_kernel(uint64_t n, const int64_t* __restrict__ elems, uint64_t m, const int
         const uint8_t* pb = reinterpret_cast<const uint8_t*>(&prev);
         uint2 res;
         uint8_t* rb = reinterpret_cast<uint8_t*>(&res);
-        // first probe of all eight elements at once (independent shared-memory loads); the few
-        // that meet a foreign key in their home slot walk on
-        unsigned long long sl[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) sl[q] = slots[isin_hash(static_cast<unsigned long long>(v[q]))];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const unsigned long long u = static_cast<unsigned long long>(v[q]);
-          bool hit;
-          if (u == kIsinEmpty) hit = hek;
-          else if (sl[q] == u) hit = true;
-          else if (sl[q] == kIsinEmpty) hit = false;
-          else hit = isin_probe(slots, hek, v[q]);
-          rb[q] = finish(hit, pb[q]);
-        }
+        for (int q = 0; q < 8; ++q) rb[q] = finish(isin_probe(slots, hek, v[q]), pb[q]);
         *reinterpret_cast<uint2*>(out + e) = res;
       }
       e0 = lo + groups * 8;

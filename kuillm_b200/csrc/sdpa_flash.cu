@@ -14,8 +14,10 @@
 //                      A operand of the next UMMA is then read from TMEM; no shared-memory round
 //                      trip, no proxy fence) or written into a K-major 128-byte-swizzled shared tile
 //     O += P V         UMMA 128 x 128 x 64, V MN-major as loaded
-// The CTA is small enough (112 KB of shared memory, 256 TMEM columns) for two CTAs per SM, so one
-// CTA's softmax overlaps the other's MMAs.  Epilogue: O / l to global, natural-log LSE.
+// The CTA is small enough (96 to 112 KB of shared memory, 256 TMEM columns) for two CTAs per SM,
+// so one CTA's softmax overlaps the other's MMAs.  Its two warpgroups split the register file
+// unevenly (setmaxnreg): the copy / issue warps keep 56 registers a thread, the four softmax
+// warps take 200, enough to keep a whole 64-column row of S in flight without serialising it.  Epilogue: O / l to global, natural-log LSE.
 // This is the causal / grouped-query attention the dispatcher reaches as
 // aten._scaled_dot_product_flash_attention; the reference only has the naive biased kernel
 // (kuiops/sdpa/Kuiops.Sdpa.fst.1) and keeps it disconnected.
@@ -29,7 +31,9 @@ namespace kuiops {
 constexpr int FBM = 128;      // query rows per CTA (TMEM lanes)
 constexpr int FBN = 64;       // keys per tile
 constexpr int FD = 128;       // head dim
-constexpr int kFlashThreads = 192;
+constexpr int kFlashThreads = 256;      // warp 0: TMA, warp 1: UMMA issue, warps 2-3: idle, warps 4-7: softmax
+constexpr int kFlashRegsLow = 56;       // registers per thread kept by warps 0-3 ...
+constexpr int kFlashRegsHigh = 200;     // ... and taken by the softmax warps (2 CTAs x 128 x (56 + 200) = the whole file)
 constexpr uint32_t F_Q_BYTES = FBM * FD * 2;        // 32 KB: two 64-column halves of 16 KB
 constexpr uint32_t F_K_BYTES = FBN * FD * 2;        // 16 KB: two halves of 8 KB
 constexpr uint32_t F_V_BYTES = FBN * FD * 2;        // 16 KB: two 64-column boxes of 8 KB
@@ -146,6 +150,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   pdl_wait();          // Q, K, V may still be being written by the previous kernel in the stream
   pdl_trigger();
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFlashRegsLow));
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
     if (lane == 0) {
@@ -219,8 +225,10 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc::umma_commit(o_done);
       }
     }
+  }
   } else {
     // ------------------------------ softmax + epilogue ------------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kFlashRegsHigh));
     const uint32_t quarter = warp & 3;
     const uint32_t r = quarter * 32 + lane;               // row inside the tile
     const uint32_t row = row0 + r;
@@ -264,16 +272,16 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       const float nmm = (m_used == -INFINITY) ? 0.f : -m_used;   // a fully masked row keeps p = 0
       float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+      uint32_t pk[FBN / 2];                       // P as packed 16-bit pairs (key 2c, key 2c + 1)
 #pragma unroll
       for (int c = 0; c < FBN; c += 4) {
         f_fma2(sv[c], sv[c + 1], p.scale_log2, nmm);
         f_fma2(sv[c + 2], sv[c + 3], p.scale_log2, nmm);
-        sv[c] = f_ex2(sv[c]);
-        sv[c + 1] = f_ex2(sv[c + 1]);
-        sv[c + 2] = f_ex2(sv[c + 2]);
-        sv[c + 3] = f_ex2(sv[c + 3]);
-        f_add2(r0, r1, sv[c], sv[c + 1]);
-        f_add2(r2, r3, sv[c + 2], sv[c + 3]);
+        const float e0 = f_ex2(sv[c]), e1 = f_ex2(sv[c + 1]), e2 = f_ex2(sv[c + 2]), e3 = f_ex2(sv[c + 3]);
+        f_add2(r0, r1, e0, e1);
+        f_add2(r2, r3, e2, e3);
+        pk[c / 2] = pack2<T>(e0, e1);
+        pk[c / 2 + 1] = pack2<T>(e2, e3);
       }
       l_run = l_run * corr + ((r0 + r1) + (r2 + r3));
       const bool rescale = j > 0 && __any_sync(0xffffffffu, corr != 1.f);
@@ -300,24 +308,15 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc::tmem_st_wait();
       }
       if (PT) {
-        // row r of P: bf16 pairs (key 2c, key 2c + 1) in column c of the S buffer this tile came from
-        uint32_t pk[FBN / 2];
-#pragma unroll
-        for (int c = 0; c < FBN / 2; ++c) pk[c] = pack2<T>(sv[2 * c], sv[2 * c + 1]);
+        // row r of P goes into the S buffer this tile came from, column c = keys 2c and 2c + 1
         tc::tmem_st32(tmem_S + (j & 1) * FBN + lane_addr, pk);
         tc::tmem_st_wait();
       } else {
         // P row -> K-major 128-byte-swizzled tile: 16-byte chunk c of row r sits at chunk (c ^ (r & 7))
         unsigned char* prow = p_s + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-        for (int c = 0; c < FBN / 8; ++c) {
-          uint4 pk;
-          pk.x = pack2<T>(sv[c * 8 + 0], sv[c * 8 + 1]);
-          pk.y = pack2<T>(sv[c * 8 + 2], sv[c * 8 + 3]);
-          pk.z = pack2<T>(sv[c * 8 + 4], sv[c * 8 + 5]);
-          pk.w = pack2<T>(sv[c * 8 + 6], sv[c * 8 + 7]);
-          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
-        }
+        for (int c = 0; c < FBN / 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         tc::fence_proxy_async();          // make the generic-proxy writes visible to the UMMA (async proxy)
       }
       tc::tc_fence_before();

@@ -448,12 +448,6 @@ argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __r
   const uint64_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
   const uint64_t lo = min(uint64_t(part) * nv_per * VN, n), hi = min(lo + nv_per * VN, n);
   ArgBest best{-INFINITY, LLONG_MAX};
-  // The hot loop only asks "is v above the running value, or is either a NaN"; the full rule runs
-  // on the few elements that pass.  A thread meets its elements in index order, so a later equal
-  // value never replaces an earlier one.
-  auto scan = [&](float v, long long i) {
-    if (!(v <= best.v) || best.i == LLONG_MAX) arg_consider(best, v, i);
-  };
   if (vec_ok) {
     const uint64_t nvec = (hi - lo) / VN;
     const uint64_t nt = blockDim.x;
@@ -461,12 +455,29 @@ argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __r
       Vec16<T> t[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16_stream(x + lo + (v0 + u * nt) * VN);
+      // The hot path only finds the largest value of the round (a max tree) and whether a NaN may
+      // be present (the sum is NaN then; inf - inf also trips it, which only costs the slow path).
+      // The exact rule (NaN first, lowest index among equals) runs when the round can change the
+      // thread's candidate.  A thread meets its elements in index order, so a later equal value
+      // never replaces an earlier one.
+      float rm = -INFINITY, rsum = 0.f;
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         if (v0 + u * nt < nvec) {
+          float vm = ElemTraits<T>::to_f(t[u].v[0]), vs = vm;
 #pragma unroll
-          for (int e = 0; e < VN; ++e) scan(ElemTraits<T>::to_f(t[u].v[e]), (long long)(lo + (v0 + u * nt) * VN + e));
+          for (int e = 1; e < VN; ++e) { const float f = ElemTraits<T>::to_f(t[u].v[e]); vm = fmaxf(vm, f); vs += f; }
+          rm = fmaxf(rm, vm);
+          rsum += vs;
         }
+      if (rm > best.v || rsum != rsum || best.i == LLONG_MAX || best.v != best.v) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v0 + u * nt < nvec) {
+#pragma unroll
+            for (int e = 0; e < VN; ++e) arg_consider(best, ElemTraits<T>::to_f(t[u].v[e]), (long long)(lo + (v0 + u * nt) * VN + e));
+          }
+      }
     }
     for (uint64_t i = lo + nvec * VN + threadIdx.x; i < hi; i += blockDim.x)
       arg_consider(best, ElemTraits<T>::to_f(x[i]), (long long)i);

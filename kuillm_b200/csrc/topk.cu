@@ -376,8 +376,11 @@ topk_sel_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X,
   pdl_wait();
   pdl_trigger();
 
-  // ---- pass 1: the largest key each thread meets (no atomics in the stream) -------------------
-  uint32_t kmax = 0;                          // 0 is the key of no value: "this thread saw nothing"
+  // ---- pass 1: the largest value each thread meets (no atomics in the stream) -----------------
+  // fmaxf skips NaNs, so a thread that saw NaNs reports a smaller value than its true maximum;
+  // the bound below only needs "some element of the thread is at least this large", which holds.
+  float fm = -INFINITY;
+  bool saw = false;
   for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
     float4 f[4];
 #pragma unroll
@@ -385,11 +388,11 @@ topk_sel_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X,
       f[u] = (v0 + u * nt < nvec) ? __ldcs(reinterpret_cast<const float4*>(x + lo + size_t(v0 + u * nt) * 4))
                                   : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (v0 + u * nt < nvec)
-        kmax = max(max(kmax, max(key_of(f[u].x), key_of(f[u].y))), max(key_of(f[u].z), key_of(f[u].w)));
+    for (int u = 0; u < 4; ++u) fm = fmaxf(fmaxf(fm, fmaxf(f[u].x, f[u].y)), fmaxf(f[u].z, f[u].w));
+    saw = true;
   }
-  for (uint32_t i = lo + nvec * 4 + tid; i < hi; i += nt) kmax = max(kmax, key_of(x[i]));
+  for (uint32_t i = lo + nvec * 4 + tid; i < hi; i += nt) { fm = fmaxf(fm, x[i]); saw = true; }
+  const uint32_t kmax = saw ? key_of(fm) : 0u;      // 0 is the key of no value: "this thread saw nothing"
   {
     // one histogram entry per thread, duplicates inside a warp combined first
     const uint32_t b = kmax >> 21;
@@ -412,11 +415,16 @@ topk_sel_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X,
   const uint32_t bin = lead->bin;
 
   // ---- pass 2 (served by L2): every element at or above the bound's bin goes to the leader ----
+  // The bin's lower edge as a float: keys are monotonic in the value, so "key >= edge" is one
+  // float compare; NaNs (the top keys) always qualify.
+  const uint32_t edge = bin << 21;
+  const bool nan_only = edge > 0xFF800000u;                       // above the key of +inf
+  const float thr = edge >= 0x80000000u ? __uint_as_float(edge & 0x7FFFFFFFu)
+                  : (edge < 0x00800000u ? -INFINITY : __uint_as_float(~edge));
   auto route = [&](float v, uint32_t i) {
-    const uint32_t key = key_of(v);
-    if ((key >> 21) >= bin) {
+    if (v != v || (!nan_only && v >= thr)) {
       const uint32_t pos = atomicAdd(&lead->cand_cnt, 1u);
-      if (pos < uint32_t(kCandMax)) lead->cand[pos] = pack(key, i);
+      if (pos < uint32_t(kCandMax)) lead->cand[pos] = pack(key_of(v), i);
     }
   };
   for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {

@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include <cooperative_groups.h>
 #include <climits>
+#include <cstdlib>
 
 namespace cg = cooperative_groups;
 namespace kuiops {
@@ -451,33 +452,41 @@ argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __r
   if (vec_ok) {
     const uint64_t nvec = (hi - lo) / VN;
     const uint64_t nt = blockDim.x;
+    // Hot loop, per 16-byte vector: its largest value (max tree), "is it above the thread's running
+    // maximum" (strict, so the first vector that holds the maximum wins) and a NaN detector (the
+    // sum is NaN when an element is; inf - inf also trips it, which only costs the exact path).
+    // Which element of the winning vector it was is settled after the loop by reading that one
+    // vector again.
+    float bm = -INFINITY, nan_acc = 0.f;
+    uint64_t bvec = ~0ull;
     for (uint64_t v0 = threadIdx.x; v0 < nvec; v0 += 4 * nt) {      // four loads in flight per thread
       Vec16<T> t[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16_stream(x + lo + (v0 + u * nt) * VN);
-      // The hot path only finds the largest value of the round (a max tree) and whether a NaN may
-      // be present (the sum is NaN then; inf - inf also trips it, which only costs the slow path).
-      // The exact rule (NaN first, lowest index among equals) runs when the round can change the
-      // thread's candidate.  A thread meets its elements in index order, so a later equal value
-      // never replaces an earlier one.
-      float rm = -INFINITY, rsum = 0.f;
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         if (v0 + u * nt < nvec) {
           float vm = ElemTraits<T>::to_f(t[u].v[0]), vs = vm;
 #pragma unroll
           for (int e = 1; e < VN; ++e) { const float f = ElemTraits<T>::to_f(t[u].v[e]); vm = fmaxf(vm, f); vs += f; }
-          rm = fmaxf(rm, vm);
-          rsum += vs;
+          nan_acc += vs * 0.f;                            // stays 0 unless vs is NaN or infinite
+          const bool take = vm > bm || bvec == ~0ull;
+          bm = take ? vm : bm;
+          bvec = take ? v0 + u * nt : bvec;
         }
-      if (rm > best.v || rsum != rsum || best.i == LLONG_MAX || best.v != best.v) {
+    }
+    if (nan_acc != nan_acc) {
+      // a NaN (or an infinity) somewhere in this thread's vectors: redo them with the exact rule
+      for (uint64_t v = threadIdx.x; v < nvec; v += nt) {
+        const Vec16<T> t = ld16(x + lo + v * VN);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (v0 + u * nt < nvec) {
-#pragma unroll
-            for (int e = 0; e < VN; ++e) arg_consider(best, ElemTraits<T>::to_f(t[u].v[e]), (long long)(lo + (v0 + u * nt) * VN + e));
-          }
+        for (int e = 0; e < VN; ++e) arg_consider(best, ElemTraits<T>::to_f(t.v[e]), (long long)(lo + v * VN + e));
       }
+    } else if (bvec != ~0ull) {
+      const Vec16<T> t = ld16(x + lo + bvec * VN);
+#pragma unroll
+      for (int e = VN - 1; e >= 0; --e)
+        if (ElemTraits<T>::to_f(t.v[e]) == bm) { best.v = bm; best.i = (long long)(lo + bvec * VN + e); }
     }
     for (uint64_t i = lo + nvec * VN + threadIdx.x; i < hi; i += blockDim.x)
       arg_consider(best, ElemTraits<T>::to_f(x[i]), (long long)i);
@@ -528,6 +537,8 @@ static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cu
   // cluster width: enough CTAs to give every SM two when rows are few and long
   uint32_t c = 1;
   while (c < 8 && m * c < 2 * uint64_t(kNumSMs) && n / (c * 2) >= 8192) c *= 2;
+  if (const char* e = getenv("KUIOPS_ARGMAX_CLUSTER")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) c = uint32_t(v); }
+  if (const char* e = getenv("KUIOPS_ARGMAX_THREADS")) { const int v = atoi(e); if (v >= 32 && v <= 256 && v % 32 == 0) threads = unsigned(v); }
   return launch_cluster_pdl(argmax_rows_kernel<T>, dim3(unsigned(m * c)), dim3(threads), 0, st, c, m, n,
                             static_cast<const T*>(X), out, vec_ok, c);
 }

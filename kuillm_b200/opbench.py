@@ -125,6 +125,12 @@ def bench_stream(T, iters):
             del ps
         T.add("argmax_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.argmax_lastdim(xs[i]), nv, iters)), bytes_=m * n * 4)
         del xs
+    if wanted("reduce_max_f32", "8208384"):
+        nv = variants_for(m * n * 4)
+        fl = [torch.randn(m * n, device=dev) for _ in range(nv)]
+        T.add("reduce_max_f32", f"{m * n}", (lambda: time_us(lambda i: _ffi.reduce("max", fl[i]), nv, iters)), bytes_=m * n * 4)
+        T.add("mean_f32_lastdim", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.mean_lastdim(fl[i].view(m, n)), nv, iters)), bytes_=m * n * 4)
+        del fl
     if wanted("argmax_bf16", "32x128256"):
         nv = variants_for(32 * n * 2)
         lb = [torch.randn(32, n, device=dev).bfloat16() for _ in range(nv)]

@@ -17,7 +17,7 @@
 // Two CTAs share an SM (97 KB of shared memory and 256 TMEM columns each), so there are four
 // softmax warps per scheduler to hide each other's latencies, and one CTA's softmax overlaps the
 // other's MMAs.  The warpgroups split the register file unevenly (setmaxnreg): the copy / issue
-// warpgroup keeps 40 registers a thread, the two softmax warpgroups take 104.
+// warpgroup keeps 32 registers a thread, the two softmax warpgroups take 104.
 // Epilogue: O / l to global, natural-log LSE.
 // This is the causal / grouped-query attention the dispatcher reaches as
 // aten._scaled_dot_product_flash_attention; the reference only has the naive biased kernel
@@ -33,8 +33,15 @@ constexpr int FBN = 64;       // keys per tile
 constexpr int FHALF = FBN / 2;  // keys per softmax thread
 constexpr int FD = 128;       // head dim
 constexpr int kFlashThreads = 384;      // warp 0: TMA, warp 1: UMMA issue, warps 2-3: idle, warps 4-11: softmax
-constexpr int kFlashRegsLow = 40;       // registers per thread kept by warps 0-3 ...
-constexpr int kFlashRegsHigh = 104;     // ... and taken by the softmax warps: 128 x 40 + 256 x 104 <= half the file
+// setmaxnreg moves registers between the warpgroups of one CTA; the CTA's total stays what it was
+// given at launch (384 threads x 80 registers, the most that lets two CTAs share an SM), and a
+// warpgroup that asks for more than the others released would wait for ever.
+constexpr int kFlashRegsLaunch = 80;
+constexpr int kFlashRegsLow = 32;       // registers per thread kept by warps 0-3 ...
+constexpr int kFlashRegsHigh = 104;     // ... and taken by the eight softmax warps
+static_assert(128 * kFlashRegsLow + 256 * kFlashRegsHigh <= kFlashThreads * kFlashRegsLaunch,
+              "register budget of the CTA after setmaxnreg");
+static_assert(2 * kFlashThreads * kFlashRegsLaunch <= 65536, "two CTAs per SM");
 constexpr uint32_t F_Q_BYTES = FBM * FD * 2;        // 32 KB: two 64-column halves of 16 KB
 constexpr uint32_t F_K_BYTES = FBN * FD * 2;        // 16 KB: two halves of 8 KB
 constexpr uint32_t F_V_BYTES = FBN * FD * 2;        // 16 KB: two 64-column boxes of 8 KB
@@ -411,6 +418,11 @@ static int flash_launch(const SdpaArgs& a, cudaStream_t st) {
   const uint64_t bit = 1ull << (dev & 63);
   if (!(configured.load(std::memory_order_acquire) & bit)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return KUIOPS_ELAUNCH;
+    // the register hand-over inside the kernel assumes the allocation the compiler reported; a
+    // build with fewer registers per thread would leave a warpgroup waiting for registers for ever
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return KUIOPS_ELAUNCH;
+    if (fa.numRegs * kFlashThreads < 128 * kFlashRegsLow + 256 * kFlashRegsHigh) return KUIOPS_EUNSUPPORTED;
     configured.fetch_or(bit, std::memory_order_release);
   }
   const unsigned grid = unsigned(uint64_t(a.n) * a.h * ((a.l + FBM - 1) / FBM));

@@ -37,6 +37,8 @@ WORKLOADS = {
     "tiny-llama-shaped b4 p64 d8": (dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=1000), 4, 64, 8),
 }
 DEFAULT_WORKLOAD = "llama3-8b-shaped b32 p2048 d256"
+# bytes per launch of gemm_tc_kernel with the SwiGLU epilogue at M=32, N=28672, K=4096 (bf16), from ncu
+NCU_TRAFFIC_GATEUP_M32 = 241.8e6
 
 
 class ClockSampler:
@@ -260,23 +262,38 @@ def run_ours(args):
     if _ffi.tc_error() != 0:
         raise SystemExit("a tensor-core pipeline wait timed out during the bench; numbers discarded")
 
-    # roofline of the dominant decode kernel: the gate|up weight-streaming GEMM, timed live over the
-    # 32 layers' distinct weights (7.5 GB, far beyond L2) with events on this stream
+    # roofline of the dominant decode kernel: the gate|up weight-streaming GEMM with its fused SwiGLU
+    # epilogue, exactly the launch the decode step makes, timed live over the 32 layers' distinct
+    # weights (7.5 GB, far beyond L2): the 32 launches are replayed from a CUDA graph, as in the
+    # decode step, with events on the replaying stream
     x = torch.randn(batch, cfg.d_model, device=dev).to(cfg.dtype)
-    for L in dec.layers[:3]:
-        _ffi.gemm(x, L["wgu"], trans_b=True)
-    r0, r1 = ev(), ev()
-    torch.cuda.synchronize()
-    r0.record()
-    for L in dec.layers:
-        _ffi.gemm(x, L["wgu"], trans_b=True)
-    r1.record()
-    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for L in dec.layers[:3]:
+            _ffi.gemm_swiglu(x, L["wgu"])
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for L in dec.layers:
+                _ffi.gemm_swiglu(x, L["wgu"])
+        g.replay()
+        side.synchronize()
+        r0, r1 = ev(), ev()
+        r0.record(side)
+        g.replay()
+        r1.record(side)
+        side.synchronize()
+    torch.cuda.current_stream(dev).wait_stream(side)
     gemm_ms = r0.elapsed_time(r1) / len(dec.layers)
+    del g
     n_out, k_in = dec.layers[0]["wgu"].shape
-    alg_bytes = 2 * (n_out * k_in + batch * k_in + batch * n_out)
+    alg_bytes = 2 * (n_out * k_in + batch * k_in + batch * n_out // 2)
     peaks, peak_kind = measured_peaks()
     achieved = alg_bytes / (gemm_ms * 1e-3) / 1e9
+    # DRAM bytes one such launch moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum of the
+    # capture summarised in profiles/ncu_gemm_m32_gateup.md); only meaningful for the full-size weights
+    traffic = NCU_TRAFFIC_GATEUP_M32 if (n_out, k_in, batch, tp) == (28672, 4096, 32, 1) else None
 
     vals = torch.tensor([total_ms, e2e_ms, prefill_ms, decode_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -302,9 +319,9 @@ def run_ours(args):
                     "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": out_host.numel() * 8},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": {"kernel": "gemm_tc_kernel (gate|up projection of one decode step)", "bound": "hbm",
+            "roofline": {"kernel": "gemm_tc_kernel (gate|up projection + SwiGLU epilogue of one decode step)", "bound": "hbm",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_kind": peak_kind, "traffic": None, "us_per_launch": gemm_ms * 1e3,
+                         "peak_kind": peak_kind, "traffic": traffic, "us_per_launch": gemm_ms * 1e3,
                          "algorithmic_bytes_per_launch": alg_bytes},
         }
         if world == 1 and not args.no_cpu_baseline:

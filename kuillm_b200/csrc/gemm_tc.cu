@@ -475,11 +475,16 @@ static TcPlan make_plan(const GemmArgs& a) {
       if (cap < 1) cap = 1;
       pl.splits = want < cap ? want : cap;
       if (pl.splits > 8) pl.splits = 8;
+      if (pl.splits > 4 && pl.splits < 8) pl.splits = 4;   // clusters of 5..7 CTAs place badly on the GPCs (measured: 6 is far slower than 4 or 8)
       if (pl.splits < 1) pl.splits = 1;
     }
   }
   pl.kb_per_split = (pl.kblocks + pl.splits - 1) / pl.splits;
   pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;   // no empty slice
+  if (pl.splits > 4 && pl.splits < 8) {
+    pl.kb_per_split = (pl.kblocks + 3) / 4;
+    pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;
+  }
   return pl;
 }
 

@@ -186,6 +186,14 @@ def bench_index(T, iters):
 
 def bench_gemm(T, iters):
     dev = "cuda"
+    if wanted("gemm_swiglu_bf16_tn", "M32 N28672 K4096"):
+        N, K, M = 28672, 4096, 32
+        nv = variants_for(N * K * 2)
+        Ws = [(torch.randn(N, K, device=dev) / K ** 0.5).bfloat16() for _ in range(nv)]
+        A = torch.randn(M, K, device=dev).bfloat16()
+        T.add("gemm_swiglu_bf16_tn", f"M{M} N{N} K{K}", (lambda: time_us(lambda i: _ffi.gemm_swiglu(A, Ws[i]), nv, iters)),
+              bytes_=2 * (N * K + M * K + M * N // 2), flops=2 * M * N * K, bound="hbm", note="gate|up projection with the SwiGLU epilogue")
+        del Ws
     for (N, K) in ((4096, 4096), (6144, 4096), (14336, 4096), (28672, 4096), (4096, 14336), (128256, 4096)):
         if MATCH and not any(wanted(o, f"M{M} N{N} K{K}") for o in ("gemm_bf16_tn", "addmm_bias_bf16_tn") for M in (1, 8, 16, 32, 128, 4096)):
             continue

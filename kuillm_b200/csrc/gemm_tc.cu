@@ -34,6 +34,7 @@ constexpr int kTcThreadsWide = 320;    // normal placement: one epilogue warpgro
 struct TcParams {
   uint32_t rowsP, rowsQ, K, batch;
   uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split;
+  uint32_t bandP;            // P tiles per rasterisation band
   int swapped, out_f32, epi;
   uint32_t M, N;
   float alpha, beta;
@@ -57,6 +58,20 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity) {
     if (global_ns() - t0 > 2000000000ull) return false;
   }
   return true;
+}
+
+// Tile t of a batch -> (P tile, Q tile).  Tiles are walked down the P axis in bands of p.bandP
+// P-tiles, all Q tiles of a band before the next band: the CTAs that run at the same time then
+// share a band of the P operand (32 tiles x 128 rows x K: it stays in L2 while the Q operand
+// streams past) instead of each re-reading a P panel that no longer fits the cache when the P
+// extent is large (prefill: 65536 rows).
+__device__ __forceinline__ void tile_coords(const TcParams& p, uint32_t t, uint32_t& tp, uint32_t& tq) {
+  const uint32_t band_tiles = p.bandP * p.tilesQ;
+  const uint32_t band = t / band_tiles, r = t % band_tiles;
+  const uint32_t first = band * p.bandP;
+  const uint32_t height = min(p.bandP, p.tilesP - first);      // the last band may be shorter
+  tp = first + r % height;
+  tq = r / height;
 }
 
 template <typename TIN>
@@ -144,7 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const uint32_t split = u % p.splits, tile = u / p.splits;
         const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
-        const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+        uint32_t tp, tq;
+        tile_coords(p, t, tp, tq);
         const uint32_t kb0 = split * p.kb_per_split;
         const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
@@ -224,7 +240,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     for (uint32_t u = blockIdx.x + group * gridDim.x; u < units && ok; u += kGroups * gridDim.x, acc_it += kGroups) {
       const uint32_t tile = u / p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
-      const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+      uint32_t tp, tq;
+        tile_coords(p, t, tp, tq);
       const uint32_t as = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1;
       if (!bounded_wait(&acc_full[as], aph)) { atomicExch(p.err, 4u); ok = false; break; }
       tc::tc_fence_after();
@@ -357,7 +374,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       const uint32_t quarter = warp & 3, lane_in_tile = quarter * 32 + lane;
       const uint32_t tile = blockIdx.x / p.splits, rank = blockIdx.x % p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
-      const uint32_t tp = t % p.tilesP, tq = t / p.tilesP;
+      uint32_t tp, tq;
+        tile_coords(p, t, tp, tq);
       const uint32_t row = tp * TBM + lane_in_tile, col0 = tq * BN;
       const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
       float* red = reinterpret_cast<float*>(smem);
@@ -556,6 +574,7 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   }
   TcParams p = {};
   p.K = a.K; p.batch = a.batch;
+  p.bandP = pl.tilesP < 32 ? pl.tilesP : 32;
   p.tilesP = pl.tilesP; p.tilesQ = pl.tilesQ; p.splits = pl.splits; p.kblocks = pl.kblocks; p.kb_per_split = pl.kb_per_split;
   p.swapped = pl.swapped ? 1 : 0; p.out_f32 = a.out_dtype == KUIOPS_F32 ? 1 : 0; p.epi = a.epilogue;
   p.M = a.M; p.N = a.N;

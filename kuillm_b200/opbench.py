@@ -215,6 +215,17 @@ def bench_gemm(T, iters):
                 us = (lambda: time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, Cin=bias, out=C), len(Ws), iters))
                 T.add("addmm_bias_bf16_tn", f"M{M} N{N} K{K}", us, bytes_=by, flops=fl, bound="tensor" if M >= 4096 else "hbm")
         del Ws
+    # the prefill shapes of the whole-model benchmark: 32 x 2048 rows at once
+    for (N, K) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+        M = 65536
+        if not wanted("gemm_bf16_tn", f"M{M} N{N} K{K}"):
+            continue
+        A = torch.randn(M, K, device=dev).bfloat16()
+        W = (torch.randn(N, K, device=dev) / K ** 0.5).bfloat16()
+        C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        T.add("gemm_bf16_tn", f"M{M} N{N} K{K}", (lambda: time_us(lambda i: _ffi.gemm(A, W, trans_b=True, out=C), 1, max(2, iters // 4))),
+              bytes_=2 * (M * K + N * K + M * N), flops=2 * M * N * K, bound="tensor")
+        del A, W, C
     if MATCH and not any(wanted(o, "") for o in ("mm_bf16_nn", "bmm_bf16", "mm_f32_simt")):
         return
     # row-major B (MN-major tiles), the aten.mm operand form

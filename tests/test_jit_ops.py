@@ -100,6 +100,19 @@ def test_gemm_swiglu_fused_epilogue(cuda, dtype, M):
     assert _ffi.tc_error() == 0
 
 
+def test_mm_many_row_tiles_walked_in_bands(cuda):
+    """More than 32 row tiles with a ragged last band and a ragged last tile: every output tile is
+    produced exactly once whatever order the tiles are walked in."""
+    from kuipy import _ffi
+    A, B = randn(4700, 192, dtype=torch.bfloat16), randn(520, 192, dtype=torch.bfloat16, seed=1)
+    out = _ffi.gemm(A, B, trans_b=True)
+    assert_close_ref_bar(out, O.mm(to_np(A), to_np(B).T), torch.bfloat16)
+    bias = randn(520, dtype=torch.bfloat16, seed=2)
+    out = _ffi.gemm(A, B, trans_b=True, Cin=bias)
+    assert_close_ref_bar(out, O.mm(to_np(A), to_np(B).T) + to_np(bias)[None, :], torch.bfloat16)
+    assert _ffi.tc_error() == 0
+
+
 # ---- softmax / mean / folds / topk -----------------------------------------------------------------
 @pytest.mark.parametrize("dtype", FLOATS)
 @pytest.mark.parametrize("shape", [(128, 64), (8, 5, 33), (3, 4100), (2, 40000)])

@@ -81,13 +81,8 @@ KUIOPS_API uint64_t    kuiops_launch_count(void);
 /* General entry every GEMM-shaped op lowers to.
  *   C[b] = alpha * A[b] x B[b] + beta * Cin[b]          (b = 0..batch-1)
  * A is [M,K] with leading dimension lda.  B is [K,N] with leading dimension ldb
- * when bit KUIOPS_GEMM_B_TRANS of trans_b is clear, or is stored as [N,K] (the
- * `weight.t()` view of a Linear layer) with leading dimension ldb when it is set.
- * Bit KUIOPS_GEMM_B_STATIC of trans_b declares that B is not written by any work
- * still in flight on `stream` (a weight): the weight-streaming placement then
- * requests its first B tiles before the previous kernel of the stream has
- * finished (programmatic dependent launch).  Leave it clear when B was produced
- * by an earlier call on the same stream.  Cin may be NULL (beta is
+ * when trans_b == 0, or is stored as [N,K] (the `weight.t()` view of a Linear
+ * layer) with leading dimension ldb when trans_b == 1.  Cin may be NULL (beta is
  * then ignored); ldcin == 0 means Cin is a length-N row vector broadcast over
  * rows (the fused bias of addmm).  Inputs are `dtype`; C is `out_dtype`
  * (same as dtype, or KUIOPS_F32).  Accumulation is always fp32.
@@ -102,8 +97,6 @@ KUIOPS_API uint64_t    kuiops_launch_count(void);
  * Replaces the launchers at wrapper_mm.cu.j2:15-19, wrapper_addmm.cu.j2:18-24
  * and wrapper_bmm.cu.j2:16-20. */
 #define KUIOPS_GEMM_COUNTER_BYTES 16384
-#define KUIOPS_GEMM_B_TRANS 1
-#define KUIOPS_GEMM_B_STATIC 2
 KUIOPS_API size_t kuiops_gemm_workspace_bytes(int dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
 KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
                 uint32_t M, uint32_t N, uint32_t K,
@@ -119,9 +112,7 @@ KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
  * epilogue applies the activation, so the [M, 2N] gate|up product never reaches memory.
  * W is [2N, K] (leading dimension ldw) with gate and up rows interleaved: row 2j = w_gate_j,
  * row 2j + 1 = w_up_j.  bf16 / f16 operands that meet the tensor-core alignment rules only
- * (KUIOPS_EUNSUPPORTED otherwise: run kuiops_gemm then kuiops_swiglu).  W is a weight prepared
- * ahead of time and is treated as KUIOPS_GEMM_B_STATIC: it must not be written by work still in
- * flight on `stream`.  The dispatcher sees this
+ * (KUIOPS_EUNSUPPORTED otherwise: run kuiops_gemm then kuiops_swiglu).  The dispatcher sees this
  * as mm, mm, silu, mul (kuipy/kuiops.py:158,166 of the reference); no reference counterpart. */
 KUIOPS_API int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, const void* W, int64_t ldw, void* Y, int64_t ldy,

@@ -25,13 +25,12 @@ inline cudaStream_t as_stream(kuiops_stream_t s) { return reinterpret_cast<cudaS
 // Kernels on the decode path are a few microseconds long, so launch latency and prologue are a
 // large share of a step.  A kernel launched with the programmatic-serialisation attribute may
 // begin (block scheduling, barrier / TMEM set-up) while its predecessor in the stream is still
-// running.  Such a kernel calls pdl_trigger() once the block has claimed everything it will ever
-// allocate (shared memory, TMEM) -- a dependent that parks on an SM can then never starve the grid
-// it is waiting for -- and pdl_wait() before it touches global memory that earlier work on the
-// stream may still write or read; pdl_wait() returns when the predecessor grid has completed and
-// its writes are visible.  Triggering before waiting is safe: the dependent's own pdl_wait()
-// returns only after this grid has completed, which is after this grid's wait, so completion
-// stays transitive along the stream.  Without the launch attribute both are no-ops.
+// running; it must execute pdl_wait() before it touches global memory, which blocks until the
+// predecessor grid has completed and its writes are visible.  pdl_trigger() tells the scheduler
+// that this block no longer minds dependents being scheduled next to it; it is called after the
+// block has claimed everything it will ever allocate (shared memory, TMEM), so a dependent that
+// parks on an SM can never starve the grid it is waiting for.  Without the launch attribute both
+// are no-ops.
 extern std::atomic<int> g_pdl_enabled;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -158,8 +158,8 @@ template <typename T, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residual, const T* __restrict__ w,
                float eps, T* __restrict__ y, T* residual_out) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   // WPR warps share a row (1, 2, 4 or 8), each thread keeps at most 4 vectors of it in registers
   constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
   __shared__ float red[8];
@@ -219,8 +219,8 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(uint64_t m, uint32_t n, const T* __restrict__ gu, T* __restrict__ y) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   constexpr int VN = Vec16<T>::N;
   const uint32_t nvec = n / VN;
   const uint64_t total = m * nvec;
@@ -245,8 +245,8 @@ __global__ void __launch_bounds__(256)
 rope_qkv_kernel(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, T* qkv, int64_t row_stride,
                 const int64_t* __restrict__ positions, float log2_theta, T* k_cache, T* v_cache,
                 uint64_t cache_cap, uint32_t rows_per_seq) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   constexpr int VN = Vec16<T>::N;
   const uint32_t half = d / 2, vec_per_half = half / VN;
   const uint32_t heads = hq + 2 * hk;                 // q heads, k heads, v heads
@@ -304,8 +304,8 @@ template <typename P>
 __global__ void __launch_bounds__(256)
 embedding_kernel(uint64_t rows, uint64_t width_p, uint64_t vocab, const P* __restrict__ table,
                  const int64_t* __restrict__ ids, P* __restrict__ out, int32_t* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const uint64_t total = rows * width_p;
   const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
   for (uint64_t t = gt; t < total; t += gs) {
@@ -322,8 +322,8 @@ embedding_kernel(uint64_t rows, uint64_t width_p, uint64_t vocab, const P* __res
 // x[i] += delta over int64 (position counters kept on the device between captured decode steps)
 __global__ void __launch_bounds__(256)
 add_i64_kernel(uint64_t len, long long* x, long long delta) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const uint64_t gs = uint64_t(gridDim.x) * blockDim.x;
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < len; i += gs) x[i] += delta;
 }

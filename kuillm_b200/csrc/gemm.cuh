@@ -9,7 +9,6 @@ struct GemmArgs {
   uint32_t batch, M, N, K;
   const void* A; int64_t lda, stride_a;
   const void* B; int64_t ldb, stride_b; int trans_b;
-  int b_static;   // B is not written by work still in flight on the stream (weights): its tiles may be fetched early
   const void* Cin; int64_t ldcin, stride_cin;
   float alpha, beta;
   void* C; int64_t ldc, stride_c;

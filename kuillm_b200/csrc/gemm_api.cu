@@ -64,15 +64,12 @@ int kuiops_gemm(int dtype, int out_dtype, uint32_t batch, uint32_t M, uint32_t N
   if (batch == 0 || M == 0 || N == 0 || K == 0) return KUIOPS_EINVAL;
   if (!A || !B || !C) return KUIOPS_EINVAL;
   if (lda < int64_t(K) || ldc < int64_t(N)) return KUIOPS_EINVAL;
-  const bool b_trans = (trans_b & KUIOPS_GEMM_B_TRANS) != 0;
-  if (trans_b & ~(KUIOPS_GEMM_B_TRANS | KUIOPS_GEMM_B_STATIC)) return KUIOPS_EINVAL;
-  if (ldb < int64_t(b_trans ? K : N)) return KUIOPS_EINVAL;
+  if (ldb < int64_t(trans_b ? K : N)) return KUIOPS_EINVAL;
   if (Cin && ldcin != 0 && ldcin < int64_t(N)) return KUIOPS_EINVAL;
-  GemmArgs a = {};
+  GemmArgs a;
   a.dtype = dtype; a.out_dtype = out_dtype; a.batch = batch; a.M = M; a.N = N; a.K = K;
   a.A = A; a.lda = lda; a.stride_a = stride_a;
-  a.B = B; a.ldb = ldb; a.stride_b = stride_b; a.trans_b = b_trans ? 1 : 0;
-  a.b_static = (trans_b & KUIOPS_GEMM_B_STATIC) ? 1 : 0;
+  a.B = B; a.ldb = ldb; a.stride_b = stride_b; a.trans_b = trans_b ? 1 : 0;
   a.Cin = Cin; a.ldcin = ldcin; a.stride_cin = stride_cin;
   a.alpha = alpha; a.beta = Cin ? beta : 0.f;
   a.C = C; a.ldc = ldc; a.stride_c = stride_c; a.epilogue = 0;
@@ -89,7 +86,7 @@ int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
   if (lda < int64_t(K) || ldw < int64_t(K) || ldy < int64_t(N) || N > 0x7FFFFFFFu) return KUIOPS_EINVAL;
   GemmArgs a = {};
   a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = 2 * N; a.K = K;
-  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1; a.b_static = 1;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
   a.alpha = 1.f; a.beta = 0.f; a.C = Y; a.ldc = ldy; a.epilogue = 1;
   if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
   return gemm_tc(a, workspace, workspace_bytes, as_stream(stream));

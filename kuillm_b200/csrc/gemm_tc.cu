@@ -36,7 +36,6 @@ struct TcParams {
   uint32_t tilesP, tilesQ, splits, kblocks, kb_per_split;
   uint32_t bandP;            // P tiles per rasterisation band
   int swapped, out_f32, epi;
-  int static_p;              // swapped placement: the P operand (weights) is not written by work in flight
   uint32_t M, N;
   float alpha, beta;
   const void* Cin; int64_t ldcin, stride_cin;
@@ -144,15 +143,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters; the
-  // operands may still be being written by the previous kernel in the stream.  Dependents may be
-  // scheduled from here on (this CTA holds everything it will ever allocate); every thread then
-  // waits for the previous grid before it touches global memory -- except the producer lane, which
-  // first starts the loads of an operand the caller declared constant (the weights of the swapped
-  // placement), so that weight tiles are already on their way while the previous kernel finishes.
+  // everything above touched only this CTA's shared memory, TMEM and the kernel parameters; the
+  // operands may still be being written by the previous kernel in the stream
+  pdl_wait();
   pdl_trigger();
-  const bool producer_lane = warp == 0 && lane == 0;
-  if (!producer_lane) pdl_wait();
 
   const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
   const uint32_t units = tiles_per_batch * p.batch * p.splits;
@@ -160,33 +154,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
     if (lane == 0) {
-      auto load_p = [&](uint32_t s, uint32_t kb, uint32_t tp, uint32_t b) {
-        unsigned char* ps = smem + s * STAGE_BYTES;
-        const int k0 = int(kb * TBK);
-        if (P_MN) {
-#pragma unroll
-          for (int j = 0; j < TBM / 64; ++j)
-            tc::tma_load_3d(ps + j * (TBK * 128), &tmapP, &full_bar[s], int(tp * TBM) + j * 64, k0, int(b));
-        } else {
-          tc::tma_load_3d(ps, &tmapP, &full_bar[s], k0, int(tp * TBM), int(b));
-        }
-      };
-      // stages whose P tile is requested before the grid dependency resolves (first unit only)
-      uint32_t npre = 0;
-      if (p.static_p && blockIdx.x < units) {
-        const uint32_t u = blockIdx.x, split = u % p.splits, tile = u / p.splits;
-        const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
-        uint32_t tp, tq;
-        tile_coords(p, t, tp, tq);
-        const uint32_t kb0 = split * p.kb_per_split;
-        const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
-        npre = min(uint32_t(STAGES), kb1 - kb0);
-        for (uint32_t i = 0; i < npre; ++i) {
-          tc::mbar_expect_tx(&full_bar[i], STAGE_BYTES);      // covers the Q tile that follows after the wait
-          load_p(i, kb0 + i, tp, b);
-        }
-      }
-      pdl_wait();
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -198,12 +165,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-          unsigned char* qs = smem + s * STAGE_BYTES + P_BYTES;
+          if (!bounded_wait(&empty_bar[s], ph ^ 1)) { atomicExch(p.err, 1u); ok = false; break; }
+          unsigned char* ps = smem + s * STAGE_BYTES;
+          unsigned char* qs = ps + P_BYTES;
+          tc::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           const int k0 = int(kb * TBK);
-          if (it >= npre) {
-            if (!bounded_wait(&empty_bar[s], ph ^ 1)) { atomicExch(p.err, 1u); ok = false; break; }
-            tc::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            load_p(s, kb, tp, b);
+          if (P_MN) {
+#pragma unroll
+            for (int j = 0; j < TBM / 64; ++j)
+              tc::tma_load_3d(ps + j * (TBK * 128), &tmapP, &full_bar[s], int(tp * TBM) + j * 64, k0, int(b));
+          } else {
+            tc::tma_load_3d(ps, &tmapP, &full_bar[s], k0, int(tp * TBM), int(b));
           }
           if (Q_MN) {
 #pragma unroll
@@ -605,7 +577,6 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.bandP = pl.tilesP < 32 ? pl.tilesP : 32;
   p.tilesP = pl.tilesP; p.tilesQ = pl.tilesQ; p.splits = pl.splits; p.kblocks = pl.kblocks; p.kb_per_split = pl.kb_per_split;
   p.swapped = pl.swapped ? 1 : 0; p.out_f32 = a.out_dtype == KUIOPS_F32 ? 1 : 0; p.epi = a.epilogue;
-  p.static_p = (pl.swapped && a.b_static) ? 1 : 0;
   p.M = a.M; p.N = a.N;
   p.rowsP = pl.swapped ? a.N : a.M; p.rowsQ = pl.swapped ? a.M : a.N;
   p.alpha = a.alpha; p.beta = a.beta;

@@ -120,8 +120,8 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
-  pdl_trigger();
   pdl_wait();          // Q, the cache and the key counts may still be being written by earlier kernels
+  pdl_trigger();
   // keys of this batch entry, optionally counted on the device
   uint32_t S = p.s;
   if (p.kv_lens) {

@@ -151,8 +151,8 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
-  pdl_trigger();
   pdl_wait();          // Q, K, V may still be being written by the previous kernel in the stream
+  pdl_trigger();
 
   if (warp < 4) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFlashRegsLow));

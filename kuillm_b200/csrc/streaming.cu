@@ -82,8 +82,8 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
   const uint32_t row = blockIdx.x / cluster_ctas;
   // peers must be running before their shared memory is written; arrive now, wait just before the push
   if (cluster_ctas > 1) cluster.barrier_arrive();
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   // slice boundaries in elements, multiples of VN so vector accesses stay aligned
   const uint32_t nv_total = (n + VN - 1) / VN;
   const uint32_t nv_per = (nv_total + cluster_ctas - 1) / cluster_ctas;
@@ -440,8 +440,8 @@ argmax_rows_kernel(uint64_t m, uint64_t n, const T* __restrict__ X, int64_t* __r
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
   if (cluster_ctas > 1) cluster.barrier_arrive();      // peers are running before their memory is written
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const uint64_t row = blockIdx.x / cluster_ctas;      // grid = m * cluster_ctas
   const T* x = X + row * n;
   // slice of this CTA in whole vectors

@@ -200,8 +200,8 @@ topk_rows_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X
   for (int i = tid; i < kBins; i += blockDim.x) sh.hist[i] = 0;
   if (tid == 0) { sh.sel_cnt = 0; sh.cand_cnt = 0; sh.bin = 0; sh.need = 0; sh.bin_cnt = 0; }
   __syncthreads();
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 
   // ---- pass 1: histogram of the top 11 key bits over the slice -------------------------
   // (uniform trip counts: hist_add is warp-collective; four 16-byte loads in flight per thread)
@@ -373,8 +373,8 @@ topk_sel_kernel(uint32_t m, uint32_t n, uint32_t k, const float* __restrict__ X,
   for (int i = tid; i < kBins; i += blockDim.x) sh.hist[i] = 0;
   if (tid == 0) { sh.sel_cnt = 0; sh.cand_cnt = 0; sh.bin = 0; sh.need = 0; sh.bin_cnt = 0; }
   __syncthreads();
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 
   // ---- pass 1: the largest value each thread meets (no atomics in the stream) -----------------
   // fmaxf skips NaNs, so a thread that saw NaNs reports a smaller value than its true maximum;

@@ -144,7 +144,7 @@ class Decoder:
                 resid = x
             else:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)      # resid += x ; h = norm(resid)
-            qkv = _ffi.gemm(h, L["wqkv"], trans_b=True, static_b=True)                  # [rows, (hq + 2 hk) * hd]
+            qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)                  # [rows, (hq + 2 hk) * hd]
             _ffi.rope_qkv(qkv, hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
             W = qkv.shape[1]
             q4 = qkv.as_strided((B, hq, seq, hd), (seq * W, hd, W, 1))
@@ -160,10 +160,10 @@ class Decoder:
                 k4 = self.k_cache[li][:, :, :end]
                 v4 = self.v_cache[li][:, :, :end]
             _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4, kv_lens=kv_lens)
-            o = self._allreduce(_ffi.gemm(attn, L["wo"], trans_b=True, static_b=True))
+            o = self._allreduce(_ffi.gemm(attn, L["wo"], trans_b=True))
             h2 = _ffi.rmsnorm(o, L["n2"], cfg.eps, residual=resid)
             act = _ffi.gemm_swiglu(h2, L["wgu"])
-            x = self._allreduce(_ffi.gemm(act, L["wd"], trans_b=True, static_b=True))
+            x = self._allreduce(_ffi.gemm(act, L["wd"], trans_b=True))
         self.length = end
         if last_only and seq > 1:
             # only the last position of each sequence feeds the vocabulary GEMM
@@ -171,7 +171,7 @@ class Decoder:
             x = _ffi.index(x, 0, [last])
             resid = _ffi.index(resid, 0, [last])
         hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
-        return _ffi.gemm(hf, self.lm_head, trans_b=True, static_b=True)                 # [B or rows, vocab]
+        return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab]
 
     def prefill(self, ids):
         B, S = ids.shape

@@ -207,11 +207,9 @@ def workspace(kind, device, nbytes):
 # --------------------------------------------------------------------------------------------
 # GEMM family
 # --------------------------------------------------------------------------------------------
-def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dtype=None, static_b=False):
+def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dtype=None):
     """C = alpha * A @ (B.T if trans_b else B) + beta * Cin.  A: [M,K] or [b,M,K].
-    B: [K,N] ([N,K] if trans_b), optionally batched.  Cin: [M,N], [b,M,N] or a length-N bias.
-    static_b: B is a weight that nothing in flight on the stream writes (its tiles may be fetched
-    before the previous kernel has finished)."""
+    B: [K,N] ([N,K] if trans_b), optionally batched.  Cin: [M,N], [b,M,N] or a length-N bias."""
     batched = A.dim() == 3
     if batched:
         bsz, M, K = A.shape
@@ -251,7 +249,7 @@ def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dt
     wsb = L.kuiops_gemm_workspace_bytes(code, bsz, M, N, K)
     ws = workspace("gemm", A.device, wsb)
     _check(L.kuiops_gemm(code, dtype_code(odt), bsz, M, N, K,
-                         A.data_ptr(), lda, sa, B.data_ptr(), ldb, sb, (1 if trans_b else 0) | (2 if static_b else 0),
+                         A.data_ptr(), lda, sa, B.data_ptr(), ldb, sb, 1 if trans_b else 0,
                          cin_p, ldcin, scin, float(alpha), float(beta),
                          out.data_ptr(), ldc, sc, ws.data_ptr(), ws.numel(), _stream()), "gemm")
     return out

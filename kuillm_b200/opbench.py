@@ -302,10 +302,10 @@ def bench_decode_breakdown(T, iters):
 
     def gemms():
         for L in dec.layers:
-            _ffi.gemm(x, L["wqkv"], trans_b=True, static_b=True)
-            _ffi.gemm(attn, L["wo"], trans_b=True, static_b=True)
+            _ffi.gemm(x, L["wqkv"], trans_b=True)
+            _ffi.gemm(attn, L["wo"], trans_b=True)
             _ffi.gemm_swiglu(x, L["wgu"])
-            _ffi.gemm(act, L["wd"], trans_b=True, static_b=True)
+            _ffi.gemm(act, L["wd"], trans_b=True)
 
     def attention():
         for li in range(cfg.n_layers):
@@ -320,7 +320,7 @@ def bench_decode_breakdown(T, iters):
     def head():
         h = _ffi.embedding(dec.embed, tok)
         hf = _ffi.rmsnorm(h, dec.norm_f, cfg.eps, residual=resid)
-        logits = _ffi.gemm(hf, dec.lm_head, trans_b=True, static_b=True)
+        logits = _ffi.gemm(hf, dec.lm_head, trans_b=True)
         _ffi.argmax_lastdim(logits)
 
     def step():

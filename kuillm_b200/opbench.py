@@ -1,6 +1,6 @@
 """Per-operator roofline table at the benchmark configurations.
 
-    python -m kuillm_b200.opbench [--only gemm,sdpa,stream,index,decode] [--iters 20] [--out file.jsonl]
+    python -m kuillm_b200.opbench [--only stream,index,decode,gemm,sdpa] [--iters 20] [--out file.jsonl]
 
 Each line: op, shape, microseconds per launch (CUDA events on the launching stream, after
 warm-up), the algorithmic bytes or flops of one launch, the achieved rate and its fraction of
@@ -11,6 +11,7 @@ working set exceeds the 126 MB L2.
 import argparse
 import json
 import sys
+import time
 from pathlib import Path
 
 import torch
@@ -215,7 +216,24 @@ def bench_gemm(T, iters):
                 us = (lambda: time_us(lambda i: _ffi.gemm(A, Ws[i % len(Ws)], trans_b=True, Cin=bias, out=C), len(Ws), iters))
                 T.add("addmm_bias_bf16_tn", f"M{M} N{N} K{K}", us, bytes_=by, flops=fl, bound="tensor" if M >= 4096 else "hbm")
         del Ws
-    # the prefill shapes of the whole-model benchmark: 32 x 2048 rows at once
+    if not MATCH or any(wanted(o, "") for o in ("mm_bf16_nn", "bmm_bf16", "mm_f32_simt")):
+        # row-major B (MN-major tiles), the aten.mm operand form
+        A = torch.randn(4096, 4096, device=dev).bfloat16()
+        Bs = [(torch.randn(4096, 4096, device=dev) / 64).bfloat16() for _ in range(8)]
+        T.add("mm_bf16_nn", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A, Bs[i % 8]), 8, iters)), flops=2 * 4096 ** 3,
+              bytes_=3 * 2 * 4096 ** 2, bound="tensor")
+        A3 = [torch.randn(32, 4096, 128, device=dev).bfloat16() for _ in range(4)]
+        B3 = [(torch.randn(32, 128, 4096, device=dev) / 11.3).bfloat16() for _ in range(4)]
+        T.add("bmm_bf16", "32 x 4096x128x4096", (lambda: time_us(lambda i: _ffi.bmm(A3[i % 4], B3[i % 4]), 4, iters)),
+              bytes_=2 * 32 * (2 * 4096 * 128 + 4096 * 4096), flops=2 * 32 * 4096 * 128 * 4096, bound="hbm")
+        A32 = torch.randn(4096, 4096, device=dev)
+        B32 = torch.randn(4096, 4096, device=dev) / 64
+        T.add("mm_f32_simt", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A32, B32), 1, max(3, iters // 4))), flops=2 * 4096 ** 3,
+              bytes_=3 * 4 * 4096 ** 2, bound="tensor", note="SIMT fp32 path; fraction is against the bf16 tensor peak")
+
+        del A, Bs, A3, B3, A32, B32
+    # the prefill shapes of the whole-model benchmark: 32 x 2048 rows at once (last: tens of
+    # milliseconds of dense tensor work heat the part and would depress whatever is timed next)
     for (N, K) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
         M = 65536
         if not wanted("gemm_bf16_tn", f"M{M} N{N} K{K}"):
@@ -226,26 +244,36 @@ def bench_gemm(T, iters):
         T.add("gemm_bf16_tn", f"M{M} N{N} K{K}", (lambda: time_us(lambda i: _ffi.gemm(A, W, trans_b=True, out=C), 1, max(2, iters // 4))),
               bytes_=2 * (M * K + N * K + M * N), flops=2 * M * N * K, bound="tensor")
         del A, W, C
-    if MATCH and not any(wanted(o, "") for o in ("mm_bf16_nn", "bmm_bf16", "mm_f32_simt")):
-        return
-    # row-major B (MN-major tiles), the aten.mm operand form
-    A = torch.randn(4096, 4096, device=dev).bfloat16()
-    Bs = [(torch.randn(4096, 4096, device=dev) / 64).bfloat16() for _ in range(8)]
-    T.add("mm_bf16_nn", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A, Bs[i % 8]), 8, iters)), flops=2 * 4096 ** 3,
-          bytes_=3 * 2 * 4096 ** 2, bound="tensor")
-    A3 = [torch.randn(32, 4096, 128, device=dev).bfloat16() for _ in range(4)]
-    B3 = [(torch.randn(32, 128, 4096, device=dev) / 11.3).bfloat16() for _ in range(4)]
-    T.add("bmm_bf16", "32 x 4096x128x4096", (lambda: time_us(lambda i: _ffi.bmm(A3[i % 4], B3[i % 4]), 4, iters)),
-          bytes_=2 * 32 * (2 * 4096 * 128 + 4096 * 4096), flops=2 * 32 * 4096 * 128 * 4096, bound="hbm")
-    A32 = torch.randn(4096, 4096, device=dev)
-    B32 = torch.randn(4096, 4096, device=dev) / 64
-    T.add("mm_f32_simt", "M4096 N4096 K4096", (lambda: time_us(lambda i: _ffi.mm(A32, B32), 1, max(3, iters // 4))), flops=2 * 4096 ** 3,
-          bytes_=3 * 4 * 4096 ** 2, bound="tensor", note="SIMT fp32 path; fraction is against the bf16 tensor peak")
+
+
+def _sdpa_decode_cases(T, iters, hkv):
+    dev = "cuda"
+    D = 128
+    for S in (4096, 32768):
+        B, H = 64, 32
+        if not wanted("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}"):
+            continue
+        kv_bytes = 2 * B * hkv * S * D * 2
+        nv = variants_for(kv_bytes) if kv_bytes < (8 << 30) else 1
+        nv = min(nv, 2)
+        Q = torch.randn(B, H, 1, D, device=dev).bfloat16()
+        Ks = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
+        Vs = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
+        O = torch.empty_like(Q)
+        us = (lambda: time_us(lambda i: _ffi.sdpa(Q, Ks[i], Vs[i], is_causal=True, need_lse=False, out=O), nv, max(3, iters // 2)))
+        T.add("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}", us, bytes_=kv_bytes + 2 * B * H * D * 2 * 2,
+              flops=4 * B * H * S * D, bound="hbm")
+        del Ks, Vs
+
 
 
 def bench_sdpa(T, iters):
     dev = "cuda"
     D = 128
+    # decode (memory bound) first: seconds of dense tensor work in the prefill cases heat the
+    # part and would depress whatever is timed right after them
+    for hkv in (32, 8):
+        _sdpa_decode_cases(T, iters, hkv)
     for hkv in (32, 8):
         for S in (1024, 4096, 16384):
             B, H = 8, 32
@@ -260,21 +288,6 @@ def bench_sdpa(T, iters):
             T.add("sdpa_prefill_causal_bf16", f"B{B} Hq{H} Hkv{hkv} S{S} D{D}", us, flops=2 * B * H * S * S * D,
                   bytes_=2 * (2 * B * H * S * D + 2 * B * hkv * S * D), bound="tensor")
             del Q, K, V, O
-        for S in (4096, 32768):
-            B, H = 64, 32
-            if not wanted("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}"):
-                continue
-            kv_bytes = 2 * B * hkv * S * D * 2
-            nv = variants_for(kv_bytes) if kv_bytes < (8 << 30) else 1
-            nv = min(nv, 2)
-            Q = torch.randn(B, H, 1, D, device=dev).bfloat16()
-            Ks = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
-            Vs = [torch.randn(B, hkv, S, D, device=dev).bfloat16() for _ in range(nv)]
-            O = torch.empty_like(Q)
-            us = (lambda: time_us(lambda i: _ffi.sdpa(Q, Ks[i], Vs[i], is_causal=True, need_lse=False, out=O), nv, max(3, iters // 2)))
-            T.add("sdpa_decode_bf16", f"B{B} Hq{H} Hkv{hkv} Skv{S} D{D}", us, bytes_=kv_bytes + 2 * B * H * D * 2 * 2,
-                  flops=4 * B * H * S * D, bound="hbm")
-            del Ks, Vs
 
 
 def bench_decode_breakdown(T, iters):
@@ -348,7 +361,7 @@ def bench_decode_breakdown(T, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="stream,index,gemm,sdpa")
+    ap.add_argument("--only", default="stream,index,decode,gemm,sdpa")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
     ap.add_argument("--match", default="", help='only cases whose "op shape" text contains this')
@@ -362,6 +375,8 @@ def main():
         Path(a.out).write_text("")
     T = Table(a.out)
     for name in a.only.split(","):
+        torch.cuda.synchronize()
+        time.sleep(2.0)          # let the part cool between sections: the dense cases run at the power cap
         {"stream": bench_stream, "index": bench_index, "gemm": bench_gemm, "sdpa": bench_sdpa,
          "decode": bench_decode_breakdown}[name](T, a.iters)
         torch.cuda.empty_cache()

@@ -184,6 +184,9 @@ def run_ours(args):
     cfg = DecoderConfig(**cfg_kw) if cfg_kw else DecoderConfig.llama3_8b()
     dec = Decoder(cfg, device=dev, seed=0, tp_rank=rank if tp > 1 else 0, tp_size=tp)
     dec.alloc_cache(batch, prompt + new)
+    fused = tp > 1 and args.allreduce == "fused"
+    if fused:
+        dec.enable_fused_allreduce(batch)      # decode steps only (batch rows); the prefill keeps NCCL
     g = torch.Generator().manual_seed(1000 + (0 if tp > 1 else rank))
     ids_host = torch.randint(0, cfg.vocab, (batch, prompt), generator=g).pin_memory()
     ids_dev = ids_host.to(dev)
@@ -311,6 +314,7 @@ def run_ours(args):
             "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "global_batch": batch * replicas, "prompt_len": prompt, "new_tokens": new,
                        "parallelism": (f"tp{tp}" if tp > 1 else f"dp{world}"), "decode_cuda_graph": use_graph,
+                       **({"decode_allreduce": "fused into the GEMM epilogue and the next norm (peer stores)" if fused else "nccl"} if tp > 1 else {}),
                        "prefill_tok_s": batch * prompt * replicas / (prefill_ms * 1e-3),
                        "decode_tok_s": batch * (new - 1) * replicas / (decode_ms * 1e-3),
                        "prefill_ms": prefill_ms, "decode_ms_per_token": decode_ms / (new - 1),
@@ -346,6 +350,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--parallel", default="dp", choices=["dp", "tp"])
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="tensor parallel only: how the decode step sums the row-split projections")
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every decode kernel from the host instead of replaying a CUDA graph")

@@ -118,6 +118,45 @@ KUIOPS_API int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, const void* W, int64_t ldw, void* Y, int64_t ldy,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
 
+/* Tensor-parallel row-split GEMM fused with the first half of its all-reduce (decode shapes,
+ * M <= 128, bf16 / f16): rank `rank` of `n_ranks` computes its partial product A x B (B as in
+ * kuiops_gemm: [K,N], or [N,K] when trans_b) and the epilogue stores it, through peer pointers,
+ * into the receive area of EVERY rank (its own included) instead of a local C:
+ *     peer_base[r] + ((epoch & 1) * n_ranks + rank) * slot_bytes      M x N elements, row-major
+ * When the last CTA has finished, flag word
+ *     peer_base[r] + flags_offset + ((epoch & 1) * n_ranks + rank) * 4
+ * of every rank is set to epoch + 1 (release, system scope).  `peer_base` is a HOST array of
+ * n_ranks device addresses: the same symmetric allocation as mapped into this process for each
+ * rank (16-byte aligned; flags_offset >= 2 * n_ranks * slot_bytes; zero-filled once before the
+ * first launch).  `epoch` is this rank's device word that kuiops_rmsnorm_gather advances after it
+ * has consumed the partials; `ticket` a zeroed device word the kernel leaves zero.  Producer and
+ * consumer alternate on the stream, so two halves of slots are enough: a rank cannot push epoch
+ * e + 2 before it has consumed e + 1, which every peer pushed only after consuming e.
+ * The collective is plain peer stores over NVLink; no library call, no multicast.
+ * No counterpart in the reference (it has no multi-GPU path); the single-rank form is
+ * wrapper_mm.cu.j2:15-19. */
+#define KUIOPS_MAX_PEERS 8
+KUIOPS_API int kuiops_gemm_push(int dtype, uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, const void* B, int64_t ldb, int trans_b,
+                uint32_t n_ranks, uint32_t rank, const uint64_t* peer_base,
+                uint64_t slot_bytes, uint64_t flags_offset,
+                const uint32_t* epoch, uint32_t* ticket, kuiops_stream_t stream);
+
+/* Second half of that all-reduce, fused with the residual add and the RMSNorm that follow a
+ * row-split projection in a decoder layer: waits until the flags of all `n_ranks` ranks for the
+ * current epoch have arrived in this rank's receive area (each wait bounded to about 2 s; on
+ * expiry the error word read by kuiops_debug_tc_error is set to 30 and the kernel continues),
+ * then   x = sum_r slot(epoch & 1, r)   (fp32, rank order, rounded to dtype),
+ *        residual_out = x + residual,   y = rmsnorm(residual_out) * weight,
+ * and advances `epoch` by one.  `recv_base` is this rank's own receive area (peer_base[rank] of
+ * kuiops_gemm_push), `ticket` a zeroed device word of its own.  bf16 / f16.
+ * No counterpart in the reference. */
+KUIOPS_API int kuiops_rmsnorm_gather(int dtype, uint64_t m, uint32_t n, uint32_t n_ranks,
+                const void* recv_base, uint64_t slot_bytes, uint64_t flags_offset,
+                uint32_t* epoch, uint32_t* ticket,
+                const void* residual, const void* weight, float eps,
+                void* y, void* residual_out, kuiops_stream_t stream);
+
 /* aten.mm: C[M,N] = A[M,K] x B[K,N], all dense row-major.
  * Reference launcher: (u32 M, u32 N, u32 K, in* A, in* B, out* C), kuiops/mm/wrapper_mm.cu.j2:15-19.
  * The reference's bf16 kernel writes fp32 and the Python side casts

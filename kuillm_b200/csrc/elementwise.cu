@@ -1,6 +1,7 @@
 // Elementwise maps and the fused decoder-layer helpers built from them.
 // One launch per map, 16-byte accesses, grid sized in whole multiples of the SM count.
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace kuiops {
 
@@ -215,6 +216,115 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
   }
 }
 
+// RMSNorm whose input row is the sum of the partial rows that the ranks of a tensor-parallel group
+// pushed into this rank's receive area (kuiops_gemm_push): the second half of the all-reduce, fused
+// with the residual add and the normalisation that follow it.
+//   x[row] = round_T( sum over r of slot(epoch & 1, r)[row] )   (fp32 sum in rank order)
+//   resid_out[row] = x[row] + residual[row];  y[row] = rmsnorm(resid_out[row]) * w
+// Every thread first waits (at most ~2 s, then the error word is set and the kernel carries on) until
+// flag (epoch & 1, r) of every rank r has reached epoch + 1.  The last CTA advances the epoch.
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t elementwise_global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <typename T, int WPR>
+__global__ void __launch_bounds__(256)
+rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned char* recv_base, uint64_t slot_bytes,
+                      uint64_t flags_offset, unsigned int* epoch, unsigned int* ticket, unsigned int* err,
+                      const T* residual, const T* __restrict__ w, float eps, T* __restrict__ y, T* residual_out) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
+  __shared__ float red[8];
+  const unsigned int e = *reinterpret_cast<volatile unsigned int*>(epoch);
+  {
+    const unsigned int* flags = reinterpret_cast<const unsigned int*>(recv_base + flags_offset) + size_t(e & 1u) * n_ranks;
+    bool ok = true;
+    uint64_t t0 = 0;
+    for (uint32_t r = 0; r < n_ranks && ok; ++r) {
+      while (ld_acquire_sys(flags + r) < e + 1u) {
+        if (t0 == 0) t0 = elementwise_global_ns();
+        if (elementwise_global_ns() - t0 > 2000000000ull) { ok = false; break; }
+      }
+    }
+    if (!ok && threadIdx.x == 0) atomicExch(err, 30u);
+  }
+  const unsigned char* slots = recv_base + size_t(e & 1u) * n_ranks * slot_bytes;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row_in_block = warp / WPR, wsub = warp % WPR;
+  const uint32_t nvec = n / VN;
+  for (uint64_t base = uint64_t(blockIdx.x) * RPB; base < m; base += uint64_t(gridDim.x) * RPB) {
+    const uint64_t row = base + row_in_block;
+    const bool valid = row < m;
+    Vec16<T> c[VECS];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+      const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+      if (valid && v < nvec) {
+        float acc[VN];
+#pragma unroll
+        for (int k = 0; k < VN; ++k) acc[k] = 0.f;
+        for (uint32_t r = 0; r < n_ranks; ++r) {
+          // written by another GPU: read through L2, never from a stale L1 line
+          const int4 raw = __ldcg(reinterpret_cast<const int4*>(slots + r * slot_bytes + (row * n + size_t(v) * VN) * sizeof(T)));
+          const Vec16<T>& pv = *reinterpret_cast<const Vec16<T>*>(&raw);
+#pragma unroll
+          for (int k = 0; k < VN; ++k) acc[k] += ElemTraits<T>::to_f(pv.v[k]);
+        }
+        const Vec16<T> res = ld16(residual + row * n + size_t(v) * VN);
+#pragma unroll
+        for (int k = 0; k < VN; ++k) {
+          const float x = ElemTraits<T>::to_f(ElemTraits<T>::from_f(acc[k]));      // the all-reduce result, rounded as a stored tensor would be
+          c[i].v[k] = ElemTraits<T>::from_f(x + ElemTraits<T>::to_f(res.v[k]));
+        }
+        st16(residual_out + row * n + size_t(v) * VN, c[i]);
+#pragma unroll
+        for (int k = 0; k < VN; ++k) { float f = ElemTraits<T>::to_f(c[i].v[k]); ss += f * f; }
+      }
+    }
+    ss = warp_sum(ss);
+    if (WPR > 1) {
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < WPR; ++k) ss += red[row_in_block * WPR + k];
+      __syncthreads();
+    }
+    const float rs = rsqrtf(ss / float(n) + eps);
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+      const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+      if (valid && v < nvec) {
+        Vec16<T> wv = ld16(w + size_t(v) * VN), o;
+#pragma unroll
+        for (int k = 0; k < VN; ++k) {
+          float nx = ElemTraits<T>::to_f(ElemTraits<T>::from_f(ElemTraits<T>::to_f(c[i].v[k]) * rs));
+          o.v[k] = ElemTraits<T>::from_f(nx * ElemTraits<T>::to_f(wv.v[k]));
+        }
+        st16(y + row * n + size_t(v) * VN, o);
+      }
+    }
+  }
+  // every CTA read the epoch before it got here; the last one moves it on for the next exchange
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(ticket, 1u);
+    if (t == gridDim.x - 1) {
+      atomicExch(ticket, 0u);
+      atomicAdd(epoch, 1u);
+    }
+  }
+}
+
 // silu(gate) * up over a fused [m, 2n] gate|up activation
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -418,6 +528,47 @@ static int rmsnorm_launch(uint64_t m, uint32_t n, const void* x, const void* res
   if (nvec <= 1024) return launch_pdl(rmsnorm_kernel<T, 8>, dim3(stream_grid(m, 1, 16)), dim3(256), 0, st, m, n, X, R, W, eps, Y, RO);
   return KUIOPS_EUNSUPPORTED;
 }
+
+template <typename T>
+static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const void* base, uint64_t slot_bytes, uint64_t flags_offset,
+                                 uint32_t* epoch, uint32_t* ticket, const void* res, const void* w, float eps, void* y,
+                                 void* res_out, cudaStream_t st) {
+  constexpr int VN = Vec16<T>::N;
+  if (m == 0 || n == 0 || !base || !epoch || !ticket || !res || !w || !y || !res_out) return KUIOPS_EINVAL;
+  if (n_ranks < 2 || n_ranks > KUIOPS_MAX_PEERS) return KUIOPS_EINVAL;
+  if (slot_bytes < m * n * sizeof(T) || (slot_bytes & 15u) || (flags_offset & 3u) || flags_offset < 2ull * n_ranks * slot_bytes)
+    return KUIOPS_EINVAL;
+  if (n % VN || !aligned16(base) || !aligned16(res) || !aligned16(w) || !aligned16(y) || !aligned16(res_out)) return KUIOPS_EUNSUPPORTED;
+  unsigned int* err = tc_error_word_device();
+  if (!err) return KUIOPS_ELAUNCH;
+  const uint32_t nvec = n / VN;
+  auto B = static_cast<const unsigned char*>(base);
+  auto R = static_cast<const T*>(res); auto W = static_cast<const T*>(w);
+  auto Y = static_cast<T*>(y); auto RO = static_cast<T*>(res_out);
+#define KUIOPS_RG(WPRV, RPBV) \
+  return launch_pdl(rmsnorm_gather_kernel<T, WPRV>, dim3(stream_grid(m, RPBV, 16)), dim3(256), 0, st, m, n, n_ranks, B, slot_bytes, \
+                    flags_offset, epoch, ticket, err, R, W, eps, Y, RO)
+  if (nvec <= 128) KUIOPS_RG(1, 8);
+  if (nvec <= 256) KUIOPS_RG(2, 4);
+  if (nvec <= 512) KUIOPS_RG(4, 2);
+  if (nvec <= 1024) KUIOPS_RG(8, 1);
+#undef KUIOPS_RG
+  return KUIOPS_EUNSUPPORTED;
+}
+
+extern "C" {
+int kuiops_rmsnorm_gather(int dtype, uint64_t m, uint32_t n, uint32_t n_ranks, const void* recv_base, uint64_t slot_bytes,
+                          uint64_t flags_offset, uint32_t* epoch, uint32_t* ticket, const void* residual, const void* weight,
+                          float eps, void* y, void* residual_out, kuiops_stream_t s) {
+  switch (dtype) {
+    case KUIOPS_BF16: return rmsnorm_gather_launch<__nv_bfloat16>(m, n, n_ranks, recv_base, slot_bytes, flags_offset, epoch, ticket,
+                                                                  residual, weight, eps, y, residual_out, as_stream(s));
+    case KUIOPS_F16: return rmsnorm_gather_launch<__half>(m, n, n_ranks, recv_base, slot_bytes, flags_offset, epoch, ticket,
+                                                          residual, weight, eps, y, residual_out, as_stream(s));
+  }
+  return KUIOPS_EUNSUPPORTED;
+}
+}  // extern "C"
 
 extern "C" {
 int kuiops_rmsnorm(int dtype, uint64_t m, uint32_t n, const void* x, const void* residual, const void* weight,

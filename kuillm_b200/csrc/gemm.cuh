@@ -4,6 +4,15 @@
 
 namespace kuiops {
 
+// Tensor-parallel "push" epilogue: see kuiops_gemm_push.
+struct GemmPush {
+  uint32_t n_ranks, rank;
+  uint64_t peer_base[KUIOPS_MAX_PEERS];
+  uint64_t slot_bytes, flags_offset;
+  const unsigned int* epoch;
+  unsigned int* ticket;
+};
+
 struct GemmArgs {
   int dtype, out_dtype;
   uint32_t batch, M, N, K;
@@ -12,6 +21,7 @@ struct GemmArgs {
   const void* Cin; int64_t ldcin, stride_cin;
   float alpha, beta;
   void* C; int64_t ldc, stride_c;
+  const GemmPush* push;   // non-null: partial sums go to every rank's receive area instead of C
   int epilogue;   // 0: C = alpha*acc + beta*Cin;  1: C[m, j] = silu(acc[m, 2j]) * acc[m, 2j+1] (gate/up rows interleaved in B)
 };
 

@@ -41,6 +41,13 @@ struct TcParams {
   const void* Cin; int64_t ldcin, stride_cin;
   void* C; int64_t ldc, stride_c;
   unsigned int* err;
+  // "push" epilogue (tensor parallel, swapped placement only): the result is a partial sum that
+  // goes into slot (epoch & 1, my_rank) of every rank's receive area instead of C
+  uint32_t n_ranks, my_rank;          // n_ranks == 0: ordinary epilogue
+  uint64_t peer_base[KUIOPS_MAX_PEERS];
+  uint64_t slot_bytes, flags_offset;
+  const unsigned int* epoch;          // device word, advanced by the consumer of the partials
+  unsigned int* ticket;               // device word, zero between launches
 };
 
 __device__ unsigned int g_tc_error = 0;
@@ -75,11 +82,20 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, uint32_t t, uint3
 }
 
 template <typename TIN>
-__device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32_t lane_row, uint32_t col, float acc) {
+__device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32_t lane_row, uint32_t col, float acc,
+                                           uint64_t push_off = 0) {
   const uint32_t m = p.swapped ? col : lane_row;
   const uint32_t n = p.swapped ? lane_row : col;
   if (m >= p.M || n >= p.N) return;
   float v = p.alpha * acc;
+  if (p.n_ranks) {
+    // same element of the (epoch & 1, my_rank) slot on every rank, this one included
+    const uint64_t off = push_off + (size_t(m) * p.N + n) * sizeof(TIN);
+    const TIN val = ElemTraits<TIN>::from_f(v);
+#pragma unroll 1
+    for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<TIN*>(p.peer_base[r] + off) = val;
+    return;
+  }
   if (p.Cin) {
     const TIN* cin = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin;
     v += p.beta * ElemTraits<TIN>::to_f(cin[size_t(m) * p.ldcin + n]);
@@ -147,6 +163,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   // operands may still be being written by the previous kernel in the stream
   pdl_wait();
   pdl_trigger();
+  // push epilogue: which half of the double-buffered receive areas this launch writes
+  unsigned int push_epoch = 0;
+  uint64_t push_off = 0;
+  if (p.n_ranks) {
+    push_epoch = *reinterpret_cast<const volatile unsigned int*>(p.epoch);
+    push_off = (uint64_t(push_epoch & 1u) * p.n_ranks + p.my_rank) * p.slot_bytes;
+  }
 
   const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
   const uint32_t units = tiles_per_batch * p.batch * p.splits;
@@ -340,7 +363,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             st16(dst + 8, o1);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j]);
+            for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j], push_off);
           }
         }
         tc::tc_fence_before();
@@ -390,15 +413,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 #pragma unroll
         for (int s2 = 1; s2 < 8; ++s2) sum += part[s2];
         if (p.epi == 1) store_swiglu_swapped<TIN>(p, row, col0 + c, sum);
-        else store_elem<TIN>(p, b, row, col0 + c, sum);
+        else store_elem<TIN>(p, b, row, col0 + c, sum, push_off);
       }
     }
     __syncwarp();
     cluster.sync();          // nobody's shared memory goes away while a peer may still read it
   }
   // ------------------------------ teardown ------------------------------------------------
+  if (p.n_ranks) __threadfence_system();        // this thread's pushed partials are visible system-wide ...
   tc::tc_fence_before();
   __syncthreads();
+  if (p.n_ranks && threadIdx.x == 0) {
+    // ... before this CTA takes its ticket; the CTA that draws the last one publishes the epoch
+    // to every rank (flag (epoch & 1, my_rank) = epoch + 1), after a fence that orders all the
+    // partials it has observed complete before the flags
+    __threadfence_system();
+    const unsigned int t = atomicAdd(p.ticket, 1u);
+    if (t == gridDim.x - 1) {
+      atomicExch(p.ticket, 0u);
+      __threadfence_system();
+      const uint64_t foff = p.flags_offset + (uint64_t(push_epoch & 1u) * p.n_ranks + p.my_rank) * sizeof(unsigned int);
+      for (uint32_t r = 0; r < p.n_ranks; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_base[r] + foff), "r"(push_epoch + 1u) : "memory");
+    }
+  }
   if (warp == 1) {
     __syncwarp();                      // the allocator instructions want the whole warp converged
     tc::tc_fence_after();
@@ -584,6 +622,13 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.C = a.C; p.ldc = a.ldc; p.stride_c = a.stride_c;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
+  if (a.push) {
+    if (!pl.swapped || a.epilogue != 0 || a.batch != 1) return KUIOPS_EUNSUPPORTED;
+    p.n_ranks = a.push->n_ranks; p.my_rank = a.push->rank;
+    for (uint32_t r = 0; r < p.n_ranks; ++r) p.peer_base[r] = a.push->peer_base[r];
+    p.slot_bytes = a.push->slot_bytes; p.flags_offset = a.push->flags_offset;
+    p.epoch = a.push->epoch; p.ticket = a.push->ticket;
+  }
   const uint64_t units = uint64_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits;
   if (units >= (1ull << 31)) return KUIOPS_EUNSUPPORTED;
   const bool b_mn = !a.trans_b;

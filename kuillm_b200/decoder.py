@@ -12,7 +12,9 @@ CUDA-graph capture of the decode step.
 
 Parallel forms: batch data-parallel is "one Decoder per rank on its slice of the batch, no
 collective"; tensor-parallel splits QKV / gate-up by output columns and O / down by input rows
-across ``tp`` ranks with one all-reduce after each row-split GEMM (two per layer).
+across ``tp`` ranks with one all-reduce after each row-split GEMM (two per layer): NCCL, or for
+decode-sized steps the fused form (``enable_fused_allreduce``) in which the GEMM epilogue stores
+its partial product into every rank's memory and the following RMSNorm sums the partials.
 """
 from dataclasses import dataclass
 
@@ -114,6 +116,7 @@ class Decoder:
         self.k_cache = self.v_cache = None
         self.cap = 0
         self.length = 0
+        self.exchange, self.exchange_rows = None, 0
 
     # ---- state ---------------------------------------------------------------------------
     def alloc_cache(self, batch, capacity):
@@ -121,6 +124,17 @@ class Decoder:
         self.k_cache = torch.zeros(shape, device=self.device, dtype=self.cfg.dtype)
         self.v_cache = torch.zeros(shape, device=self.device, dtype=self.cfg.dtype)
         self.cap, self.length, self.batch = capacity, 0, batch
+
+    def enable_fused_allreduce(self, max_rows=128):
+        """Tensor-parallel groups only: map every rank's receive area (kuillm_b200.peer) so that steps
+        of at most `max_rows` rows replace the two NCCL all-reduces of a layer by the push epilogue
+        of the row-split GEMMs plus the gathering norm.  Larger steps (prefill) keep NCCL."""
+        if self.tp_size <= 1:
+            return None
+        from .peer import PeerExchange
+        self.exchange_rows = min(int(max_rows), 128)
+        self.exchange = PeerExchange(self.tp_group, self.device, self.exchange_rows, self.cfg.d_model, self.cfg.dtype)
+        return self.exchange
 
     def _allreduce(self, t):
         if self.tp_size > 1:
@@ -138,10 +152,15 @@ class Decoder:
         x = _ffi.embedding(self.embed, ids.reshape(-1))                  # [rows, d]
         resid = None
         start, end = self.length, self.length + seq
+        # decode-sized steps of a tensor-parallel group: the row-split projections push their partial
+        # products straight into every rank's receive area and the norm that follows sums them
+        ex = self.exchange if (self.tp_size > 1 and self.exchange is not None and rows <= self.exchange_rows) else None
         for li, L in enumerate(self.layers):
             if resid is None:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps)
                 resid = x
+            elif ex is not None:
+                h = _ffi.rmsnorm_gather(ex, rows, L["n1"], cfg.eps, resid)
             else:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)      # resid += x ; h = norm(resid)
             qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)                  # [rows, (hq + 2 hk) * hd]
@@ -160,6 +179,12 @@ class Decoder:
                 k4 = self.k_cache[li][:, :, :end]
                 v4 = self.v_cache[li][:, :, :end]
             _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4, kv_lens=kv_lens)
+            if ex is not None:
+                _ffi.gemm_push(attn, L["wo"], trans_b=True, exchange=ex)
+                h2 = _ffi.rmsnorm_gather(ex, rows, L["n2"], cfg.eps, resid)
+                act = _ffi.gemm_swiglu(h2, L["wgu"])
+                _ffi.gemm_push(act, L["wd"], trans_b=True, exchange=ex)   # summed by the next norm
+                continue
             o = self._allreduce(_ffi.gemm(attn, L["wo"], trans_b=True))
             h2 = _ffi.rmsnorm(o, L["n2"], cfg.eps, residual=resid)
             act = _ffi.gemm_swiglu(h2, L["wgu"])
@@ -170,7 +195,10 @@ class Decoder:
             last = torch.arange(seq - 1, rows, seq, device=self.device)
             x = _ffi.index(x, 0, [last])
             resid = _ffi.index(resid, 0, [last])
-        hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
+        if ex is not None:
+            hf = _ffi.rmsnorm_gather(ex, rows, self.norm_f, cfg.eps, resid)
+        else:
+            hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
         return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab]
 
     def prefill(self, ids):

@@ -1,6 +1,7 @@
 """Tensor-parallel and data-parallel decoder on two GPUs (skipped with fewer): the TP logits must
 match the single-GPU logits of the same weights within the bf16 bar, with exactly two all-reduces
-per layer; DP ranks reproduce their slice of the single-GPU result bit for bit."""
+per layer; the fused GEMM + all-reduce form must reproduce the NCCL form bit for bit without any
+NCCL call; DP ranks reproduce their slice of the single-GPU result bit for bit."""
 import os
 import socket
 
@@ -52,6 +53,28 @@ def _tp_worker(rank, size, port, q):
     dist.all_reduce = real
     rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
     ok_tp = rel(out, ref) < 3e-2 and rel(out2, ref2) < 3e-2 and n_calls == 2 * cfg.n_layers
+    # the fused form: row-split GEMMs push their partials into both ranks' memory, the next norm sums
+    # them; no NCCL call on that path, and with two ranks the sum rounds exactly as NCCL's does
+    from kuipy import _ffi
+    tpf = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
+    tpf.alloc_cache(4, 24)
+    tpf.enable_fused_allreduce(128)
+    calls[0] = 0
+    dist.all_reduce = counted
+    f1 = tpf.prefill(ids)                     # 64 rows: small enough for the fused path
+    tok = ref_tok
+    same = torch.equal(f1, out)
+    worst = rel(f1, ref)
+    tp.length = tpf.length                    # the NCCL decoder took one decode step above: rewind it
+    for _ in range(5):
+        a, bq = tp.decode_step(tok), tpf.decode_step(tok)
+        same = same and torch.equal(a, bq)
+        tok = a.argmax(-1)
+    fused_calls = calls[0] - 5 * 2 * cfg.n_layers      # the NCCL decoder's own calls in the loop
+    dist.all_reduce = real
+    torch.cuda.synchronize()
+    ok_fused = same and worst < 3e-2 and fused_calls == 0 and _ffi.tc_error() == 0 and int(tpf.exchange.epoch.item()) == 6 * 2 * cfg.n_layers
+    ok_tp = ok_tp and ok_fused
     # data parallel: this rank's slice of the batch, no collective
     lo, hi = dp_slice(4, rank, size)
     dp = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05)
@@ -60,7 +83,7 @@ def _tp_worker(rank, size, port, q):
     flag = torch.tensor([1 if (ok_tp and ok_dp) else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        q.put((int(flag.item()), rel(out, ref), rel(out2, ref2), n_calls))
+        q.put((int(flag.item()), rel(out, ref), rel(out2, ref2), n_calls, bool(ok_fused), bool(same), fused_calls))
     dist.destroy_process_group()
 
 
@@ -77,5 +100,5 @@ def test_tp2_and_dp2_match_single_gpu():
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    ok, r1, r2, n = q.get(timeout=10)
-    assert ok == 1, (r1, r2, n)
+    ok, r1, r2, n, ok_fused, same, fused_calls = q.get(timeout=10)
+    assert ok == 1, (r1, r2, n, ok_fused, same, fused_calls)

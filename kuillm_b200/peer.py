@@ -21,6 +21,8 @@ class PeerExchange:
         import torch.distributed as dist
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
+        if group is None:
+            group = dist.group.WORLD
         self.n_ranks = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         item = torch.empty((), dtype=dtype).element_size()

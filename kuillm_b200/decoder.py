@@ -190,14 +190,18 @@ class Decoder:
             act = _ffi.gemm_swiglu(h2, L["wgu"])
             x = self._allreduce(_ffi.gemm(act, L["wd"], trans_b=True))
         self.length = end
-        if last_only and seq > 1:
-            # only the last position of each sequence feeds the vocabulary GEMM
-            last = torch.arange(seq - 1, rows, seq, device=self.device)
-            x = _ffi.index(x, 0, [last])
-            resid = _ffi.index(resid, 0, [last])
+        last = torch.arange(seq - 1, rows, seq, device=self.device) if (last_only and seq > 1) else None
         if ex is not None:
+            # the last projection's partials are still in the exchange: sum and normalise every row,
+            # then keep the rows that feed the vocabulary GEMM
             hf = _ffi.rmsnorm_gather(ex, rows, self.norm_f, cfg.eps, resid)
+            if last is not None:
+                hf = _ffi.index(hf, 0, [last])
         else:
+            if last is not None:
+                # only the last position of each sequence feeds the vocabulary GEMM
+                x = _ffi.index(x, 0, [last])
+                resid = _ffi.index(resid, 0, [last])
             hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
         return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab]
 

@@ -276,6 +276,8 @@ def rmsnorm_gather(exchange, rows, weight, eps, residual, out=None):
     """residual += sum of the ranks' partials; returns rmsnorm(residual) * weight (the consumer of gemm_push)."""
     x = exchange
     n = weight.shape[0]
+    if residual.numel() != rows * n or not residual.is_contiguous() or rows * n * weight.element_size() > x.slot_bytes:
+        raise ValueError("kuiops: rmsnorm_gather needs a contiguous [rows, n] residual that fits the exchange slots")
     if out is None:
         out = torch.empty((rows, n), dtype=weight.dtype, device=weight.device)
     _check(lib().kuiops_rmsnorm_gather(dtype_code(weight.dtype), rows, n, x.n_ranks, x.local_base, x.slot_bytes, x.flags_offset,

@@ -221,7 +221,7 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
 // with the residual add and the normalisation that follow it.
 //   x[row] = round_T( sum over r of slot(epoch & 1, r)[row] )   (fp32 sum in rank order)
 //   resid_out[row] = x[row] + residual[row];  y[row] = rmsnorm(resid_out[row]) * w
-// Every thread first waits (at most ~2 s, then the error word is set and the kernel carries on) until
+// Every CTA first waits (at most ~2 s, then the error word is set and the kernel carries on) until
 // flag (epoch & 1, r) of every rank r has reached epoch + 1.  The last CTA advances the epoch.
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
@@ -244,7 +244,8 @@ rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned c
   constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
   __shared__ float red[8];
   const unsigned int e = *reinterpret_cast<volatile unsigned int*>(epoch);
-  {
+  if (threadIdx.x == 0) {
+    // one thread polls (acquire, system scope); the barrier below hands what it acquired to the CTA
     const unsigned int* flags = reinterpret_cast<const unsigned int*>(recv_base + flags_offset) + size_t(e & 1u) * n_ranks;
     bool ok = true;
     uint64_t t0 = 0;
@@ -254,8 +255,9 @@ rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned c
         if (elementwise_global_ns() - t0 > 2000000000ull) { ok = false; break; }
       }
     }
-    if (!ok && threadIdx.x == 0) atomicExch(err, 30u);
+    if (!ok) atomicExch(err, 30u);
   }
+  __syncthreads();
   const unsigned char* slots = recv_base + size_t(e & 1u) * n_ranks * slot_bytes;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row_in_block = warp / WPR, wsub = warp % WPR;

@@ -420,13 +420,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     cluster.sync();          // nobody's shared memory goes away while a peer may still read it
   }
   // ------------------------------ teardown ------------------------------------------------
-  if (p.n_ranks) __threadfence_system();        // this thread's pushed partials are visible system-wide ...
   tc::tc_fence_before();
   __syncthreads();
   if (p.n_ranks && threadIdx.x == 0) {
-    // ... before this CTA takes its ticket; the CTA that draws the last one publishes the epoch
-    // to every rank (flag (epoch & 1, my_rank) = epoch + 1), after a fence that orders all the
-    // partials it has observed complete before the flags
+    // All threads of the CTA have issued their pushes (the barrier above); one cumulative
+    // system-scope fence by this thread orders them before the CTA's ticket.  The CTA that draws
+    // the last ticket publishes the epoch to every rank (flag (epoch & 1, my_rank) = epoch + 1)
+    // after a fence that orders everything it has observed before the flags.
     __threadfence_system();
     const unsigned int t = atomicAdd(p.ticket, 1u);
     if (t == gridDim.x - 1) {

@@ -155,75 +155,76 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   pdl_trigger();
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFlashRegsLow));
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------------------
-    if (lane == 0) {
-      tc::mbar_expect_tx(q_full, F_Q_BYTES);
-      tc::tma_load_4d(q_s, &tmQ, q_full, 0, int(row0), int(head), int(b));
-      tc::tma_load_4d(q_s + FBM * 128, &tmQ, q_full, 64, int(row0), int(head), int(b));
-      // ring position n = 2 j (K of tile j) or 2 j + 1 (V): buffer n % F_RING, use number n / F_RING
-      for (uint32_t n = 0; n < 2 * n_tiles; ++n) {
-        const uint32_t buf = n % F_RING, ph = (n / F_RING) & 1;
-        if (!flash_wait(&t_empty[buf], ph ^ 1)) { atomicExch(p.err, 11u); break; }
-        unsigned char* dst = ring + buf * F_T_BYTES;
-        const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
-        const int key0 = int((n >> 1) * FBN);
-        tc::mbar_expect_tx(&t_full[buf], F_T_BYTES);
-        tc::tma_load_4d(dst, tm, &t_full[buf], 0, key0, int(kvh), int(b));
-        tc::tma_load_4d(dst + FBN * 128, tm, &t_full[buf], 64, key0, int(kvh), int(b));
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------ UMMA issuer -------------------------------------------
-    if (lane == 0) {
-      constexpr int is_bf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_qk = tc::make_idesc(is_bf16, 0, 0, FBM, FBN);
-      constexpr uint32_t idesc_pv = tc::make_idesc(is_bf16, 0, 1, FBM, FD);
-      bool ok = flash_wait(q_full, 0);
-      if (!ok) atomicExch(p.err, 12u);
-      const uint32_t qa = tc::smem_u32(q_s);
-      // S = Q K^T of tile j into S buffer j & 1: two 64-wide halves of the head dim x four 16-wide steps
-      auto issue_qk = [&](uint32_t j) -> bool {
-        const uint32_t n = 2 * j, buf = n % F_RING, ph = (n / F_RING) & 1;
-        const uint32_t ka = tc::smem_u32(ring + buf * F_T_BYTES);
-        if (!flash_wait(&t_full[buf], ph)) { atomicExch(p.err, 13u); return false; }
-        tc::tc_fence_after();
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = tc::make_smem_desc(qa + hh * (FBM * 128) + kk * 32, 16, 1024);
-            const uint64_t db = tc::make_smem_desc(ka + hh * (FBN * 128) + kk * 32, 16, 1024);
-            tc::umma_f16(tmem_S + (j & 1) * FBN, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
-          }
-        tc::umma_commit(&t_empty[buf]);      // K of tile j may be overwritten once these have run
-        tc::umma_commit(&s_full[j & 1]);
-        return true;
-      };
-      if (ok && n_tiles > 0) ok = issue_qk(0);
-      for (uint32_t j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t n = 2 * j + 1, buf = n % F_RING, ph = (n / F_RING) & 1;
-        const uint32_t va = tc::smem_u32(ring + buf * F_T_BYTES);
-        // The next tile's scores are computed while the softmax warps work on this one.  Their S
-        // buffer holds P of tile j - 1; the UMMA that reads it was issued before this one and the
-        // pipe runs in order, and the softmax warps left it when p_ready of tile j - 1 arrived.
-        if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
-        if (!flash_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
-        if (!flash_wait(&t_full[buf], ph)) { atomicExch(p.err, 15u); ok = false; break; }
-        tc::tc_fence_after();
-        // O += P V over the 64 keys of the tile: four 16-key steps; P (16 keys = 8 TMEM columns of
-        // the S buffer the softmax overwrote) from TMEM, V MN-major (head dim contiguous)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t db = tc::make_smem_desc(va + kk * 2048, FBN * 128, 1024);
-          tc::umma_f16_ts(tmem_O, tmem_S + (j & 1) * FBN + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+    // the warpgroup that only copies and issues gives most of its registers away
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFlashRegsLow));
+    if (warp == 0) {
+      // ------------------------------ TMA producer ------------------------------------------
+      if (lane == 0) {
+        tc::mbar_expect_tx(q_full, F_Q_BYTES);
+        tc::tma_load_4d(q_s, &tmQ, q_full, 0, int(row0), int(head), int(b));
+        tc::tma_load_4d(q_s + FBM * 128, &tmQ, q_full, 64, int(row0), int(head), int(b));
+        // ring position n = 2 j (K of tile j) or 2 j + 1 (V): buffer n % F_RING, use number n / F_RING
+        for (uint32_t n = 0; n < 2 * n_tiles; ++n) {
+          const uint32_t buf = n % F_RING, ph = (n / F_RING) & 1;
+          if (!flash_wait(&t_empty[buf], ph ^ 1)) { atomicExch(p.err, 11u); break; }
+          unsigned char* dst = ring + buf * F_T_BYTES;
+          const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
+          const int key0 = int((n >> 1) * FBN);
+          tc::mbar_expect_tx(&t_full[buf], F_T_BYTES);
+          tc::tma_load_4d(dst, tm, &t_full[buf], 0, key0, int(kvh), int(b));
+          tc::tma_load_4d(dst + FBN * 128, tm, &t_full[buf], 64, key0, int(kvh), int(b));
         }
-        tc::umma_commit(&t_empty[buf]);
-        tc::umma_commit(o_done);
+      }
+    } else if (warp == 1) {
+      // ------------------------------ UMMA issuer -------------------------------------------
+      if (lane == 0) {
+        constexpr int is_bf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+        constexpr uint32_t idesc_qk = tc::make_idesc(is_bf16, 0, 0, FBM, FBN);
+        constexpr uint32_t idesc_pv = tc::make_idesc(is_bf16, 0, 1, FBM, FD);
+        bool ok = flash_wait(q_full, 0);
+        if (!ok) atomicExch(p.err, 12u);
+        const uint32_t qa = tc::smem_u32(q_s);
+        // S = Q K^T of tile j into S buffer j & 1: two 64-wide halves of the head dim x four 16-wide steps
+        auto issue_qk = [&](uint32_t j) -> bool {
+          const uint32_t n = 2 * j, buf = n % F_RING, ph = (n / F_RING) & 1;
+          const uint32_t ka = tc::smem_u32(ring + buf * F_T_BYTES);
+          if (!flash_wait(&t_full[buf], ph)) { atomicExch(p.err, 13u); return false; }
+          tc::tc_fence_after();
+  #pragma unroll
+          for (int hh = 0; hh < 2; ++hh)
+  #pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t da = tc::make_smem_desc(qa + hh * (FBM * 128) + kk * 32, 16, 1024);
+              const uint64_t db = tc::make_smem_desc(ka + hh * (FBN * 128) + kk * 32, 16, 1024);
+              tc::umma_f16(tmem_S + (j & 1) * FBN, da, db, idesc_qk, (hh | kk) ? 1u : 0u);
+            }
+          tc::umma_commit(&t_empty[buf]);      // K of tile j may be overwritten once these have run
+          tc::umma_commit(&s_full[j & 1]);
+          return true;
+        };
+        if (ok && n_tiles > 0) ok = issue_qk(0);
+        for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+          const uint32_t n = 2 * j + 1, buf = n % F_RING, ph = (n / F_RING) & 1;
+          const uint32_t va = tc::smem_u32(ring + buf * F_T_BYTES);
+          // The next tile's scores are computed while the softmax warps work on this one.  Their S
+          // buffer holds P of tile j - 1; the UMMA that reads it was issued before this one and the
+          // pipe runs in order, and the softmax warps left it when p_ready of tile j - 1 arrived.
+          if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
+          if (!flash_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
+          if (!flash_wait(&t_full[buf], ph)) { atomicExch(p.err, 15u); ok = false; break; }
+          tc::tc_fence_after();
+          // O += P V over the 64 keys of the tile: four 16-key steps; P (16 keys = 8 TMEM columns of
+          // the S buffer the softmax overwrote) from TMEM, V MN-major (head dim contiguous)
+  #pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t db = tc::make_smem_desc(va + kk * 2048, FBN * 128, 1024);
+            tc::umma_f16_ts(tmem_O, tmem_S + (j & 1) * FBN + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc::umma_commit(&t_empty[buf]);
+          tc::umma_commit(o_done);
+        }
       }
     }
-  }
   } else {
     // ------------------------------ softmax + epilogue ------------------------------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kFlashRegsHigh));

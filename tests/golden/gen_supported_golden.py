@@ -1,7 +1,7 @@
 """Record the reference's accept / reject decision for every call in ``gate_cases.cases()``.
 
-Run in a container that has the reference checkout:
-    python tests/golden/gen_supported_golden.py /root/reference
+Run where a checkout of the reference is at hand:
+    python tests/golden/gen_supported_golden.py <path to the reference checkout>
 It imports the reference's own ``kuipy`` package (pure Python; no kernel is built or run),
 hands its ``supported()`` gates fake-CUDA tensors and writes ``supported_golden.json`` next to
 this file: one entry per case with ``accept`` (true / false).  Also records the reference's
@@ -73,4 +73,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])

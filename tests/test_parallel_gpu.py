@@ -28,7 +28,7 @@ def _tp_worker(rank, size, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=size, device_id=torch.device("cuda", rank))
-    cfg = DecoderConfig.tiny(n_heads=4, n_kv_heads=2)
+    cfg = DecoderConfig.tiny(n_heads=2 * size, n_kv_heads=size)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab, (4, 16), generator=g).cuda()
     # reference: the whole model on this rank's GPU
@@ -63,12 +63,15 @@ def _tp_worker(rank, size, port, q):
     dist.all_reduce = counted
     f1 = tpf.prefill(ids)                     # 64 rows: small enough for the fused path
     tok = ref_tok
-    same = torch.equal(f1, out)
+    # two ranks: fp32 sum of two rounded partials, rounded once, is what NCCL computes too; with more
+    # ranks NCCL's order of additions is its own, so the forms agree only within rounding
+    agree = (lambda a, bq: torch.equal(a, bq)) if size == 2 else (lambda a, bq: rel(a, bq) < 1e-2)
+    same = agree(f1, out)
     worst = rel(f1, ref)
     tp.length = tpf.length                    # the NCCL decoder took one decode step above: rewind it
     for _ in range(5):
         a, bq = tp.decode_step(tok), tpf.decode_step(tok)
-        same = same and torch.equal(a, bq)
+        same = same and agree(a, bq)
         tok = a.argmax(-1)
     fused_calls = calls[0] - 5 * 2 * cfg.n_layers      # the NCCL decoder's own calls in the loop
     dist.all_reduce = real
@@ -87,14 +90,15 @@ def _tp_worker(rank, size, port, q):
     dist.destroy_process_group()
 
 
-def test_tp2_and_dp2_match_single_gpu():
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("size", [2, 4])
+def test_tp_and_dp_match_single_gpu(size):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < size:
+        pytest.skip(f"needs {size} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, size, port, q)) for r in range(size)]
     for p in procs:
         p.start()
     for p in procs:

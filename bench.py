@@ -149,10 +149,13 @@ def run_reference(args):
         vals.append(v)
     v = sorted(vals)[len(vals) // 2]
     cfg_kw, batch, prompt, new = WORKLOADS[args.workload]
+    replicas = 1 if args.parallel == "tp" else max(1, args.gpus)
     line = {"impl": "reference", "metric": "decode+prefill tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": batch * new / v * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": batch, "prompt_len": prompt, "new_tokens": new,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": batch * replicas * new / v * 1e3, "higher_is_better": True,
+            "scaling": "strong" if args.parallel == "tp" else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            # the same workload as this library's arm at --gpus N: N replicas of the batch (weak scaling); the host's
+            # rate in tok/s does not depend on how many replicas are queued, only the time per step does
+            "config": {"workload": args.workload, "global_batch": batch * replicas, "prompt_len": prompt, "new_tokens": new,
                        "parallelism": "cpu"},
             "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc},
             "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}

@@ -447,6 +447,16 @@ KUIOPS_API int kuiops_rope_qkv(int dtype, uint64_t rows, uint32_t hq, uint32_t h
                     void* qkv, int64_t row_stride, const int64_t* positions, float theta,
                     void* k_cache, void* v_cache, uint64_t cache_cap, uint32_t rows_per_seq,
                     kuiops_stream_t stream);
+/* Dtype cast of a dense buffer between the float types (aten._to_copy with a dtype change;
+ * src == dst is aten.clone).  Rounds to nearest even, as the eager cast does.  The reference lists
+ * these as backlog (KERNELS.md:46-48) and has no kernel: no counterpart. */
+KUIOPS_API int kuiops_cast(int src_dtype, int dst_dtype, uint64_t len, const void* X, void* Y, kuiops_stream_t stream);
+
+/* aten.masked_fill.Scalar on same-shape dense operands: Y[i] = mask[i] ? value : X[i], mask as
+ * bool bytes, value rounded to dtype.  Backlog in the reference (KERNELS.md:68-90): no counterpart. */
+KUIOPS_API int kuiops_masked_fill(int dtype, uint64_t len, const void* X, const void* mask, double value, void* Y,
+                kuiops_stream_t stream);
+
 /* out[r, :] = table[ids[r], :] (aten.embedding), row length `width` elements. */
 KUIOPS_API int kuiops_embedding(uint32_t elem_bytes, uint64_t rows, uint64_t width, uint64_t vocab,
                      const void* table, const int64_t* ids, void* out, int32_t* status,

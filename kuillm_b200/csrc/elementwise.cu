@@ -650,3 +650,86 @@ int kuiops_embedding(uint32_t elem_bytes, uint64_t rows, uint64_t width, uint64_
 }
 
 }  // extern "C"
+
+// --------------------------------------------------------------------------------------
+// Data movement the dispatcher sees on every token next to the compute ops: dtype casts
+// (aten._to_copy between the float types, aten.clone as the identity cast) and masked_fill with a
+// scalar.  The reference lists them as backlog (KERNELS.md:46-48,68-90) and has no kernel.
+// --------------------------------------------------------------------------------------
+namespace kuiops {
+
+template <typename TS, typename TD>
+__global__ void __launch_bounds__(256)
+cast_kernel(uint64_t len, const TS* __restrict__ X, TD* __restrict__ Y, int vec_ok) {
+  // 8 elements per thread step: 16 or 32 bytes in, 16 or 32 bytes out, whichever type is wider
+  const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
+  uint64_t start = 0;
+  if (vec_ok) {
+    const uint64_t ngrp = len / 8;
+    for (uint64_t g = gt; g < ngrp; g += gs) {
+      TS in[8];
+      TD out[8];
+      if (sizeof(TS) == 2) *reinterpret_cast<int4*>(in) = __ldcs(reinterpret_cast<const int4*>(X + g * 8));
+      else { reinterpret_cast<int4*>(in)[0] = __ldcs(reinterpret_cast<const int4*>(X + g * 8)); reinterpret_cast<int4*>(in)[1] = __ldcs(reinterpret_cast<const int4*>(X + g * 8) + 1); }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) out[e] = ElemTraits<TD>::from_f(ElemTraits<TS>::to_f(in[e]));
+      if (sizeof(TD) == 2) *reinterpret_cast<int4*>(Y + g * 8) = *reinterpret_cast<int4*>(out);
+      else { reinterpret_cast<int4*>(Y + g * 8)[0] = reinterpret_cast<int4*>(out)[0]; reinterpret_cast<int4*>(Y + g * 8)[1] = reinterpret_cast<int4*>(out)[1]; }
+    }
+    start = ngrp * 8;
+  }
+  for (uint64_t i = start + gt; i < len; i += gs) Y[i] = ElemTraits<TD>::from_f(ElemTraits<TS>::to_f(X[i]));
+}
+
+template <typename TS, typename TD>
+static int cast_launch(uint64_t len, const void* X, void* Y, cudaStream_t st) {
+  const int vec_ok = aligned16(X) && aligned16(Y);
+  const unsigned grid = stream_grid((len + 7) / 8, 256, 16);
+  cast_kernel<TS, TD><<<grid, 256, 0, st>>>(len, static_cast<const TS*>(X), static_cast<TD*>(Y), vec_ok);
+  return check_launch();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+masked_fill_kernel(uint64_t len, const T* __restrict__ X, const uint8_t* __restrict__ mask, T value, T* __restrict__ Y) {
+  const uint64_t gs = uint64_t(gridDim.x) * blockDim.x;
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < len; i += gs) Y[i] = mask[i] ? value : X[i];
+}
+
+}  // namespace kuiops
+
+extern "C" {
+
+int kuiops_cast(int src_dtype, int dst_dtype, uint64_t len, const void* X, void* Y, kuiops_stream_t s) {
+  if (len == 0 || !X || !Y) return KUIOPS_EINVAL;
+  cudaStream_t st = as_stream(s);
+#define KUIOPS_CAST(SD, ST, DD, DT) if (src_dtype == SD && dst_dtype == DD) return cast_launch<ST, DT>(len, X, Y, st);
+  KUIOPS_CAST(KUIOPS_F32, float, KUIOPS_F32, float)
+  KUIOPS_CAST(KUIOPS_F32, float, KUIOPS_BF16, __nv_bfloat16)
+  KUIOPS_CAST(KUIOPS_F32, float, KUIOPS_F16, __half)
+  KUIOPS_CAST(KUIOPS_BF16, __nv_bfloat16, KUIOPS_F32, float)
+  KUIOPS_CAST(KUIOPS_BF16, __nv_bfloat16, KUIOPS_BF16, __nv_bfloat16)
+  KUIOPS_CAST(KUIOPS_BF16, __nv_bfloat16, KUIOPS_F16, __half)
+  KUIOPS_CAST(KUIOPS_F16, __half, KUIOPS_F32, float)
+  KUIOPS_CAST(KUIOPS_F16, __half, KUIOPS_BF16, __nv_bfloat16)
+  KUIOPS_CAST(KUIOPS_F16, __half, KUIOPS_F16, __half)
+#undef KUIOPS_CAST
+  return KUIOPS_EINVAL;
+}
+
+int kuiops_masked_fill(int dtype, uint64_t len, const void* X, const void* mask, double value, void* Y, kuiops_stream_t s) {
+  if (len == 0 || !X || !mask || !Y) return KUIOPS_EINVAL;
+  const unsigned grid = stream_grid(len, 256 * 4, 16);
+  cudaStream_t st = as_stream(s);
+  auto M = static_cast<const uint8_t*>(mask);
+  switch (dtype) {
+    case KUIOPS_F32: masked_fill_kernel<float><<<grid, 256, 0, st>>>(len, static_cast<const float*>(X), M, float(value), static_cast<float*>(Y)); break;
+    case KUIOPS_BF16: masked_fill_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(len, static_cast<const __nv_bfloat16*>(X), M, __float2bfloat16_rn(float(value)), static_cast<__nv_bfloat16*>(Y)); break;
+    case KUIOPS_F16: masked_fill_kernel<__half><<<grid, 256, 0, st>>>(len, static_cast<const __half*>(X), M, __float2half_rn(float(value)), static_cast<__half*>(Y)); break;
+    default: return KUIOPS_EINVAL;
+  }
+  return check_launch();
+}
+
+}  // extern "C"
+

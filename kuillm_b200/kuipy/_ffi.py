@@ -95,6 +95,8 @@ SIGNATURES = {
     "kuiops_swiglu": (c_int, [c_int, c_u64, c_u32, c_void_p, c_void_p, c_void_p]),
     "kuiops_rope_qkv": (c_int, [c_int, c_u64, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_float,
                                 c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
+    "kuiops_cast": (c_int, [c_int, c_int, c_u64, c_void_p, c_void_p, c_void_p]),
+    "kuiops_masked_fill": (c_int, [c_int, c_u64, c_void_p, c_void_p, c_double, c_void_p, c_void_p]),
     "kuiops_embedding": (c_int, [c_u32, c_u64, c_u64, c_u64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
 }
@@ -434,6 +436,26 @@ def topk(X, k):
     idx = torch.empty(tuple(Xc.shape[:-1]) + (k,), dtype=torch.int64, device=Xc.device)
     _check(lib().kuiops_topk_f32(m, n, k, Xc.data_ptr(), vals.data_ptr(), idx.data_ptr(), _stream()), "topk")
     return vals, idx
+
+
+def cast(X, dtype, out=None):
+    """X converted to `dtype` (one of the float types); the same dtype gives a copy."""
+    Xc = X.contiguous()
+    if out is None:
+        out = torch.empty(Xc.shape, dtype=dtype, device=Xc.device)
+    if Xc.numel():
+        _check(lib().kuiops_cast(dtype_code(Xc.dtype), dtype_code(dtype), Xc.numel(), Xc.data_ptr(), out.data_ptr(), _stream()), "cast")
+    return out
+
+
+def masked_fill(X, mask, value, out=None):
+    Xc, Mc = X.contiguous(), mask.contiguous()
+    if out is None:
+        out = torch.empty_like(Xc)
+    if Xc.numel():
+        _check(lib().kuiops_masked_fill(dtype_code(Xc.dtype), Xc.numel(), Xc.data_ptr(), Mc.data_ptr(), float(value), out.data_ptr(),
+                                        _stream()), "masked_fill")
+    return out
 
 
 def argmax_lastdim(X):

@@ -869,3 +869,85 @@ class IsinImpl(_Family):
 
 
 _compile.register_binder(IsinImpl.wrapper_template, lambda ctx: (lambda E, T, inv=False: _ffi.isin(E, T, inv)))
+
+
+class DataMoveImpl(_Family):
+    """The data-movement ops a decoder issues next to its compute on every token: dtype casts
+    (aten._to_copy between float types), aten.clone, aten.masked_fill.Scalar, aten.argmax over the
+    last axis and aten.embedding.  The reference lists them as backlog without kernels
+    (KERNELS.md:46-48,68-90); dense, contiguous operands only, everything else falls through."""
+    fst_template = "datamove/Kuiops.DataMove.Inst.fst.j2"
+    wrapper_template = "datamove/wrapper_datamove.cu.j2"
+    tune_key = "DATAMOVE"
+    tune_params = ()
+    _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
+    overloads = (aten._to_copy.default, aten.clone.default, aten.masked_fill.Scalar, aten.argmax.default,
+                 aten.embedding.default)
+
+    @staticmethod
+    def _dense(X):
+        return _is_cuda_tensor(X) and X.is_contiguous() and 0 < X.numel() <= _MAX_NUMEL
+
+    def supported(self, func, args, kwargs):
+        if not args:
+            return None
+        X = args[0]
+        if func is aten._to_copy.default:
+            dt = kwargs.get("dtype") or X.dtype
+            plain = (kwargs.get("device") in (None, X.device) and kwargs.get("layout") in (None, torch.strided)
+                     and not kwargs.get("pin_memory") and kwargs.get("memory_format") in (None, torch.preserve_format, torch.contiguous_format))
+            if len(args) == 1 and self._dense(X) and plain and X.dtype in self._FLOATS and dt in self._FLOATS:
+                return ("cast", dt, [X])
+            return None
+        if func is aten.clone.default:
+            fmt = kwargs.get("memory_format", args[1] if len(args) > 1 else None)
+            if self._dense(X) and X.dtype in self._FLOATS and fmt in (None, torch.preserve_format, torch.contiguous_format):
+                return ("cast", X.dtype, [X])
+            return None
+        if func is aten.masked_fill.Scalar:
+            if len(args) != 3 or kwargs:
+                return None
+            M, v = args[1], args[2]
+            if (self._dense(X) and X.dtype in self._FLOATS and self._dense(M) and M.dtype == torch.bool
+                    and tuple(M.shape) == tuple(X.shape) and isinstance(v, (int, float)) and not isinstance(v, bool)):
+                return ("masked_fill", float(v), [X, M])
+            return None
+        if func is aten.argmax.default:
+            dim = kwargs.get("dim", args[1] if len(args) > 1 else None)
+            keep = kwargs.get("keepdim", args[2] if len(args) > 2 else False)
+            if (self._dense(X) and X.dtype in self._FLOATS and X.dim() >= 1 and dim is not None and not keep
+                    and _wrap_dim(dim, X.dim()) == X.dim() - 1):
+                return ("argmax", None, [X])
+            return None
+        if func is aten.embedding.default:
+            if len(args) < 2:
+                return None
+            ids = args[1]
+            extra = list(args[2:]) + list(kwargs.values())
+            if any(bool(e) and e != -1 for e in extra[1:]):          # scale_grad_by_freq / sparse
+                return None
+            if (self._dense(X) and X.dim() == 2 and X.dtype in self._FLOATS and _is_cuda_tensor(ids) and ids.dtype == torch.int64
+                    and ids.numel() > 0):
+                return ("embedding", None, [X, ids])
+            return None
+        return None
+
+    def run(self, spec, args, kwargs):
+        op, extra, call = spec
+        module = f"Kuiops.DataMove.{op.title().replace('_', '')}"
+        return self._mod(module, dict(module=module, name="datamove_jit", op=op), {}).run(*call, extra)
+
+
+def _datamove_binder(ctx):
+    op = ctx["op"]
+    if op == "cast":
+        return lambda X, dt: _ffi.cast(X, dt)
+    if op == "masked_fill":
+        return lambda X, M, v: _ffi.masked_fill(X, M, v)
+    if op == "argmax":
+        return lambda X, _=None: _ffi.argmax_lastdim(X)
+    return lambda W, ids, _=None: _ffi.embedding(W, ids)
+
+
+_compile.register_binder(DataMoveImpl.wrapper_template, _datamove_binder)
+

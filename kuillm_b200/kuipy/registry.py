@@ -5,8 +5,8 @@ takes the call so that the caller falls through to stock PyTorch - the contract 
 reference's ``kuipy/registry.py:67-84``.  The table is built on first use from the overloads
 each family declares.  Under ``config.GATES == "reference"`` it holds exactly the reference's
 29 keys (its SDPA family exists but is left unconnected, registry.py:27-28,59 there); "wide"
-gates add attention and the topk / isin / index / reduce families the reference only lists as
-backlog.  Tuned parameters are loaded from and saved to ``config.TUNE_FILE``.
+gates add attention, the topk / isin / index / reduce families and the per-token data-movement
+ops (casts, clone, masked_fill, argmax, embedding) the reference only lists as backlog.  Tuned parameters are loaded from and saved to ``config.TUNE_FILE``.
 """
 import json
 
@@ -18,7 +18,7 @@ _FAMILIES = None
 
 _REFERENCE_FAMILIES = (K.ElementwiseImpl, K.MmImpl, K.BmmImpl, K.AddmmImpl, K.SoftmaxImpl,
                        K.GatherImpl, K.ScatterImpl, K.CatImpl, K.MeanImpl)
-_WIDE_FAMILIES = (K.SdpaImpl, K.TopkImpl, K.IsinImpl, K.IndexImpl, K.ReduceImpl)
+_WIDE_FAMILIES = (K.SdpaImpl, K.TopkImpl, K.IsinImpl, K.IndexImpl, K.ReduceImpl, K.DataMoveImpl)
 
 
 def _load_tune_params():

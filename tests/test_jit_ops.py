@@ -238,6 +238,38 @@ def test_topk_small_k_of_a_long_row_with_duplicates(cuda, gates):
     assert_bit_exact(vals, rv)
 
 
+# ---- per-token data movement (wide gates) -----------------------------------------------------------
+def test_datamove_family_matches_eager(cuda, gates):
+    gates("wide")
+    impl = kuiops.DataMoveImpl({})
+    for src in FLOATS:
+        X = randn(3, 5, 1027, dtype=src)
+        for dst in FLOATS:
+            out = run_family(impl, aten._to_copy.default, (X,), {"dtype": dst})
+            assert out.dtype == dst and torch.equal(out.cpu(), X.cpu().to(dst))
+        c = run_family(impl, aten.clone.default, (X,))
+        assert c.data_ptr() != X.data_ptr() and torch.equal(c, X)
+        M = (randn(3, 5, 1027, seed=3) > 0.3)
+        out = run_family(impl, aten.masked_fill.Scalar, (X, M, -1e4))
+        assert torch.equal(out.cpu(), X.cpu().masked_fill(M.cpu(), -1e4))
+        am = run_family(impl, aten.argmax.default, (X, -1))
+        assert torch.equal(am.cpu(), X.cpu().float().argmax(-1))
+    W = randn(50, 24, dtype=torch.bfloat16)
+    ids = torch.randint(0, 50, (4, 7), generator=torch.Generator().manual_seed(2)).cuda()
+    e = run_family(impl, aten.embedding.default, (W, ids))
+    assert tuple(e.shape) == (4, 7, 24) and torch.equal(e.cpu(), torch.nn.functional.embedding(ids.cpu(), W.cpu()))
+    # what it leaves to PyTorch
+    assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.int32}) is None
+    assert impl.supported(aten._to_copy.default, (X,), {"device": torch.device("cpu")}) is None
+    assert impl.supported(aten._to_copy.default, (X.transpose(0, 1),), {"dtype": torch.float32}) is None
+    assert impl.supported(aten.masked_fill.Scalar, (X, M[0], 0.0), {}) is None          # broadcast mask
+    assert impl.supported(aten.argmax.default, (X,), {}) is None                        # flattened arg-max
+    assert impl.supported(aten.argmax.default, (X, 0), {}) is None
+    gates("reference")
+    from kuipy import registry
+    assert aten._to_copy.default not in registry.table()
+
+
 # ---- attention --------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", FLOATS)
 def test_sdpa_biased(cuda, gates, dtype):

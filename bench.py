@@ -188,8 +188,22 @@ def run_ours(args):
     dec = Decoder(cfg, device=dev, seed=0, tp_rank=rank if tp > 1 else 0, tp_size=tp)
     dec.alloc_cache(batch, prompt + new)
     fused = tp > 1 and args.allreduce == "fused"
+    fused_note = ""
     if fused:
-        dec.enable_fused_allreduce(batch)      # decode steps only (batch rows); the prefill keeps NCCL
+        # decode steps only (batch rows); the prefill keeps NCCL.  The fused form needs every rank's
+        # receive area mapped into every process; where that cannot be had the step keeps NCCL, and says so
+        import torch.distributed as dist
+        try:
+            dec.enable_fused_allreduce(batch)
+            ok = torch.ones(1, device=dev)
+        except Exception as e:            # noqa: BLE001 - whatever the mapping raised is reported, not hidden
+            fused_note = f"{type(e).__name__}: {e}"[:160]
+            ok = torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            dec.exchange, fused = None, False
+            if rank == 0:
+                print(f"[bench] fused all-reduce unavailable, using NCCL: {fused_note or 'another rank failed'}", file=sys.stderr)
     g = torch.Generator().manual_seed(1000 + (0 if tp > 1 else rank))
     ids_host = torch.randint(0, cfg.vocab, (batch, prompt), generator=g).pin_memory()
     ids_dev = ids_host.to(dev)

@@ -391,18 +391,23 @@ index_kernel(const __grid_constant__ IndexParams p, const W* __restrict__ self_,
 // ---- isin -------------------------------------------------------------------------------
 // The test set goes into an open-addressing hash table in shared memory (kIsinTile entries per
 // pass at load factor 1/2; a 1024-entry stop-id set is one pass) and every element probes it.
+// A 64 Kbit filter (one bit per 16-bit hash of a test value) answers "certainly absent" with a
+// single 4-byte shared-memory load, which is the common answer for a small stop-id set.
 // Elements are read two per 16-byte load and results written eight per store.
 constexpr int kIsinTile = 2048;
 constexpr int kIsinSlots = 2 * kIsinTile;
 constexpr unsigned long long kIsinEmpty = 0x8000000000000000ull;    // INT64_MIN marks a free slot
 
-__device__ __forceinline__ uint32_t isin_hash(unsigned long long v) {
-  return uint32_t((v * 0x9E3779B97F4A7C15ull) >> 52);               // 12 bits = kIsinSlots
+constexpr int kIsinFilterWords = 2048;                              // 65536 bits
+__device__ __forceinline__ uint32_t isin_filter_hash(unsigned long long v) {
+  return uint32_t((v * 0x9E3779B97F4A7C15ull) >> 48);               // 16 bits; the top 12 index the table (kIsinSlots)
 }
-__device__ __forceinline__ bool isin_probe(const unsigned long long* slots, bool has_empty_key, long long v) {
+__device__ __forceinline__ bool isin_probe(const unsigned long long* slots, const uint32_t* filter, bool has_empty_key, long long v) {
   const unsigned long long u = static_cast<unsigned long long>(v);
   if (u == kIsinEmpty) return has_empty_key;
-  uint32_t h = isin_hash(u);
+  const uint32_t fh = isin_filter_hash(u);
+  if (!((filter[fh >> 5] >> (fh & 31u)) & 1u)) return false;
+  uint32_t h = fh >> 4;
   for (int probes = 0; probes < kIsinSlots; ++probes) {             // ends at the first free slot
     const unsigned long long sl = slots[h];
     if (sl == u) return true;
@@ -416,6 +421,7 @@ __global__ void __launch_bounds__(512)
 isin_kernel(uint64_t n, const int64_t* __restrict__ elems, uint64_t m, const int64_t* __restrict__ tests, int invert,
             uint8_t* __restrict__ out, uint64_t per_block, int vec_ok) {
   __shared__ unsigned long long slots[kIsinSlots];
+  __shared__ uint32_t filter[kIsinFilterWords];
   __shared__ int has_empty_key;
   const uint64_t lo = uint64_t(blockIdx.x) * per_block;      // per_block is a multiple of 8
   const uint64_t hi = lo + per_block < n ? lo + per_block : n;
@@ -426,12 +432,15 @@ isin_kernel(uint64_t n, const int64_t* __restrict__ elems, uint64_t m, const int
     const bool first = t0 == 0, last = t0 + kIsinTile >= m;
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < uint32_t(kIsinSlots); i += blockDim.x) slots[i] = kIsinEmpty;
+    for (uint32_t i = threadIdx.x; i < uint32_t(kIsinFilterWords); i += blockDim.x) filter[i] = 0u;
     if (threadIdx.x == 0) has_empty_key = 0;
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < cnt; i += blockDim.x) {
       const unsigned long long u = static_cast<unsigned long long>(tests[t0 + i]);
       if (u == kIsinEmpty) { has_empty_key = 1; continue; }
-      uint32_t h = isin_hash(u);
+      const uint32_t fh = isin_filter_hash(u);
+      atomicOr(&filter[fh >> 5], 1u << (fh & 31u));
+      uint32_t h = fh >> 4;
       for (int probes = 0; probes < kIsinSlots; ++probes) {
         const unsigned long long prev = atomicCAS(&slots[h], kIsinEmpty, u);
         if (prev == kIsinEmpty || prev == u) break;
@@ -460,13 +469,13 @@ isin_kernel(uint64_t n, const int64_t* __restrict__ elems, uint64_t m, const int
         uint2 res;
         uint8_t* rb = reinterpret_cast<uint8_t*>(&res);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) rb[q] = finish(isin_probe(slots, hek, v[q]), pb[q]);
+        for (int q = 0; q < 8; ++q) rb[q] = finish(isin_probe(slots, filter, hek, v[q]), pb[q]);
         *reinterpret_cast<uint2*>(out + e) = res;
       }
       e0 = lo + groups * 8;
     }
     for (uint64_t e = e0 + threadIdx.x; e < hi; e += blockDim.x)
-      out[e] = finish(isin_probe(slots, hek, elems[e]), first ? uint8_t(0) : out[e]);
+      out[e] = finish(isin_probe(slots, filter, hek, elems[e]), first ? uint8_t(0) : out[e]);
   }
 }
 

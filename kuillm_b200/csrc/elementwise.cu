@@ -351,27 +351,32 @@ swiglu_kernel(uint64_t m, uint32_t n, const T* __restrict__ gu, T* __restrict__ 
 }
 
 // Rotary embedding on the q and k heads of packed qkv rows, plus the KV-cache append.
-// One thread handles one (i, i + d/2) pair group of 8 elements from each half.
+// One thread handles the (i, i + d/2) pair group of 8 elements from each half of `hpt` consecutive
+// heads of one row: the angles depend only on (row, i), so their sines and cosines (the expensive
+// part: accurate range reduction for positions in the thousands) are computed once and reused over
+// those heads.  hpt is 1 for decode-sized calls (parallelism matters) and 8 for prefill.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_qkv_kernel(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, T* qkv, int64_t row_stride,
                 const int64_t* __restrict__ positions, float log2_theta, T* k_cache, T* v_cache,
-                uint64_t cache_cap, uint32_t rows_per_seq) {
+                uint64_t cache_cap, uint32_t rows_per_seq, uint32_t hpt) {
   pdl_wait();
   pdl_trigger();
   constexpr int VN = Vec16<T>::N;
   const uint32_t half = d / 2, vec_per_half = half / VN;
   const uint32_t heads = hq + 2 * hk;                 // q heads, k heads, v heads
-  const uint64_t total = rows * heads * vec_per_half;
+  const uint32_t groups = (heads + hpt - 1) / hpt;
+  const uint64_t total = rows * groups * vec_per_half;
   const uint64_t gt = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x, gs = uint64_t(gridDim.x) * blockDim.x;
   for (uint64_t t = gt; t < total; t += gs) {
     const uint32_t v = t % vec_per_half;
-    const uint32_t head = (t / vec_per_half) % heads;
-    const uint64_t row = t / (uint64_t(vec_per_half) * heads);
+    const uint32_t group = (t / vec_per_half) % groups;
+    const uint64_t row = t / (uint64_t(vec_per_half) * groups);
     const int64_t pos = positions[row];
-    T* base = qkv + row * row_stride + size_t(head) * d;
-    Vec16<T> lo = ld16(base + v * VN), hi = ld16(base + half + v * VN);
-    if (head < hq + hk) {
+    const uint32_t h0 = group * hpt, h1 = min(h0 + hpt, heads);
+    // eager computes cos / sin in fp32 and rounds them to the element type
+    float csr[VN], snr[VN];
+    if (h0 < hq + hk) {
 #pragma unroll
       for (int e = 0; e < VN; ++e) {
         const float fi = float(v * VN + e);
@@ -379,34 +384,43 @@ rope_qkv_kernel(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, T* qkv, int
         const float inv_freq = exp2f(-log2_theta * (2.f * fi / float(d)));
         float sn, cs;
         sincosf(float(pos) * inv_freq, &sn, &cs);
-        // eager computes q*cos and rotate_half(q)*sin in the element type, then adds
-        const float a = ElemTraits<T>::to_f(lo.v[e]), b = ElemTraits<T>::to_f(hi.v[e]);
-        const float csr = ElemTraits<T>::to_f(ElemTraits<T>::from_f(cs));
-        const float snr = ElemTraits<T>::to_f(ElemTraits<T>::from_f(sn));
-        const float a_c = ElemTraits<T>::to_f(ElemTraits<T>::from_f(a * csr));
-        const float b_s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(-b * snr));
-        const float b_c = ElemTraits<T>::to_f(ElemTraits<T>::from_f(b * csr));
-        const float a_s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(a * snr));
-        lo.v[e] = ElemTraits<T>::from_f(a_c + b_s);
-        hi.v[e] = ElemTraits<T>::from_f(b_c + a_s);
-      }
-      if (head < hq || k_cache == nullptr) {
-        st16(base + v * VN, lo);
-        st16(base + half + v * VN, hi);
+        csr[e] = ElemTraits<T>::to_f(ElemTraits<T>::from_f(cs));
+        snr[e] = ElemTraits<T>::to_f(ElemTraits<T>::from_f(sn));
       }
     }
-    if (head >= hq && k_cache != nullptr) {
-      const bool is_k = head < hq + hk;
-      const uint32_t kvh = is_k ? head - hq : head - hq - hk;
-      const uint64_t seq = row / rows_per_seq;
-      T* dst = (is_k ? k_cache : v_cache) + ((seq * hk + kvh) * cache_cap + uint64_t(pos)) * d;
-      if (uint64_t(pos) < cache_cap) {
-        st16(dst + v * VN, lo);
-        st16(dst + half + v * VN, hi);
+    for (uint32_t head = h0; head < h1; ++head) {
+      T* base = qkv + row * row_stride + size_t(head) * d;
+      Vec16<T> lo = ld16(base + v * VN), hi = ld16(base + half + v * VN);
+      if (head < hq + hk) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          // eager computes q*cos and rotate_half(q)*sin in the element type, then adds
+          const float a = ElemTraits<T>::to_f(lo.v[e]), b = ElemTraits<T>::to_f(hi.v[e]);
+          const float a_c = ElemTraits<T>::to_f(ElemTraits<T>::from_f(a * csr[e]));
+          const float b_s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(-b * snr[e]));
+          const float b_c = ElemTraits<T>::to_f(ElemTraits<T>::from_f(b * csr[e]));
+          const float a_s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(a * snr[e]));
+          lo.v[e] = ElemTraits<T>::from_f(a_c + b_s);
+          hi.v[e] = ElemTraits<T>::from_f(b_c + a_s);
+        }
+        if (head < hq || k_cache == nullptr) {
+          st16(base + v * VN, lo);
+          st16(base + half + v * VN, hi);
+        }
       }
-      if (is_k) {   // keep the packed row consistent too (prefill attention reads it)
-        st16(base + v * VN, lo);
-        st16(base + half + v * VN, hi);
+      if (head >= hq && k_cache != nullptr) {
+        const bool is_k = head < hq + hk;
+        const uint32_t kvh = is_k ? head - hq : head - hq - hk;
+        const uint64_t seq = row / rows_per_seq;
+        T* dst = (is_k ? k_cache : v_cache) + ((seq * hk + kvh) * cache_cap + uint64_t(pos)) * d;
+        if (uint64_t(pos) < cache_cap) {
+          st16(dst + v * VN, lo);
+          st16(dst + half + v * VN, hi);
+        }
+        if (is_k) {   // keep the packed row consistent too (prefill attention reads it)
+          st16(base + v * VN, lo);
+          st16(base + half + v * VN, hi);
+        }
       }
     }
   }
@@ -615,10 +629,13 @@ static int rope_launch(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, void
   if (row_stride < int64_t(hq + 2 * hk) * d) return KUIOPS_EINVAL;
   if ((d / 2) % VN || d % 2 || row_stride % VN || !aligned16(qkv) || (kc && (!aligned16(kc) || !aligned16(vc))))
     return KUIOPS_EUNSUPPORTED;
-  const uint64_t total = rows * (hq + 2 * hk) * (d / 2 / VN);
+  // heads per thread: share the sines and cosines of a row over eight heads once there are rows enough to fill the machine
+  const uint32_t heads = hq + 2 * hk;
+  const uint32_t hpt = rows * (heads / 8) * (d / 2 / VN) >= uint64_t(kNumSMs) * 2048 ? 8u : 1u;
+  const uint64_t total = rows * ((heads + hpt - 1) / hpt) * (d / 2 / VN);
   unsigned grid = stream_grid(total, 256, 16);
   return launch_pdl(rope_qkv_kernel<T>, dim3(grid), dim3(256), 0, st, rows, hq, hk, d, static_cast<T*>(qkv), row_stride,
-                    positions, log2f(theta), static_cast<T*>(kc), static_cast<T*>(vc), cap, rps ? rps : 1u);
+                    positions, log2f(theta), static_cast<T*>(kc), static_cast<T*>(vc), cap, rps ? rps : 1u, hpt);
 }
 
 extern "C" {

@@ -81,3 +81,25 @@ def test_generate_is_deterministic_and_cache_consistent(cuda):
     for t in range(3):
         l_step = dec.decode_step(a[:, t].contiguous())
     assert O.rel_frobenius(to_np(l_step), to_np(l_full)) < 3e-2
+
+
+def test_rope_prefill_sized_call_equals_row_chunks(cuda):
+    """A prefill-sized call shares each row's sines and cosines over eight heads; small calls compute
+    them per head.  Same arithmetic, so the packed rows and both caches must agree bit for bit."""
+    from kuipy import _ffi
+    hq, hk, d, seqs, per = 16, 8, 128, 10, 1024
+    rows = seqs * per
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(rows, (hq + 2 * hk) * d, generator=g).bfloat16().cuda()
+    pos = torch.arange(per).repeat(seqs).cuda()
+    kc1, vc1 = (torch.zeros(seqs, hk, per, d, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    big = qkv.clone()
+    _ffi.rope_qkv(big, hq, hk, d, pos, 5e5, kc1, vc1, rows_per_seq=per)
+    small = qkv.clone()
+    for s0 in range(0, rows, 64):                    # 64 rows at a time: the per-head form
+        seq = s0 // per
+        _ffi.rope_qkv(small[s0:s0 + 64], hq, hk, d, pos[s0:s0 + 64], 5e5, kc2[seq:seq + 1], vc2[seq:seq + 1], rows_per_seq=per)
+    assert torch.equal(big, small) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert not torch.equal(big, qkv)
+

@@ -133,6 +133,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t n_tiles = (s_end + FBN - 1) / FBN;
 
   if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmQ); tc::prefetch_tmap(&tmK); tc::prefetch_tmap(&tmV);
     tc::mbar_init(q_full, 1);
     for (int i = 0; i < F_RING; ++i) { tc::mbar_init(&t_full[i], 1); tc::mbar_init(&t_empty[i], 1); }
     tc::mbar_init(&s_full[0], 1);
@@ -140,7 +141,22 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc::mbar_init(p_ready, 4);
     tc::mbar_init(o_done, 1);
     tc::fence_barrier_init();
-    tc::prefetch_tmap(&tmQ); tc::prefetch_tmap(&tmK); tc::prefetch_tmap(&tmV);
+    // The copies of Q and of the first ring positions need nothing but these barriers: start them
+    // now, so that they fly while the tensor memory is being allocated and the CTA meets below.
+    // (Q, K, V may still be being written by the previous kernel in the stream: wait for it first.)
+    pdl_wait();
+    tc::mbar_expect_tx(q_full, F_Q_BYTES);
+    tc::tma_load_4d(q_s, &tmQ, q_full, 0, int(row0), int(head), int(b));
+    tc::tma_load_4d(q_s + FBM * 128, &tmQ, q_full, 64, int(row0), int(head), int(b));
+    const uint32_t first = min(uint32_t(F_RING), 2 * n_tiles);
+    for (uint32_t n = 0; n < first; ++n) {
+      unsigned char* dst = ring + n * F_T_BYTES;
+      const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
+      const int key0 = int((n >> 1) * FBN);
+      tc::mbar_expect_tx(&t_full[n], F_T_BYTES);
+      tc::tma_load_4d(dst, tm, &t_full[n], 0, key0, int(kvh), int(b));
+      tc::tma_load_4d(dst + FBN * 128, tm, &t_full[n], 64, key0, int(kvh), int(b));
+    }
   }
   if (warp == 1) {
     tc::tmem_alloc(tmem_slot, F_TMEM_COLS);
@@ -151,7 +167,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
-  pdl_wait();          // Q, K, V may still be being written by the previous kernel in the stream
+  if (threadIdx.x != 0) pdl_wait();      // thread 0 did before it started the first copies
   pdl_trigger();
 
   if (warp < 4) {
@@ -160,11 +176,9 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (warp == 0) {
       // ------------------------------ TMA producer ------------------------------------------
       if (lane == 0) {
-        tc::mbar_expect_tx(q_full, F_Q_BYTES);
-        tc::tma_load_4d(q_s, &tmQ, q_full, 0, int(row0), int(head), int(b));
-        tc::tma_load_4d(q_s + FBM * 128, &tmQ, q_full, 64, int(row0), int(head), int(b));
-        // ring position n = 2 j (K of tile j) or 2 j + 1 (V): buffer n % F_RING, use number n / F_RING
-        for (uint32_t n = 0; n < 2 * n_tiles; ++n) {
+        // ring position n = 2 j (K of tile j) or 2 j + 1 (V): buffer n % F_RING, use number n / F_RING;
+        // Q and the first F_RING positions were requested during set-up
+        for (uint32_t n = F_RING; n < 2 * n_tiles; ++n) {
           const uint32_t buf = n % F_RING, ph = (n / F_RING) & 1;
           if (!flash_wait(&t_empty[buf], ph ^ 1)) { atomicExch(p.err, 11u); break; }
           unsigned char* dst = ring + buf * F_T_BYTES;

@@ -8,8 +8,7 @@
 //     S = Q K^T        UMMA 128 x 64 x 128, both operands K-major in shared memory, S in TMEM
 //                      (two S buffers, so the next tile's scores are computed during this softmax)
 //     softmax          4 warps, one query row per thread: tcgen05.ld S, online max / sum in the
-//                      log2 domain in registers (3-input max, packed f32x2 FMA / add; half of the
-//                      exponentials by ex2.approx, half by a cubic on the FMA pipes);
+//                      log2 domain in registers (3-input max, packed f32x2 FMA / add, ex2.approx);
 //                      the O accumulator in TMEM is rescaled only when a row's running max grew by
 //                      more than 2^8 (the stale max stays exact because the final normalisation
 //                      uses the same max)
@@ -92,34 +91,6 @@ __device__ __forceinline__ void f_fma2(float& a0, float& a1, float s, float c) {
 __device__ __forceinline__ void f_add2(float& a0, float& a1, float b0, float b1) {
   asm("{.reg .b64 ra, rb;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n add.rn.f32x2 ra, ra, rb;\n mov.b64 {%0, %1}, ra;}"
       : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
-}
-
-// (a0, a1) = (a0, a1) * (b0, b1) + (c0, c1)
-__device__ __forceinline__ void f_fma2v(float& a0, float& a1, float b0, float b1, float c0, float c1) {
-  asm("{.reg .b64 ra, rb, rc;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n mov.b64 rc, {%4, %5};\n"
-      " fma.rn.f32x2 ra, ra, rb, rc;\n mov.b64 {%0, %1}, ra;}"
-      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1), "f"(c0), "f"(c1));
-}
-// 2^x for two finite values at once without the special-function unit (relative error below 1e-4,
-// far inside the rounding of the 16-bit P): x = n + f with n the nearest integer (the "add 1.5 * 2^23"
-// trick leaves n in the low mantissa bits), a cubic for 2^f on [-0.5, 0.5], n added to the exponent.
-// Half of a tile's exponentials go this way so that the ex2 unit, which two CTAs share, is not the
-// longest stretch of a softmax step.
-__device__ __forceinline__ void f_ex2_poly2(float& x0, float& x1) {
-  constexpr float kMagic = 12582912.f;
-  x0 = fmaxf(x0, -125.f);
-  x1 = fmaxf(x1, -125.f);
-  float t0 = x0, t1 = x1;
-  f_add2(t0, t1, kMagic, kMagic);
-  float f0 = t0, f1 = t1;
-  f_add2(f0, f1, -kMagic, -kMagic);                 // n
-  f_fma2v(f0, f1, -1.f, -1.f, x0, x1);              // f = x - n
-  float p0 = 0.05508868f, p1 = 0.05508868f;
-  f_fma2v(p0, p1, f0, f1, 0.24260405f, 0.24260405f);
-  f_fma2v(p0, p1, f0, f1, 0.69327623f, 0.69327623f);
-  f_fma2v(p0, p1, f0, f1, 0.99992895f, 0.99992895f);
-  x0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  x1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 template <typename T>
@@ -288,8 +259,7 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc::tmem_ld_wait();
       const int64_t key0 = int64_t(j) * FBN;
       // tile crosses this row's limit (or the end of the keys): only the diagonal and last tiles
-      const bool edge_tile = __any_sync(0xffffffffu, key0 + FBN - 1 > row_lim);
-      if (edge_tile) {
+      if (__any_sync(0xffffffffu, key0 + FBN - 1 > row_lim)) {
 #pragma unroll
         for (int c = 0; c < FBN; ++c)
           if (key0 + c > row_lim) sv[c] = -INFINITY;
@@ -316,31 +286,15 @@ sdpa_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float nmm = (m_used == -INFINITY) ? 0.f : -m_used;   // a fully masked row keeps p = 0
       float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
       uint32_t pk[FBN / 2];                       // P as packed 16-bit pairs (key 2c, key 2c + 1)
-      if (edge_tile) {
-        // masked entries are -inf here: every exponential on the ex2 unit, which maps them to 0
 #pragma unroll
-        for (int c = 0; c < FBN; c += 4) {
-          f_fma2(sv[c], sv[c + 1], p.scale_log2, nmm);
-          f_fma2(sv[c + 2], sv[c + 3], p.scale_log2, nmm);
-          const float e0 = f_ex2(sv[c]), e1 = f_ex2(sv[c + 1]), e2 = f_ex2(sv[c + 2]), e3 = f_ex2(sv[c + 3]);
-          f_add2(r0, r1, e0, e1);
-          f_add2(r2, r3, e2, e3);
-          pk[c / 2] = pack2<T>(e0, e1);
-          pk[c / 2 + 1] = pack2<T>(e2, e3);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < FBN; c += 4) {
-          f_fma2(sv[c], sv[c + 1], p.scale_log2, nmm);
-          f_fma2(sv[c + 2], sv[c + 3], p.scale_log2, nmm);
-          const float e0 = f_ex2(sv[c]), e1 = f_ex2(sv[c + 1]);
-          float e2 = sv[c + 2], e3 = sv[c + 3];
-          f_ex2_poly2(e2, e3);
-          f_add2(r0, r1, e0, e1);
-          f_add2(r2, r3, e2, e3);
-          pk[c / 2] = pack2<T>(e0, e1);
-          pk[c / 2 + 1] = pack2<T>(e2, e3);
-        }
+      for (int c = 0; c < FBN; c += 4) {
+        f_fma2(sv[c], sv[c + 1], p.scale_log2, nmm);
+        f_fma2(sv[c + 2], sv[c + 3], p.scale_log2, nmm);
+        const float e0 = f_ex2(sv[c]), e1 = f_ex2(sv[c + 1]), e2 = f_ex2(sv[c + 2]), e3 = f_ex2(sv[c + 3]);
+        f_add2(r0, r1, e0, e1);
+        f_add2(r2, r3, e2, e3);
+        pk[c / 2] = pack2<T>(e0, e1);
+        pk[c / 2 + 1] = pack2<T>(e2, e3);
       }
       l_run = l_run * corr + ((r0 + r1) + (r2 + r3));
       const bool rescale = j > 0 && __any_sync(0xffffffffu, corr != 1.f);

@@ -1,6 +1,6 @@
 """Per-operator roofline table at the benchmark configurations.
 
-    python -m kuillm_b200.opbench [--only stream,index,decode,gemm,sdpa] [--iters 20] [--out file.jsonl]
+    python -m kuillm_b200.opbench [--only stream,index,decode,sdpa,gemm] [--iters 20] [--out file.jsonl]
 
 Each line: op, shape, microseconds per launch (CUDA events on the launching stream, after
 warm-up), the algorithmic bytes or flops of one launch, the achieved rate and its fraction of
@@ -361,7 +361,7 @@ def bench_decode_breakdown(T, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="stream,index,decode,gemm,sdpa")
+    ap.add_argument("--only", default="stream,index,decode,sdpa,gemm")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
     ap.add_argument("--match", default="", help='only cases whose "op shape" text contains this')
@@ -376,7 +376,7 @@ def main():
     T = Table(a.out)
     for name in a.only.split(","):
         torch.cuda.synchronize()
-        time.sleep(2.0)          # let the part cool between sections: the dense cases run at the power cap
+        time.sleep(5.0)          # let the part cool between sections: the dense cases run at the power cap
         {"stream": bench_stream, "index": bench_index, "gemm": bench_gemm, "sdpa": bench_sdpa,
          "decode": bench_decode_breakdown}[name](T, a.iters)
         torch.cuda.empty_cache()

@@ -9,7 +9,6 @@ import argparse
 import concurrent.futures
 import os
 import subprocess
-import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent

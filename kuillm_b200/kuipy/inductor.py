@@ -19,7 +19,6 @@ Elementwise maps are left to the compiler on purpose: fusing them is its job.
 import torch
 from torch.utils._pytree import tree_map
 
-from . import kuiops as K
 from . import registry
 
 aten = torch.ops.aten

@@ -21,7 +21,6 @@ import torch
 from . import _ffi
 from . import compile as _compile
 from . import config as C
-from .config import log
 
 aten = torch.ops.aten
 

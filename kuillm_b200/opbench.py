@@ -5,7 +5,7 @@
 Each line: op, shape, microseconds per launch (CUDA events on the launching stream, after
 warm-up), the algorithmic bytes or flops of one launch, the achieved rate and its fraction of
 this pool's measured peak (MEASURED_PEAKS.json next to the repository root, else the fallback
-6650 GB/s / 1590 TFLOP/s).  Memory-bound ops rotate over enough distinct input buffers that the
+6650 GB/s / 1590 TFLOP/s), and of the nominal 8 TB/s / 2.25 PFLOP/s.  Memory-bound ops rotate over enough distinct input buffers that the
 working set exceeds the 126 MB L2.
 """
 import argparse
@@ -103,6 +103,8 @@ class Table:
             row["alg_flops"] = int(flops)
             row["TFLOPs"] = round(flops / us / 1e6, 1)
         row["frac"] = round((row["GBps"] / self.hbm) if bound == "hbm" else (row["TFLOPs"] / self.tf), 3)
+        # the same against the data-sheet figures (8 TB/s HBM3e, 2.25 PFLOP/s dense bf16)
+        row["frac_nominal"] = round((row["GBps"] / 8000.0) if bound == "hbm" else (row["TFLOPs"] / 2250.0), 3)
         if note:
             row["note"] = note
         self.rows.append(row)

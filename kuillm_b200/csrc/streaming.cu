@@ -24,6 +24,7 @@ namespace kuiops {
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct MaxSum { float m, s; };
+constexpr int kSoftmaxInFlight = 8;      // 16-byte loads a thread of the streaming (uncached) form keeps in flight
 
 // Every thread gets the block-wide max (or sum) of v; `red` is a 32-float shared scratch.
 __device__ __forceinline__ float block_allreduce_max(float v, float* red) {
@@ -124,12 +125,12 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
     // reads the slice again (from L2 when the matrix fits there)
     OnlineMaxSum st;
     if (vec_ok) {
-      for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
-        Vec16<T> t[4];
+      for (uint32_t v0 = tid; v0 < nvec; v0 += kSoftmaxInFlight * nt) {      // eight loads in flight per thread
+        Vec16<T> t[kSoftmaxInFlight];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+        for (int u = 0; u < kSoftmaxInFlight; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < kSoftmaxInFlight; ++u)
           if (v0 + u * nt < nvec) {
             float f[VN];
 #pragma unroll
@@ -174,12 +175,12 @@ softmax_rows_kernel(uint32_t m, uint32_t n, const T* X, T* Y,   // Y may alias X
         st16(y + lo + size_t(tid + c * nt) * VN, o);
       }
   } else if (vec_ok) {
-    for (uint32_t v0 = tid; v0 < nvec; v0 += 4 * nt) {
-      Vec16<T> t[4];
+    for (uint32_t v0 = tid; v0 < nvec; v0 += kSoftmaxInFlight * nt) {
+      Vec16<T> t[kSoftmaxInFlight];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
+      for (int u = 0; u < kSoftmaxInFlight; ++u) if (v0 + u * nt < nvec) t[u] = ld16(x + lo + size_t(v0 + u * nt) * VN);
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < kSoftmaxInFlight; ++u)
         if (v0 + u * nt < nvec) {
           Vec16<T> o;
 #pragma unroll

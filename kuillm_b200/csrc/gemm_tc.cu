@@ -144,12 +144,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
+  const uint32_t units = tiles_per_batch * p.batch * p.splits;
+  // one pipeline stage: the P and Q tiles of k-block kb of tile (tp, tq) of batch b
+  auto issue_stage = [&](uint32_t s, uint32_t kb, uint32_t tp, uint32_t tq, uint32_t b) {
+    unsigned char* ps = smem + s * STAGE_BYTES;
+    unsigned char* qs = ps + P_BYTES;
+    tc::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+    const int k0 = int(kb * TBK);
+    if (P_MN) {
+#pragma unroll
+      for (int j = 0; j < TBM / 64; ++j)
+        tc::tma_load_3d(ps + j * (TBK * 128), &tmapP, &full_bar[s], int(tp * TBM) + j * 64, k0, int(b));
+    } else {
+      tc::tma_load_3d(ps, &tmapP, &full_bar[s], k0, int(tp * TBM), int(b));
+    }
+    if (Q_MN) {
+#pragma unroll
+      for (int j = 0; j < BN / 64; ++j)
+        tc::tma_load_3d(qs + j * (TBK * 128), &tmapQ, &full_bar[s], int(tq * BN) + j * 64, k0, int(b));
+    } else {
+      tc::tma_load_3d(qs, &tmapQ, &full_bar[s], k0, int(tq * BN), int(b));
+    }
+  };
+  uint32_t npre = 0;          // stages of the first unit already requested during set-up (thread 0 only)
+
   if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmapP);
+    tc::prefetch_tmap(&tmapQ);
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < ACC_STAGES; ++s) { tc::mbar_init(&acc_full[s], 1); tc::mbar_init(&acc_empty[s], 4); }
     tc::fence_barrier_init();
-    tc::prefetch_tmap(&tmapP);
-    tc::prefetch_tmap(&tmapQ);
+    // The first copies need nothing but these barriers: start them now, so that they fly while the
+    // tensor memory is being allocated and the CTA meets below.  (The operands may still be being
+    // written by the previous kernel in the stream: wait for it first.)
+    pdl_wait();
+    if (blockIdx.x < units) {
+      const uint32_t u = blockIdx.x, split = u % p.splits, tile = u / p.splits;
+      const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
+      uint32_t tp, tq;
+      tile_coords(p, t, tp, tq);
+      const uint32_t kb0 = split * p.kb_per_split;
+      const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
+      npre = min(uint32_t(STAGES), kb1 - kb0);
+      for (uint32_t i = 0; i < npre; ++i) issue_stage(i, kb0 + i, tp, tq, b);
+    }
   }
   if (warp == 1) {
     tc::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -161,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   // everything above touched only this CTA's shared memory, TMEM and the kernel parameters; the
   // operands may still be being written by the previous kernel in the stream
-  pdl_wait();
+  if (threadIdx.x != 0) pdl_wait();      // thread 0 did before it started the first copies
   pdl_trigger();
   // push epilogue: which half of the double-buffered receive areas this launch writes
   unsigned int push_epoch = 0;
@@ -170,9 +209,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     push_epoch = *reinterpret_cast<const volatile unsigned int*>(p.epoch);
     push_off = (uint64_t(push_epoch & 1u) * p.n_ranks + p.my_rank) * p.slot_bytes;
   }
-
-  const uint32_t tiles_per_batch = p.tilesP * p.tilesQ;
-  const uint32_t units = tiles_per_batch * p.batch * p.splits;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -187,26 +223,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         const uint32_t kb0 = split * p.kb_per_split;
         const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kblocks);
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
+          if (it < npre) continue;                    // requested during set-up
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!bounded_wait(&empty_bar[s], ph ^ 1)) { atomicExch(p.err, 1u); ok = false; break; }
-          unsigned char* ps = smem + s * STAGE_BYTES;
-          unsigned char* qs = ps + P_BYTES;
-          tc::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          const int k0 = int(kb * TBK);
-          if (P_MN) {
-#pragma unroll
-            for (int j = 0; j < TBM / 64; ++j)
-              tc::tma_load_3d(ps + j * (TBK * 128), &tmapP, &full_bar[s], int(tp * TBM) + j * 64, k0, int(b));
-          } else {
-            tc::tma_load_3d(ps, &tmapP, &full_bar[s], k0, int(tp * TBM), int(b));
-          }
-          if (Q_MN) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tc::tma_load_3d(qs + j * (TBK * 128), &tmapQ, &full_bar[s], int(tq * BN) + j * 64, k0, int(b));
-          } else {
-            tc::tma_load_3d(qs, &tmapQ, &full_bar[s], k0, int(tq * BN), int(b));
-          }
+          issue_stage(s, kb, tp, tq, b);
         }
       }
     }

@@ -893,7 +893,9 @@ class DataMoveImpl(_Family):
         X = args[0]
         if func is aten._to_copy.default:
             dt = kwargs.get("dtype") or X.dtype
-            plain = (kwargs.get("device") in (None, X.device) and kwargs.get("layout") in (None, torch.strided)
+            dev = kwargs.get("device")
+            same_gpu = dev is None or (torch.device(dev).type == "cuda" and torch.device(dev) == X.device)
+            plain = (same_gpu and kwargs.get("layout") in (None, torch.strided)
                      and not kwargs.get("pin_memory") and kwargs.get("memory_format") in (None, torch.preserve_format, torch.contiguous_format))
             if len(args) == 1 and self._dense(X) and plain and X.dtype in self._FLOATS and dt in self._FLOATS:
                 return ("cast", dt, [X])

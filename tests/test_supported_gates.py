@@ -125,3 +125,31 @@ def test_new_families_gate_like_torch_signatures(gates):
     assert rd.supported(aten.any.default, (f((9,), torch.bool),), {}) is not None
     assert rd.supported(aten.max.default, (f((9,), torch.int64),), {}) is not None
     assert rd.supported(aten.max.default, (f((9,), torch.bfloat16),), {}) is None
+
+
+def test_datamove_gates_on_metadata_only():
+    """What the per-token data-movement family takes and what it leaves to PyTorch (no GPU: the
+    gates only read tensor metadata)."""
+    aten = torch.ops.aten
+    impl = kuiops.DataMoveImpl({})
+    X = FakeCudaTensor(torch.zeros(4, 6, 64, dtype=torch.bfloat16))
+    M = FakeCudaTensor(torch.zeros(4, 6, 64, dtype=torch.bool))
+    ids = FakeCudaTensor(torch.zeros(3, 5, dtype=torch.int64))
+    W = FakeCudaTensor(torch.zeros(100, 32, dtype=torch.float16))
+    assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.float32})[:2] == ("cast", torch.float32)
+    assert impl.supported(aten._to_copy.default, (X,), {})[:2] == ("cast", torch.bfloat16)
+    assert impl.supported(aten.clone.default, (X,), {})[0] == "cast"
+    assert impl.supported(aten.masked_fill.Scalar, (X, M, -3.0), {})[:2] == ("masked_fill", -3.0)
+    assert impl.supported(aten.argmax.default, (X, 2), {})[0] == "argmax"
+    assert impl.supported(aten.embedding.default, (W, ids), {})[0] == "embedding"
+    # left to PyTorch
+    assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.int64}) is None
+    assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.float32, "device": torch.device("cpu")}) is None
+    assert impl.supported(aten._to_copy.default, (torch.zeros(4, 4),), {"dtype": torch.bfloat16}) is None      # not on the GPU
+    assert impl.supported(aten.clone.default, (X,), {"memory_format": torch.channels_last}) is None
+    assert impl.supported(aten.masked_fill.Scalar, (X, FakeCudaTensor(torch.zeros(6, 64, dtype=torch.bool)), 0.0), {}) is None
+    assert impl.supported(aten.masked_fill.Scalar, (X, M, True), {}) is None
+    assert impl.supported(aten.argmax.default, (X,), {}) is None and impl.supported(aten.argmax.default, (X, 1), {}) is None
+    assert impl.supported(aten.argmax.default, (X, -1, True), {}) is None
+    assert impl.supported(aten.embedding.default, (W, FakeCudaTensor(torch.zeros(3, dtype=torch.int32))), {}) is None
+

@@ -16,7 +16,7 @@ Parity pin: ``tests/test_oracle_golden.py`` checks every function here against
 eager (the reference tests' own oracle), and the comparator against the reference's
 ``kuipy._verify_compare`` outputs recorded in ``tests/golden/verify_golden.json``.  For topk,
 isin, index, reduce and causal / grouped-query attention the reference has neither kernel nor
-test: those are pinned by PyTorch semantics only.
+test: parity unpinned by the reference; those are pinned by PyTorch semantics only.
 """
 import math
 

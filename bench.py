@@ -95,11 +95,13 @@ def measured_peaks():
 # ---------------------------------------------------------------------------------------------
 # the reference arm: the reference's CPU path = stock PyTorch eager generation on host cores
 # ---------------------------------------------------------------------------------------------
-def cpu_reference_sample(workload, seconds_budget=25.0):
+def cpu_reference_sample(workload):
     """Time torch-eager greedy generation (the reference with Kuiper off, infer.py:135-148) of a
     Llama-shaped model on the host CPU, on a bounded sample of the workload: the same layer
-    dimensions, but 1 layer and a short prompt, extrapolated linearly in layers and tokens.
-    Returns (tok_per_s at the full workload's shape, description, threads)."""
+    dimensions and vocabulary, but 1 and 2 layers, a small batch and a short prompt.  The two
+    layer counts separate the per-layer cost from the fixed cost (embedding, vocabulary GEMM), so
+    the extrapolation to the full depth does not multiply the fixed part; batch and prompt scale
+    linearly.  Returns (tok_per_s at the full workload's shape, description, threads)."""
     import torch
     from transformers import LlamaConfig, LlamaForCausalLM
     cfg_kw, batch, prompt, new = WORKLOADS[workload]
@@ -107,34 +109,42 @@ def cpu_reference_sample(workload, seconds_budget=25.0):
     if cfg_kw:
         full.update(cfg_kw)
     threads = torch.get_num_threads()
-    sample_layers = 1 if full["n_layers"] > 2 else full["n_layers"]
-    s_batch, s_prompt, s_new = min(batch, 4), min(prompt, 64), min(new, 4)
-    hf = LlamaConfig(hidden_size=full["d_model"], intermediate_size=full["d_ff"], num_hidden_layers=sample_layers,
+    s_batch, s_prompt, s_new = min(batch, 4), min(prompt, 256), min(new, 8)
+    hf = LlamaConfig(hidden_size=full["d_model"], intermediate_size=full["d_ff"], num_hidden_layers=2,
                      num_attention_heads=full["n_heads"], num_key_value_heads=full["n_kv_heads"], head_dim=full["head_dim"],
                      vocab_size=full["vocab"], rms_norm_eps=1e-5, rope_theta=5e5, max_position_embeddings=8192,
                      tie_word_embeddings=False)
     torch.manual_seed(0)
     model = LlamaForCausalLM(hf).eval()
     ids = torch.randint(0, full["vocab"], (s_batch, s_prompt))
+    ids_short = ids[:, :16]                            # decode steps are timed behind a short prompt, so that
+    s_new = max(s_new, 2)                              # the prefill's run-to-run noise does not swamp them
 
-    def timed(n_new):
+    def timed(inp, n_new):
         t0 = time.perf_counter()
         with torch.no_grad():
-            model.generate(ids, max_new_tokens=n_new, min_new_tokens=n_new, do_sample=False, pad_token_id=0)
+            model.generate(inp, max_new_tokens=n_new, min_new_tokens=n_new, do_sample=False, pad_token_id=0)
         return time.perf_counter() - t0
-    timed(1)                                   # warm-up
-    t_prefill = timed(1)                       # prefill = time to the first token (infer_minimal.py:68-69)
-    t_total = timed(s_new)
-    t_decode_tok = max(t_total - t_prefill, 1e-9) / max(s_new - 1, 1)
-    # extrapolate: prefill time scales with layers x prompt tokens x batch; a decode step with layers x batch
-    scale_l = full["n_layers"] / sample_layers
-    t_prefill_full = t_prefill * scale_l * (prompt / s_prompt) * (batch / s_batch)
-    t_decode_full = t_decode_tok * scale_l * (batch / s_batch) * (new - 1)
+
+    pre, dec = {}, {}
+    for layers in (1, 2):
+        model.config.num_hidden_layers = layers        # the model walks layers[:num_hidden_layers]
+        timed(ids, 1)                                  # warm-up
+        pre[layers] = min(timed(ids, 1), timed(ids, 1))      # prefill = time to the first token (infer_minimal.py:68-69)
+        first = min(timed(ids_short, 1), timed(ids_short, 1))
+        dec[layers] = max(timed(ids_short, s_new) - first, 1e-9) / (s_new - 1)
+    # t(L) = fixed + per_layer * L
+    pre_layer, dec_layer = max(pre[2] - pre[1], 0.0), max(dec[2] - dec[1], 0.0)
+    pre_fixed, dec_fixed = max(pre[1] - pre_layer, 0.0), max(dec[1] - dec_layer, 0.0)
+    L = full["n_layers"]
+    t_prefill_full = (pre_fixed + pre_layer * L) * (prompt / s_prompt) * (batch / s_batch)
+    t_decode_full = (dec_fixed + dec_layer * L) * (batch / s_batch) * (new - 1)
     tok_s = batch * new / (t_prefill_full + t_decode_full)
-    desc = (f"torch eager fp32 on CPU, HF LlamaForCausalLM with the workload's layer dims, {sample_layers} of "
-            f"{full['n_layers']} layers, batch {s_batch}, prompt {s_prompt}, {s_new} new tokens; measured prefill "
-            f"{t_prefill:.2f}s, {t_decode_tok * 1e3:.0f} ms/decode step; scaled linearly in layers, batch and tokens "
-            f"(attention's quadratic term ignored, which favours the CPU)")
+    desc = (f"torch eager fp32 on CPU, HF LlamaForCausalLM with the workload's layer dims and vocabulary, 1 and 2 of "
+            f"{L} layers, batch {s_batch}, prompt {s_prompt}, {s_new} new tokens; measured per layer: prefill "
+            f"{pre_layer:.2f}s, decode step {dec_layer * 1e3:.0f} ms; fixed part: prefill {pre_fixed:.2f}s, decode step "
+            f"{dec_fixed * 1e3:.0f} ms; extrapolated linearly in layers, batch and tokens (attention's quadratic term "
+            f"ignored, which favours the CPU)")
     return tok_s, desc, threads
 
 

@@ -210,9 +210,12 @@ KUIOPS_API int kuiops_bmm_f16 (uint32_t batch, uint32_t M, uint32_t K, uint32_t 
  * kernel-allocated out/lse, kuiops/sdpa/wrapper_sdpa.cu.j2:21-27; extended with
  * h_kv, is_causal, strides and caller-owned outputs.
  * bf16/f16 with e == ev == 128, no bias and l >= 64 run on the tcgen05 flash
- * kernel; short-query calls (l <= 8, decode) run on the split-KV kernel, which
- * needs kuiops_sdpa_workspace_bytes(...) of workspace; the rest use the generic
- * SIMT kernel. */
+ * kernel; short-query calls (l <= 16 with at most 128 query rows per KV head:
+ * decode) run on the tcgen05 split-KV kernel, which spreads the keys of a
+ * (batch, KV head) over several CTAs when there are few such pairs and then
+ * needs kuiops_sdpa_workspace_bytes(...) of zero-initialised workspace (the query
+ * returns 0 when no split is planned); everything else (bias, other head
+ * dimensions, fp32) uses the generic SIMT kernel. */
 KUIOPS_API size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
                                    uint32_t l, uint32_t s, uint32_t e, uint32_t ev);
 KUIOPS_API int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
@@ -229,8 +232,9 @@ KUIOPS_API int kuiops_sdpa(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
  * kv_lens[b] (int64, clamped to [0, s]) replaces s for entry b, s stays the
  * upper bound (the cache capacity in use).  A decode step whose launch
  * arguments never change can then be captured once in a CUDA graph and replayed
- * while the cache grows.  kv_lens == NULL is kuiops_sdpa.  Always runs on the
- * split-KV SIMT kernel.  No counterpart in the reference. */
+ * while the cache grows.  kv_lens == NULL is kuiops_sdpa.  Runs on the split-KV
+ * kernels (tcgen05 where the shape allows, SIMT otherwise), never on the flash
+ * kernel.  No counterpart in the reference. */
 KUIOPS_API int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_kv,
                 uint32_t l, uint32_t s, uint32_t e, uint32_t ev,
                 const void* Q, int64_t q_sn, int64_t q_sh, int64_t q_sl,

@@ -118,6 +118,20 @@ KUIOPS_API int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, const void* W, int64_t ldw, void* Y, int64_t ldy,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
 
+/* Packed QKV projection of a decode-sized step with the rotary embedding and the KV-cache append
+ * in its epilogue: qkv[m, :] = A[m, :] x W^T with W = [(hq + 2 hk) * 128, K] (q heads, then k heads,
+ * then v heads, head dimension 128); q and k heads get the rotary embedding of positions[m]
+ * (rotate-half convention, base theta), and k / v heads are also written to
+ * k_cache / v_cache[(m / rows_per_seq), kv head, positions[m], :] (capacity cache_cap rows per
+ * sequence; the caches may be NULL).  Results are bit for bit those of kuiops_gemm followed by
+ * kuiops_rope_qkv.  bf16 / f16, M <= 128, tensor-core alignment rules, and K large enough for the
+ * split-K placement (KUIOPS_EUNSUPPORTED otherwise: run the two calls).  The dispatcher sees this
+ * as mm, mul, cat, neg, add (kuipy/kuiops.py:158-166 of the reference); no reference counterpart. */
+KUIOPS_API int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32_t d, uint32_t K,
+                const void* A, int64_t lda, const void* W, int64_t ldw, void* qkv, int64_t ldq,
+                const int64_t* positions, float theta, void* k_cache, void* v_cache, uint64_t cache_cap,
+                uint32_t rows_per_seq, kuiops_stream_t stream);
+
 /* Tensor-parallel row-split GEMM fused with the first half of its all-reduce (decode shapes,
  * M <= 128, bf16 / f16): rank `rank` of `n_ranks` computes its partial product A x B (B as in
  * kuiops_gemm: [K,N], or [N,K] when trans_b) and the epilogue stores it, through peer pointers,

@@ -13,6 +13,15 @@ struct GemmPush {
   unsigned int* ticket;
 };
 
+// Rotary embedding + KV-cache append fused into the packed QKV projection: see kuiops_gemm_rope_qkv.
+struct GemmRope {
+  const int64_t* positions;
+  float theta;
+  void* k_cache; void* v_cache;
+  uint64_t cache_cap;
+  uint32_t hq, hk, rows_per_seq;
+};
+
 struct GemmArgs {
   int dtype, out_dtype;
   uint32_t batch, M, N, K;
@@ -21,8 +30,9 @@ struct GemmArgs {
   const void* Cin; int64_t ldcin, stride_cin;
   float alpha, beta;
   void* C; int64_t ldc, stride_c;
+  const GemmRope* rope;   // epilogue 2 only
   const GemmPush* push;   // non-null: partial sums go to every rank's receive area instead of C
-  int epilogue;   // 0: C = alpha*acc + beta*Cin;  1: C[m, j] = silu(acc[m, 2j]) * acc[m, 2j+1] (gate/up rows interleaved in B)
+  int epilogue;   // 0: C = alpha*acc + beta*Cin;  1: C[m, j] = silu(acc[m, 2j]) * acc[m, 2j+1] (gate/up rows interleaved in B);  2: rotary embedding + cache append (rope)
 };
 
 // SIMT kernel: any dtype / shape / stride.

@@ -92,6 +92,27 @@ int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K, const void
   return gemm_tc(a, workspace, workspace_bytes, as_stream(stream));
 }
 
+int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32_t d, uint32_t K,
+                         const void* A, int64_t lda, const void* W, int64_t ldw, void* qkv, int64_t ldq,
+                         const int64_t* positions, float theta, void* k_cache, void* v_cache, uint64_t cache_cap,
+                         uint32_t rows_per_seq, kuiops_stream_t stream) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || hq == 0 || K == 0 || !A || !W || !qkv || !positions || !(theta > 0.f)) return KUIOPS_EINVAL;
+  if ((k_cache == nullptr) != (v_cache == nullptr) || (k_cache && cache_cap == 0)) return KUIOPS_EINVAL;
+  if (d != 128 || M > 128) return KUIOPS_EUNSUPPORTED;         // one 128-feature tile per head, decode-sized steps
+  const uint64_t N = uint64_t(hq + 2 * hk) * d;
+  if (N > 0x7FFFFFFFull || lda < int64_t(K) || ldw < int64_t(K) || ldq < int64_t(N)) return KUIOPS_EINVAL;
+  GemmRope rope = {};
+  rope.positions = positions; rope.theta = theta; rope.k_cache = k_cache; rope.v_cache = v_cache;
+  rope.cache_cap = cache_cap; rope.hq = hq; rope.hk = hk; rope.rows_per_seq = rows_per_seq ? rows_per_seq : 1u;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = uint32_t(N); a.K = K;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
+  a.alpha = 1.f; a.beta = 0.f; a.C = qkv; a.ldc = ldq; a.epilogue = 2; a.rope = &rope;
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  return gemm_tc(a, nullptr, 0, as_stream(stream));
+}
+
 int kuiops_gemm_push(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, int trans_b, uint32_t n_ranks, uint32_t rank,
                      const uint64_t* peer_base, uint64_t slot_bytes, uint64_t flags_offset,

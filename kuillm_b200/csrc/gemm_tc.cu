@@ -48,6 +48,14 @@ struct TcParams {
   uint64_t slot_bytes, flags_offset;
   const unsigned int* epoch;          // device word, advanced by the consumer of the partials
   unsigned int* ticket;               // device word, zero between launches
+  // "rope" epilogue (epi == 2, swapped placement, split K): the output rows are packed q | k | v heads
+  // of 128; q and k heads get the rotary embedding of their row's position, k and v heads are also
+  // appended to the caches
+  const long long* positions;
+  float log2_theta;
+  void* k_cache; void* v_cache;
+  uint64_t cache_cap;
+  uint32_t hq, hk, rows_per_seq;
 };
 
 __device__ unsigned int g_tc_error = 0;
@@ -118,6 +126,41 @@ __device__ __forceinline__ void store_swiglu_swapped(const TcParams& p, uint32_t
   const size_t off = size_t(col) * p.ldc + (lane_row >> 1);
   if (p.out_f32) static_cast<float*>(p.C)[off] = v;
   else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
+}
+
+// Rotary embedding + KV-cache append on a finished element of the packed QKV projection (swapped
+// placement: lane_row = output feature n, col = row m).  `acc` is the element itself, `pacc` its
+// partner at feature n ^ 64 inside the same head of 128.  The arithmetic repeats, rounding for
+// rounding, what the separate kernel does on the stored projection (and what eager does): the
+// projection is rounded to the element type first, cos / sin are computed in fp32 and rounded,
+// each product and the sum are rounded.
+template <typename TIN>
+__device__ __forceinline__ void store_rope(const TcParams& p, uint32_t lane_row, uint32_t col, float acc, float pacc) {
+  const uint32_t m = col, n = lane_row;
+  if (m >= p.M || n >= p.N) return;
+  auto rnd = [](float x) { return ElemTraits<TIN>::to_f(ElemTraits<TIN>::from_f(x)); };
+  const uint32_t head = n >> 7, j = n & 127u, i = j & 63u;
+  const bool hi = j >= 64;
+  const long long pos = p.positions[m];
+  const float own = rnd(p.alpha * acc), partner = rnd(p.alpha * pacc);
+  float val = own;
+  if (head < p.hq + p.hk) {
+    const float inv_freq = exp2f(-p.log2_theta * (2.f * float(i) / 128.f));
+    float sn, cs;
+    sincosf(float(pos) * inv_freq, &sn, &cs);
+    const float csr = rnd(cs), snr = rnd(sn);
+    const float a = hi ? partner : own, b = hi ? own : partner;      // (x[i], x[i + 64])
+    val = hi ? rnd(rnd(b * csr) + rnd(a * snr)) : rnd(rnd(a * csr) + rnd(-b * snr));
+  }
+  const TIN out = ElemTraits<TIN>::from_f(val);
+  static_cast<TIN*>(p.C)[size_t(m) * p.ldc + n] = out;
+  if (head >= p.hq && p.k_cache != nullptr && pos >= 0 && uint64_t(pos) < p.cache_cap) {
+    const bool is_k = head < p.hq + p.hk;
+    const uint32_t kvh = is_k ? head - p.hq : head - p.hq - p.hk;
+    const uint64_t seq = m / p.rows_per_seq;
+    TIN* dst = static_cast<TIN*>(is_k ? p.k_cache : p.v_cache) + ((seq * p.hk + kvh) * p.cache_cap + uint64_t(pos)) * 128 + j;
+    *dst = out;
+  }
 }
 
 template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
@@ -432,7 +475,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         float sum = part[0];
 #pragma unroll
         for (int s2 = 1; s2 < 8; ++s2) sum += part[s2];
-        if (p.epi == 1) store_swiglu_swapped<TIN>(p, row, col0 + c, sum);
+        if (p.epi == 2) {
+          // the rotary partner (feature n ^ 64 of the same head) is summed the same way, slice by slice
+          float psum = peer[0][c * TBM + (lane_in_tile ^ 64u)];
+#pragma unroll
+          for (int s2 = 1; s2 < 8; ++s2) psum += s2 < int(p.splits) ? peer[s2][c * TBM + (lane_in_tile ^ 64u)] : 0.f;
+          store_rope<TIN>(p, row, col0 + c, sum, psum);
+        } else if (p.epi == 1) store_swiglu_swapped<TIN>(p, row, col0 + c, sum);
         else store_elem<TIN>(p, b, row, col0 + c, sum, push_off);
       }
     }
@@ -642,6 +691,13 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.C = a.C; p.ldc = a.ldc; p.stride_c = a.stride_c;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
+  if (a.epilogue == 2) {
+    // needs the swapped placement with K split (the partner feature is read from the parked partials)
+    if (!pl.swapped || pl.splits < 2 || a.batch != 1 || !a.rope || a.out_dtype != a.dtype) return KUIOPS_EUNSUPPORTED;
+    p.positions = reinterpret_cast<const long long*>(a.rope->positions); p.log2_theta = log2f(a.rope->theta);
+    p.k_cache = a.rope->k_cache; p.v_cache = a.rope->v_cache; p.cache_cap = a.rope->cache_cap;
+    p.hq = a.rope->hq; p.hk = a.rope->hk; p.rows_per_seq = a.rope->rows_per_seq ? a.rope->rows_per_seq : 1u;
+  }
   if (a.push) {
     if (!pl.swapped || a.epilogue != 0 || a.batch != 1) return KUIOPS_EUNSUPPORTED;
     p.n_ranks = a.push->n_ranks; p.my_rank = a.push->rank;

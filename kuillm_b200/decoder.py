@@ -163,8 +163,12 @@ class Decoder:
                 h = _ffi.rmsnorm_gather(ex, rows, L["n1"], cfg.eps, resid)
             else:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)      # resid += x ; h = norm(resid)
-            qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)                  # [rows, (hq + 2 hk) * hd]
-            _ffi.rope_qkv(qkv, hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
+            # decode-sized steps: projection, rotary embedding and cache append in one launch
+            qkv = _ffi.gemm_rope_qkv(h, L["wqkv"], hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li],
+                                     rows_per_seq=seq) if rows <= 128 and hd == 128 else None
+            if qkv is None:
+                qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)              # [rows, (hq + 2 hk) * hd]
+                _ffi.rope_qkv(qkv, hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
             W = qkv.shape[1]
             q4 = qkv.as_strided((B, hq, seq, hd), (seq * W, hd, W, 1))
             attn = torch.empty((rows, hq * hd), device=self.device, dtype=cfg.dtype)

@@ -58,6 +58,8 @@ SIGNATURES = {
                             c_void_p, c_i64, c_i64, c_void_p, c_size_t, c_void_p]),
     "kuiops_gemm_swiglu": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
                                    c_void_p, c_size_t, c_void_p]),
+    "kuiops_gemm_rope_qkv": (c_int, [c_int, c_u32, c_u32, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
+                                     c_void_p, c_float, c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
     "kuiops_gemm_push": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_int, c_u32, c_u32, _P64,
                                  c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
     "kuiops_rmsnorm_gather": (c_int, [c_int, c_u64, c_u32, c_u32, c_void_p, c_u64, c_u64, c_void_p, c_void_p, c_void_p,
@@ -258,6 +260,25 @@ def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dt
                          A.data_ptr(), lda, sa, B.data_ptr(), ldb, sb, 1 if trans_b else 0,
                          cin_p, ldcin, scin, float(alpha), float(beta),
                          out.data_ptr(), ldc, sc, ws.data_ptr(), ws.numel(), _stream()), "gemm")
+    return out
+
+
+def gemm_rope_qkv(A, W, hq, hk, d, positions, theta, k_cache=None, v_cache=None, rows_per_seq=1, out=None):
+    """Packed QKV projection with the rotary embedding and the KV-cache append in the GEMM's epilogue;
+    None when the shape does not suit the fused kernel (the caller then runs gemm + rope_qkv)."""
+    M, K = A.shape
+    N = (hq + 2 * hk) * d
+    if A.dtype not in (torch.bfloat16, torch.float16) or A.stride(1) != 1 or W.stride(1) != 1 or W.shape[0] != N:
+        return None
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    cap = k_cache.shape[2] if k_cache is not None else 0
+    rc = lib().kuiops_gemm_rope_qkv(dtype_code(A.dtype), M, hq, hk, d, K, A.data_ptr(), max(A.stride(0), K), W.data_ptr(), W.stride(0),
+                                    out.data_ptr(), max(out.stride(0), N), positions.data_ptr(), float(theta), _ptr(k_cache),
+                                    _ptr(v_cache), cap, rows_per_seq, _stream())
+    if rc == EUNSUPPORTED:
+        return None
+    _check(rc, "gemm_rope_qkv")
     return out
 
 

@@ -103,3 +103,27 @@ def test_rope_prefill_sized_call_equals_row_chunks(cuda):
     assert torch.equal(big, small) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert not torch.equal(big, qkv)
 
+
+@pytest.mark.parametrize("M,hq,hk,K", [(32, 32, 8, 4096), (5, 4, 2, 1024), (128, 8, 8, 2048)])
+def test_qkv_projection_with_rope_epilogue_equals_two_kernels(cuda, M, hq, hk, K):
+    """The fused projection + rotary embedding + cache append must reproduce gemm followed by
+    rope_qkv bit for bit: packed rows and both caches."""
+    from kuipy import _ffi
+    d, cap = 128, 64
+    g = torch.Generator().manual_seed(21)
+    A = torch.randn(M, K, generator=g).bfloat16().cuda()
+    W = (torch.randn((hq + 2 * hk) * d, K, generator=g) / K ** 0.5).bfloat16().cuda()
+    pos = torch.randint(0, cap, (M,), generator=g).cuda()
+    kc1, vc1 = (torch.zeros(M, hk, cap, d, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    ref = _ffi.gemm(A, W, trans_b=True)
+    plain = ref.clone()
+    _ffi.rope_qkv(ref, hq, hk, d, pos, 5e5, kc1, vc1, rows_per_seq=1)
+    out = _ffi.gemm_rope_qkv(A, W, hq, hk, d, pos, 5e5, kc2, vc2, rows_per_seq=1)
+    assert out is not None, "the shape is meant to take the fused kernel"
+    assert torch.equal(out, ref) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert not torch.equal(out, plain) and _ffi.tc_error() == 0
+    # too little K for the split-K placement: the caller is told to run the two kernels
+    small = _ffi.gemm_rope_qkv(A[:, :128].contiguous(), W[:, :128].contiguous(), hq, hk, d, pos, 5e5, kc2, vc2, rows_per_seq=1)
+    assert small is None
+

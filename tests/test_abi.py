@@ -92,6 +92,22 @@ def test_tensor_parallel_push_and_gather_contracts():
     assert gather(n=4100, slot_bytes=32 * 4100 * 2, flags_offset=4 * 32 * 4100 * 2) == _ffi.EUNSUPPORTED   # rows must be whole 16-byte vectors
 
 
+def test_qkv_projection_with_rope_epilogue_contracts():
+    """Argument checks of the fused QKV projection; every call below is refused before a launch."""
+    L = _ffi.lib()
+
+    def qkv(dtype=_ffi.BF16, M=32, hq=32, hk=8, d=128, K=4096, lda=4096, ldw=4096, ldq=48 * 128, positions=P,
+            theta=5e5, k_cache=P, v_cache=P, cap=4096):
+        return L.kuiops_gemm_rope_qkv(dtype, M, hq, hk, d, K, P, lda, P, ldw, P, ldq, positions, theta,
+                                      k_cache, v_cache, cap, 1, None)
+    assert qkv(dtype=_ffi.F32) == _ffi.EUNSUPPORTED                      # 16-bit operands only
+    assert qkv(M=0) == _ffi.EINVAL and qkv(positions=None) == _ffi.EINVAL and qkv(theta=0.0) == _ffi.EINVAL
+    assert qkv(v_cache=None) == _ffi.EINVAL                              # both caches or neither
+    assert qkv(cap=0) == _ffi.EINVAL                                     # a cache needs a capacity
+    assert qkv(d=64) == _ffi.EUNSUPPORTED and qkv(M=256) == _ffi.EUNSUPPORTED
+    assert qkv(ldq=47 * 128) == _ffi.EINVAL and qkv(lda=2048) == _ffi.EINVAL and qkv(ldw=2048) == _ffi.EINVAL
+
+
 def test_softmax_mean_topk_contracts():
     L = _ffi.lib()
     assert L.kuiops_softmax_f32(0, 8, P, P, None) == _ffi.EINVAL

@@ -482,6 +482,12 @@ KUIOPS_API int kuiops_embedding(uint32_t elem_bytes, uint64_t rows, uint64_t wid
 /* Row arg-max of an [m, n] matrix (greedy sampling); ties -> lowest index. */
 KUIOPS_API int kuiops_argmax(int dtype, uint64_t m, uint64_t n, const void* X, int64_t* out,
                   kuiops_stream_t stream);
+/* Inclusive prefix sum along the rows of an [m, n] matrix (aten.cumsum over the last axis): the
+ * position ids a decoder derives from its attention mask (int64, wraps like the eager sum) and the
+ * cumulative probabilities of nucleus sampling (fp32).  m * n <= 2^31.  Backlog in the reference
+ * (KERNELS.md:68-90): no counterpart. */
+KUIOPS_API int kuiops_cumsum_f32(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
+KUIOPS_API int kuiops_cumsum_i64(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
 
 #ifdef __cplusplus
 }

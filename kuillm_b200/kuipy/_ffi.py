@@ -100,6 +100,8 @@ SIGNATURES = {
     "kuiops_cast": (c_int, [c_int, c_int, c_u64, c_void_p, c_void_p, c_void_p]),
     "kuiops_masked_fill": (c_int, [c_int, c_u64, c_void_p, c_void_p, c_double, c_void_p, c_void_p]),
     "kuiops_embedding": (c_int, [c_u32, c_u64, c_u64, c_u64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "kuiops_cumsum_f32": (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p]),
+    "kuiops_cumsum_i64": (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p]),
     "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
 }
 for _sfx in ("f32", "bf16", "f16"):
@@ -485,6 +487,22 @@ def argmax_lastdim(X):
     m = Xc.numel() // n
     out = torch.empty(tuple(Xc.shape[:-1]), dtype=torch.int64, device=Xc.device)
     _check(lib().kuiops_argmax(dtype_code(Xc.dtype), m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def cumsum_lastdim(X, out=None):
+    """Inclusive prefix sum over the last axis of a float32 or int64 tensor."""
+    Xc = X.contiguous()
+    n = Xc.shape[-1]
+    m = Xc.numel() // n
+    fn = {torch.float32: lib().kuiops_cumsum_f32, torch.int64: lib().kuiops_cumsum_i64}.get(Xc.dtype)
+    if fn is None:
+        raise KuiopsError(EUNSUPPORTED, f"cumsum over {Xc.dtype}")
+    if out is None:
+        out = torch.empty_like(Xc)
+    elif out.shape != Xc.shape or out.dtype != Xc.dtype or not out.is_contiguous() or out.device != Xc.device:
+        raise KuiopsError(EINVAL, "cumsum: out must be a dense tensor like the input")
+    _check(fn(m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "cumsum")
     return out
 
 

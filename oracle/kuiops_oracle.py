@@ -188,6 +188,14 @@ def softmax_lastdim(X: np.ndarray) -> np.ndarray:
     return z / z.sum(axis=-1, keepdims=True)
 
 
+def cumsum_lastdim(X: np.ndarray) -> np.ndarray:
+    """aten.cumsum over the last axis (backlog in the reference, KERNELS.md:68-90; semantics are
+    torch.cumsum's).  Floats are accumulated in float64 and rounded once; int64 wraps."""
+    if np.issubdtype(X.dtype, np.floating):
+        return np.cumsum(X.astype(np.float64), axis=-1).astype(X.dtype)
+    return np.cumsum(X, axis=-1, dtype=X.dtype)
+
+
 def mean_lastdim(X: np.ndarray) -> np.ndarray:
     """sum_j (x[i,j] / n), keepdim: the division is part of the pre-map
     (kuiops/mean/Kuiops.Mean.fsti:25-32)."""

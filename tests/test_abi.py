@@ -119,6 +119,14 @@ def test_softmax_mean_topk_contracts():
     assert L.kuiops_reduce_i64(_ffi.REDUCE_ALL, 16, P, P, P, 1 << 20, None) == _ffi.EUNSUPPORTED
 
 
+def test_cumsum_contracts():
+    L = _ffi.lib()
+    for f in (L.kuiops_cumsum_f32, L.kuiops_cumsum_i64):
+        assert f(0, 8, P, P, None) == _ffi.EINVAL and f(8, 0, P, P, None) == _ffi.EINVAL
+        assert f(8, 8, None, P, None) == _ffi.EINVAL and f(8, 8, P, None, None) == _ffi.EINVAL
+        assert f(1 << 16, (1 << 15) + 1, P, P, None) == _ffi.ELIMIT          # m * n <= 2^31
+
+
 def test_gather_scatter_contracts():
     L = _ffi.lib()
     # shape_le off the gathered axis

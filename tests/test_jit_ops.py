@@ -215,6 +215,28 @@ def test_argmax_lowest_index_of_the_maximum(cuda, dtype, shape):
     assert torch.equal(got.cpu(), ref)
 
 
+@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (5, 4097), (7, 1001), (64, 128256), (32, 2048), (4096, 33), (2, 70001)])
+def test_cumsum_over_the_last_axis(cuda, gates, shape):
+    """Prefix sums over one CTA or a cluster per row; rows that do not start on 16 bytes; tails."""
+    gates("wide")
+    impl = kuiops.DataMoveImpl({})
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(-5, 9, shape, generator=g, dtype=torch.int64)
+    ids[0, 0] = (1 << 62)                                # wraps like the eager sum
+    if shape[1] > 2:
+        ids[0, 1] = (1 << 62)
+        ids[0, 2] = (1 << 62)
+    got = run_family(impl, aten.cumsum.default, (ids.cuda(), -1))
+    assert got.dtype == torch.int64
+    assert_bit_exact(got, O.cumsum_lastdim(ids.numpy()))
+    P = torch.softmax(torch.randn(*shape, generator=g) * 3, dim=-1)      # the nucleus-sampling input
+    got = run_family(impl, aten.cumsum.default, (P.cuda(), len(shape) - 1))
+    assert_fp32_1e5(got, O.cumsum_lastdim(P.numpy()))
+    mask = (torch.rand(*shape, generator=g) > 0.2).long()
+    got = run_family(impl, aten.cumsum.default, (mask.cuda(), -1), {"dtype": torch.int64})
+    assert torch.equal(got.cpu(), mask.cumsum(-1))
+
+
 def test_softmax_long_rows_in_clusters(cuda):
     """64 rows of 128256 fp32: eight CTAs per row, streamed twice; and a row of -inf except one entry."""
     X = randn(64, 128256) * 3
@@ -265,6 +287,7 @@ def test_datamove_family_matches_eager(cuda, gates):
     assert impl.supported(aten.masked_fill.Scalar, (X, M[0], 0.0), {}) is None          # broadcast mask
     assert impl.supported(aten.argmax.default, (X,), {}) is None                        # flattened arg-max
     assert impl.supported(aten.argmax.default, (X, 0), {}) is None
+    assert impl.supported(aten.cumsum.default, (X, -1), {}) is None                     # bf16 sums stay with PyTorch
     gates("reference")
     from kuipy import registry
     assert aten._to_copy.default not in registry.table()

@@ -142,6 +142,9 @@ def test_datamove_gates_on_metadata_only():
     assert impl.supported(aten.masked_fill.Scalar, (X, M, -3.0), {})[:2] == ("masked_fill", -3.0)
     assert impl.supported(aten.argmax.default, (X, 2), {})[0] == "argmax"
     assert impl.supported(aten.embedding.default, (W, ids), {})[0] == "embedding"
+    F = FakeCudaTensor(torch.zeros(4, 6, 64, dtype=torch.float32))
+    assert impl.supported(aten.cumsum.default, (ids, -1), {})[0] == "cumsum"
+    assert impl.supported(aten.cumsum.default, (F, 2), {"dtype": torch.float32})[0] == "cumsum"
     # left to PyTorch
     assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.int64}) is None
     assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.float32, "device": torch.device("cpu")}) is None
@@ -151,5 +154,8 @@ def test_datamove_gates_on_metadata_only():
     assert impl.supported(aten.masked_fill.Scalar, (X, M, True), {}) is None
     assert impl.supported(aten.argmax.default, (X,), {}) is None and impl.supported(aten.argmax.default, (X, 1), {}) is None
     assert impl.supported(aten.argmax.default, (X, -1, True), {}) is None
+    assert impl.supported(aten.cumsum.default, (ids, 0), {}) is None                                  # not the last axis
+    assert impl.supported(aten.cumsum.default, (ids, -1), {"dtype": torch.float32}) is None           # converting sum
+    assert impl.supported(aten.cumsum.default, (X, -1), {}) is None                                   # 16-bit floats
     assert impl.supported(aten.embedding.default, (W, FakeCudaTensor(torch.zeros(3, dtype=torch.int32))), {}) is None
 

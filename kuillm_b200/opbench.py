@@ -317,8 +317,9 @@ def bench_decode_breakdown(T, iters):
     tok = torch.zeros(B, dtype=torch.int64, device=dev)
 
     def gemms():
-        for L in dec.layers:
-            _ffi.gemm(x, L["wqkv"], trans_b=True)
+        for li, L in enumerate(dec.layers):
+            _ffi.gemm_rope_qkv(x, L["wqkv"], hq, hk, hd, pos, cfg.rope_theta, dec.k_cache[li], dec.v_cache[li],
+                               rows_per_seq=1, out=qkv)
             _ffi.gemm(attn, L["wo"], trans_b=True)
             _ffi.gemm_swiglu(x, L["wgu"])
             _ffi.gemm(act, L["wd"], trans_b=True)
@@ -328,9 +329,8 @@ def bench_decode_breakdown(T, iters):
             _ffi.sdpa(q4, dec.k_cache[li], dec.v_cache[li], is_causal=True, need_lse=False, out=o4, kv_lens=kvlen)
 
     def small():
-        for li, L in enumerate(dec.layers):
+        for L in dec.layers:
             _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)
-            _ffi.rope_qkv(qkv, hq, hk, hd, pos, cfg.rope_theta, dec.k_cache[li], dec.v_cache[li], rows_per_seq=1)
             _ffi.rmsnorm(x, L["n2"], cfg.eps, residual=resid)
 
     def head():
@@ -347,12 +347,12 @@ def bench_decode_breakdown(T, iters):
     dec._tok_out = torch.zeros_like(tok)
     dec._pos = pos.clone()
     dec._kvlen = kvlen.clone()
-    n_layer_launch = {"gemm": 4 * cfg.n_layers, "attention": cfg.n_layers, "norm_rope": 3 * cfg.n_layers, "embed_head_argmax": 4}
+    n_layer_launch = {"gemm": 4 * cfg.n_layers, "attention": cfg.n_layers, "norm": 2 * cfg.n_layers, "embed_head_argmax": 4}
     weights = cfg.n_layers * (W * d + hq * hd * d + 2 * dec.ff * d + dec.ff * d) * 2
     kv = 2 * cfg.n_layers * B * hk * ctx * hd * 2
     head_b = cfg.vocab * d * 2
-    small_b = cfg.n_layers * (2 * 4 * B * d * 2 + 2 * B * W * 2)
-    for name, fn, nbytes in (("gemm", gemms, weights), ("attention", attention, kv), ("norm_rope", small, small_b),
+    small_b = cfg.n_layers * 2 * 4 * B * d * 2
+    for name, fn, nbytes in (("gemm", gemms, weights), ("attention", attention, kv), ("norm", small, small_b),
                              ("embed_head_argmax", head, head_b), ("whole_step", step, weights + kv + head_b)):
         if not wanted("decode_step_part", name):
             continue

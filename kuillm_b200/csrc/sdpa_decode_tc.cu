@@ -14,7 +14,6 @@
 #include "sdpa.cuh"
 #include "tc_ptx.cuh"
 #include <type_traits>
-#include <cstdlib>
 
 namespace kuiops {
 
@@ -477,8 +476,7 @@ static int decode_tc_launch(const SdpaArgs& a, void* workspace, size_t workspace
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
   const unsigned grid = unsigned(uint64_t(a.n) * a.h_kv * p.splits);
-  static const bool small_ok = [] { const char* e = getenv("KUIOPS_DECODE_SMALL"); return !(e && e[0] == '0'); }();
-  if (p.rows <= 8 && small_ok)
+  if (p.rows <= 8)
     return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 1024 + 128, st);
   return decode_tc_launch_variant<T, false>(mq, mk, mv, p, grid, D_SMEM + 128, st);
 }

@@ -3,7 +3,6 @@
 #include "common.cuh"
 #include <cooperative_groups.h>
 #include <climits>
-#include <cstdlib>
 
 namespace cg = cooperative_groups;
 namespace kuiops {
@@ -538,8 +537,6 @@ static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cu
   // cluster width: enough CTAs to give every SM two when rows are few and long
   uint32_t c = 1;
   while (c < 8 && m * c < 2 * uint64_t(kNumSMs) && n / (c * 2) >= 8192) c *= 2;
-  if (const char* e = getenv("KUIOPS_ARGMAX_CLUSTER")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) c = uint32_t(v); }
-  if (const char* e = getenv("KUIOPS_ARGMAX_THREADS")) { const int v = atoi(e); if (v >= 32 && v <= 256 && v % 32 == 0) threads = unsigned(v); }
   return launch_cluster_pdl(argmax_rows_kernel<T>, dim3(unsigned(m * c)), dim3(threads), 0, st, c, m, n,
                             static_cast<const T*>(X), out, vec_ok, c);
 }

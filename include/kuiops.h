@@ -489,6 +489,15 @@ KUIOPS_API int kuiops_argmax(int dtype, uint64_t m, uint64_t n, const void* X, i
 KUIOPS_API int kuiops_cumsum_f32(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
 KUIOPS_API int kuiops_cumsum_i64(uint32_t m, uint32_t n, const void* X, void* Y, kuiops_stream_t stream);
 
+/* Stable sort of every row of an fp32 [m, n] matrix (aten.sort over the last axis): values and
+ * the int64 permutation, ascending or descending (descending != 0).  Equal values keep their
+ * original order, -0 equals +0, NaN is the largest value.  X and values must not overlap.
+ * m * n <= 2^31; the workspace holds two (key, index) buffers.  Backlog in the reference
+ * (KERNELS.md:68-90): no counterpart. */
+KUIOPS_API size_t kuiops_sort_workspace_bytes(uint32_t m, uint32_t n);
+KUIOPS_API int kuiops_sort_f32(uint32_t m, uint32_t n, int descending, const void* X, void* values,
+                    int64_t* indices, void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

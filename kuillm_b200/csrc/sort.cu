@@ -1,0 +1,179 @@
+// Stable sort of every row of an [m, n] fp32 matrix with the permutation (aten.sort over the last
+// axis: values + int64 indices), ascending or descending; equal values keep their original order,
+// -0 equals +0, NaN is the largest value.  The reference only lists sort as backlog
+// (KERNELS.md:68-90) and has no kernel.
+//
+// One CTA per row runs a least-significant-digit radix sort on order-preserving 32-bit keys, four
+// passes of eight bits.  The four digit histograms of the row are counted once up front.  A pass
+// walks the row tile by tile; inside a tile the rank of an element among the equal digits before
+// it is found per warp with match.any plus a per-warp counter table in shared memory, the warps'
+// tables are then turned into offsets by one thread per digit, and the elements are scattered.
+// Keys and indices ping-pong between two caller-provided buffers; the first pass reads the input
+// itself and the last pass writes the results.
+#include "common.cuh"
+
+namespace kuiops {
+
+constexpr int kSortThreads = 1024;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortItems = 8;                                  // elements per thread per tile
+constexpr uint32_t kSortTile = kSortThreads * kSortItems;
+constexpr int kSortDigits = 256;
+constexpr int kSortPasses = 4;
+
+struct SortShared {
+  uint32_t hist[kSortPasses][kSortDigits];       // per pass: elements of the row with a smaller digit
+  uint32_t warp_cnt[kSortWarps][kSortDigits];    // per tile: counts, then offsets, per (warp, digit)
+  uint32_t base[kSortDigits];                    // per pass: where the next element of a digit goes
+};
+
+// Order-preserving key of a float: ascending keys are ascending values, -0 and +0 share a key and
+// every NaN takes the largest one.  Descending order sorts the complemented key, which keeps
+// equal values in their original order too.
+__device__ __forceinline__ uint32_t sort_key(float v, bool descending) {
+  uint32_t k;
+  if (v != v) {
+    k = 0xFFFFFFFFu;
+  } else {
+    const uint32_t u = __float_as_uint(v + 0.f);
+    k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  }
+  return descending ? ~k : k;
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float* __restrict__ values,
+                 int64_t* __restrict__ indices, uint32_t* key_a, uint32_t* idx_a, uint32_t* key_b, uint32_t* idx_b) {
+  __shared__ SortShared sh;
+  const uint32_t row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t off = size_t(row) * n;
+  const float* x = X + off;
+  const bool desc = descending != 0;
+  pdl_wait();
+  pdl_trigger();
+
+  // ---- the four digit histograms of the row ---------------------------------------------------
+  static_assert(kSortPasses * kSortDigits == kSortThreads, "one histogram entry per thread");
+  (&sh.hist[0][0])[tid] = 0;
+  __syncthreads();
+  for (uint32_t i = tid; i < n; i += kSortThreads) {
+    const uint32_t k = sort_key(x[i], desc);
+#pragma unroll
+    for (int p = 0; p < kSortPasses; ++p) atomicAdd(&sh.hist[p][(k >> (8 * p)) & 255u], 1u);
+  }
+  __syncthreads();
+  if (warp < kSortPasses) {
+    // exclusive prefix over the 256 digits of pass `warp`: eight digits per lane
+    uint32_t c[8], s = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { c[q] = sh.hist[warp][lane * 8 + q]; s += c[q]; }
+    uint32_t incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    uint32_t run = incl - s;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { sh.hist[warp][lane * 8 + q] = run; run += c[q]; }
+  }
+  __syncthreads();
+
+  // ---- four scatter passes ----------------------------------------------------------------------
+  for (int pass = 0; pass < kSortPasses; ++pass) {
+    const uint32_t shift = 8u * pass;
+    const uint32_t* src_key = (pass == 2 ? key_b : key_a) + off;       // pass 0 reads x instead
+    const uint32_t* src_idx = (pass == 2 ? idx_b : idx_a) + off;
+    uint32_t* dst_key = (pass == 1 ? key_b : key_a) + off;             // pass 3 writes the results instead
+    uint32_t* dst_idx = (pass == 1 ? idx_b : idx_a) + off;
+    if (tid < kSortDigits) sh.base[tid] = sh.hist[pass][tid];          // read again by the same thread only
+    for (uint32_t tile0 = 0; tile0 < n; tile0 += kSortTile) {
+#pragma unroll
+      for (int q = 0; q < kSortDigits / 32; ++q) sh.warp_cnt[warp][lane + 32 * q] = 0;
+      // element order inside the tile: warp, then j, then lane
+      uint32_t key[kSortItems], idx[kSortItems], rank[kSortItems];
+#pragma unroll
+      for (int j = 0; j < kSortItems; ++j) {
+        const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
+        key[j] = 0; idx[j] = e;
+        if (e < n) {
+          if (pass == 0) key[j] = sort_key(x[e], desc);
+          else { key[j] = src_key[e]; idx[j] = src_idx[e]; }
+        }
+      }
+      __syncwarp();                                   // the zeroed counters are visible to the warp
+#pragma unroll
+      for (int j = 0; j < kSortItems; ++j) {
+        const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
+        const bool valid = e < n;
+        const uint32_t d = valid ? ((key[j] >> shift) & 255u) : 0xFFFFFFFFu;   // lanes past the end match only each other
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        const int leader = __ffs(peers) - 1;
+        uint32_t before = 0;
+        if (lane == leader && valid) {
+          before = sh.warp_cnt[warp][d];
+          sh.warp_cnt[warp][d] = before + __popc(peers);
+        }
+        before = __shfl_sync(0xffffffffu, before, leader);
+        rank[j] = before + __popc(peers & ((1u << lane) - 1u));
+        __syncwarp();                                 // the next step reads the counter this one wrote
+      }
+      __syncthreads();                                // every warp's counts of this tile are final
+      if (tid < kSortDigits) {
+        uint32_t run = sh.base[tid];
+        for (int w = 0; w < kSortWarps; ++w) {
+          const uint32_t c = sh.warp_cnt[w][tid];
+          sh.warp_cnt[w][tid] = run;
+          run += c;
+        }
+        sh.base[tid] = run;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < kSortItems; ++j) {
+        const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
+        if (e < n) {
+          const uint32_t pos = sh.warp_cnt[warp][(key[j] >> shift) & 255u] + rank[j];
+          if (pass == kSortPasses - 1) {
+            values[off + pos] = x[idx[j]];
+            indices[off + pos] = int64_t(idx[j]);
+          } else {
+            dst_key[pos] = key[j];
+            dst_idx[pos] = idx[j];
+          }
+        }
+      }
+      __syncthreads();                                // offsets consumed before the next tile zeroes them; stores ordered for the next pass
+    }
+  }
+}
+
+}  // namespace kuiops
+
+using namespace kuiops;
+
+extern "C" {
+
+size_t kuiops_sort_workspace_bytes(uint32_t m, uint32_t n) { return size_t(m) * n * 16; }
+
+int kuiops_sort_f32(uint32_t m, uint32_t n, int descending, const void* X, void* values, int64_t* indices,
+                    void* workspace, size_t workspace_bytes, kuiops_stream_t s) {
+  if (m == 0 || n == 0 || !X || !values || !indices) return KUIOPS_EINVAL;
+  if (uint64_t(m) * n > (1ull << 31) || m > 0x7FFFFFFFu) return KUIOPS_ELIMIT;
+  if (!workspace || workspace_bytes < kuiops_sort_workspace_bytes(m, n)) return KUIOPS_EWORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 3u) return KUIOPS_EINVAL;
+  {
+    // the last pass gathers from X while it writes the values: the two must not overlap
+    const uintptr_t a = reinterpret_cast<uintptr_t>(X), b = reinterpret_cast<uintptr_t>(values);
+    const uintptr_t bytes = uintptr_t(m) * n * sizeof(float);
+    if (a < b + bytes && b < a + bytes) return KUIOPS_EINVAL;
+  }
+  const size_t cells = size_t(m) * n;
+  uint32_t* w = static_cast<uint32_t*>(workspace);
+  return launch_pdl(sort_rows_kernel, dim3(m), dim3(kSortThreads), 0, as_stream(s), n, descending,
+                    static_cast<const float*>(X), static_cast<float*>(values), indices, w, w + cells, w + 2 * cells,
+                    w + 3 * cells);
+}
+
+}  // extern "C"

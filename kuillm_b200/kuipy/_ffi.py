@@ -102,6 +102,8 @@ SIGNATURES = {
     "kuiops_embedding": (c_int, [c_u32, c_u64, c_u64, c_u64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "kuiops_cumsum_f32": (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p]),
     "kuiops_cumsum_i64": (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p]),
+    "kuiops_sort_workspace_bytes": (c_size_t, [c_u32, c_u32]),
+    "kuiops_sort_f32": (c_int, [c_u32, c_u32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
 }
 for _sfx in ("f32", "bf16", "f16"):
@@ -488,6 +490,22 @@ def argmax_lastdim(X):
     out = torch.empty(tuple(Xc.shape[:-1]), dtype=torch.int64, device=Xc.device)
     _check(lib().kuiops_argmax(dtype_code(Xc.dtype), m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "argmax")
     return out
+
+
+def sort_lastdim(X, descending=False):
+    """Stable sort of fp32 X over its last axis: (values, int64 indices)."""
+    if X.dtype != torch.float32:
+        raise KuiopsError(EUNSUPPORTED, f"sort over {X.dtype}")
+    Xc = X.contiguous()
+    n = Xc.shape[-1]
+    m = Xc.numel() // n
+    vals = torch.empty_like(Xc)
+    idx = torch.empty(Xc.shape, dtype=torch.int64, device=Xc.device)
+    nbytes = lib().kuiops_sort_workspace_bytes(m, n)
+    ws = workspace("sort", Xc.device, nbytes)
+    _check(lib().kuiops_sort_f32(m, n, 1 if descending else 0, Xc.data_ptr(), vals.data_ptr(), idx.data_ptr(),
+                                 ws.data_ptr(), nbytes, _stream()), "sort")
+    return vals, idx
 
 
 def cumsum_lastdim(X, out=None):

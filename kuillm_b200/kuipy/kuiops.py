@@ -872,8 +872,8 @@ _compile.register_binder(IsinImpl.wrapper_template, lambda ctx: (lambda E, T, in
 
 class DataMoveImpl(_Family):
     """The data-movement ops a decoder issues next to its compute on every token: dtype casts
-    (aten._to_copy between float types), aten.clone, aten.masked_fill.Scalar, aten.argmax and
-    aten.cumsum over the last axis and aten.embedding.  The reference lists them as backlog without kernels
+    (aten._to_copy between float types), aten.clone, aten.masked_fill.Scalar, aten.argmax,
+    aten.cumsum and aten.sort over the last axis and aten.embedding.  The reference lists them as backlog without kernels
     (KERNELS.md:46-48,68-90); dense, contiguous operands only, everything else falls through."""
     fst_template = "datamove/Kuiops.DataMove.Inst.fst.j2"
     wrapper_template = "datamove/wrapper_datamove.cu.j2"
@@ -881,7 +881,7 @@ class DataMoveImpl(_Family):
     tune_params = ()
     _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
     overloads = (aten._to_copy.default, aten.clone.default, aten.masked_fill.Scalar, aten.argmax.default,
-                 aten.cumsum.default, aten.embedding.default)
+                 aten.cumsum.default, aten.sort.default, aten.sort.stable, aten.embedding.default)
 
     @staticmethod
     def _dense(X):
@@ -927,6 +927,19 @@ class DataMoveImpl(_Family):
                     and _wrap_dim(dim, X.dim()) == X.dim() - 1 and dt in (None, X.dtype)):
                 return ("cumsum", None, [X])
             return None
+        if func is aten.sort.default or func is aten.sort.stable:
+            # sort.default(self, dim=-1, descending=False); sort.stable(self, *, stable, dim=-1, descending=False).
+            # The kernel is stable, which also satisfies a call that does not ask for it.
+            if func is aten.sort.default:
+                dim = kwargs.get("dim", args[1] if len(args) > 1 else -1)
+                desc = kwargs.get("descending", args[2] if len(args) > 2 else False)
+                extra = len(args) > 3
+            else:
+                dim, desc, extra = kwargs.get("dim", -1), kwargs.get("descending", False), len(args) > 1
+            if (not extra and self._dense(X) and X.dtype == torch.float32 and X.dim() >= 1 and isinstance(dim, int)
+                    and isinstance(desc, bool) and _wrap_dim(dim, X.dim()) == X.dim() - 1):
+                return ("sort", desc, [X])
+            return None
         if func is aten.embedding.default:
             if len(args) < 2:
                 return None
@@ -956,6 +969,8 @@ def _datamove_binder(ctx):
         return lambda X, _=None: _ffi.argmax_lastdim(X)
     if op == "cumsum":
         return lambda X, _=None: _ffi.cumsum_lastdim(X)
+    if op == "sort":
+        return lambda X, desc: _ffi.sort_lastdim(X, desc)
     return lambda W, ids, _=None: _ffi.embedding(W, ids)
 
 

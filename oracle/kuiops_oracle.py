@@ -196,6 +196,25 @@ def cumsum_lastdim(X: np.ndarray) -> np.ndarray:
     return np.cumsum(X, axis=-1, dtype=X.dtype)
 
 
+def sort_lastdim(X: np.ndarray, descending: bool = False):
+    """aten.sort over the last axis, stable (backlog in the reference, KERNELS.md:68-90; semantics
+    are torch.sort(stable=True)'s): NaN is the largest value, -0 equals +0, equal values keep their
+    original order.  Returns (values, int64 indices)."""
+    rows = X.reshape(-1, X.shape[-1])
+    vals = np.empty_like(rows)
+    idxs = np.empty(rows.shape, dtype=np.int64)
+    for r in range(rows.shape[0]):
+        row = rows[r]
+        nan = np.isnan(row)
+        key = np.where(nan, 0.0, row).astype(np.float64)
+        pos = np.arange(row.size)
+        # lexsort: the last key is the primary one
+        order = np.lexsort((pos, -key, ~nan)) if descending else np.lexsort((pos, key, nan))
+        idxs[r] = order
+        vals[r] = row[order]
+    return vals.reshape(X.shape), idxs.reshape(X.shape)
+
+
 def mean_lastdim(X: np.ndarray) -> np.ndarray:
     """sum_j (x[i,j] / n), keepdim: the division is part of the pre-map
     (kuiops/mean/Kuiops.Mean.fsti:25-32)."""

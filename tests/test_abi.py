@@ -127,6 +127,18 @@ def test_cumsum_contracts():
         assert f(1 << 16, (1 << 15) + 1, P, P, None) == _ffi.ELIMIT          # m * n <= 2^31
 
 
+def test_sort_contracts():
+    L = _ffi.lib()
+    assert L.kuiops_sort_workspace_bytes(64, 128256) == 64 * 128256 * 16
+    f = L.kuiops_sort_f32
+    big = 1 << 30
+    assert f(0, 8, 0, P, P + big, P, P, 1 << 20, None) == _ffi.EINVAL and f(8, 8, 0, None, P, P, P, 1 << 20, None) == _ffi.EINVAL
+    assert f(8, 8, 0, P, P + big, P, None, 0, None) == _ffi.EWORKSPACE
+    assert f(8, 8, 0, P, P + big, P, P, 8 * 8 * 16 - 1, None) == _ffi.EWORKSPACE
+    assert f(8, 8, 0, P, P + 64, P, P, 1 << 20, None) == _ffi.EINVAL           # values overlap the input
+    assert f(1 << 16, (1 << 15) + 1, 0, P, P + (1 << 40), P, P, 1 << 62, None) == _ffi.ELIMIT
+
+
 def test_gather_scatter_contracts():
     L = _ffi.lib()
     # shape_le off the gathered axis

@@ -104,7 +104,7 @@ def test_rope_prefill_sized_call_equals_row_chunks(cuda):
     assert not torch.equal(big, qkv)
 
 
-@pytest.mark.parametrize("M,hq,hk,K", [(32, 32, 8, 4096), (5, 4, 2, 1024), (128, 8, 8, 2048)])
+@pytest.mark.parametrize("M,hq,hk,K", [(32, 32, 8, 4096), (5, 4, 2, 1024), (128, 8, 8, 2048), (32, 16, 4, 4096), (32, 4, 1, 4096)])
 def test_qkv_projection_with_rope_epilogue_equals_two_kernels(cuda, M, hq, hk, K):
     """The fused projection + rotary embedding + cache append must reproduce gemm followed by
     rope_qkv bit for bit: packed rows and both caches."""

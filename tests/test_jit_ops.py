@@ -237,6 +237,36 @@ def test_cumsum_over_the_last_axis(cuda, gates, shape):
     assert torch.equal(got.cpu(), mask.cumsum(-1))
 
 
+@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (5, 4097), (300, 8193), (2, 70001), (64, 128256)])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_over_the_last_axis_is_the_stable_sort(cuda, gates, shape, descending):
+    """Radix sort of fp32 rows: many exact ties (bf16-quantised values), NaN largest, -0 == +0, infinities;
+    one tile, several tiles and ragged tails; values and permutation against the stable CPU sort."""
+    gates("wide")
+    impl = kuiops.DataMoveImpl({})
+    g = torch.Generator().manual_seed(17)
+    X = (torch.randn(*shape, generator=g) * 3).bfloat16().float()
+    n = shape[1]
+    if n >= 7:
+        X[0, 1], X[0, n - 1] = float("nan"), float("nan")
+        X[0, 2], X[0, n - 2] = float("inf"), float("-inf")
+        X[-1, :] = 0.0
+        X[-1, 3] = -0.0
+        X[-1, n // 2] = -0.0
+    if descending:
+        vals, idx = run_family(impl, aten.sort.default, (X.cuda(), -1, True))
+    else:
+        vals, idx = run_family(impl, aten.sort.stable, (X.cuda(),), {"stable": True, "dim": len(shape) - 1})
+    rv, ri = O.sort_lastdim(X.numpy(), descending)
+    assert_bit_exact(idx, ri)
+    assert np.array_equal(to_np(vals).view(np.uint32), rv.view(np.uint32))     # the very bits: signed zeros, NaNs
+    if n == 128256:                                                            # the nucleus-sampling input
+        P = torch.softmax(torch.randn(4, n, generator=g) * 3, dim=-1)
+        vals, idx = run_family(impl, aten.sort.default, (P.cuda(),))
+        tv, ti = torch.sort(P, dim=-1, stable=True)
+        assert torch.equal(idx.cpu(), ti) and torch.equal(vals.cpu(), tv)
+
+
 def test_softmax_long_rows_in_clusters(cuda):
     """64 rows of 128256 fp32: eight CTAs per row, streamed twice; and a row of -inf except one entry."""
     X = randn(64, 128256) * 3
@@ -288,6 +318,7 @@ def test_datamove_family_matches_eager(cuda, gates):
     assert impl.supported(aten.argmax.default, (X,), {}) is None                        # flattened arg-max
     assert impl.supported(aten.argmax.default, (X, 0), {}) is None
     assert impl.supported(aten.cumsum.default, (X, -1), {}) is None                     # bf16 sums stay with PyTorch
+    assert impl.supported(aten.sort.default, (X,), {}) is None                          # fp32 rows only
     gates("reference")
     from kuipy import registry
     assert aten._to_copy.default not in registry.table()

@@ -145,6 +145,9 @@ def test_datamove_gates_on_metadata_only():
     F = FakeCudaTensor(torch.zeros(4, 6, 64, dtype=torch.float32))
     assert impl.supported(aten.cumsum.default, (ids, -1), {})[0] == "cumsum"
     assert impl.supported(aten.cumsum.default, (F, 2), {"dtype": torch.float32})[0] == "cumsum"
+    assert impl.supported(aten.sort.default, (F,), {})[:2] == ("sort", False)
+    assert impl.supported(aten.sort.default, (F, -1, True), {})[:2] == ("sort", True)
+    assert impl.supported(aten.sort.stable, (F,), {"stable": True, "dim": 2, "descending": True})[:2] == ("sort", True)
     # left to PyTorch
     assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.int64}) is None
     assert impl.supported(aten._to_copy.default, (X,), {"dtype": torch.float32, "device": torch.device("cpu")}) is None
@@ -157,5 +160,7 @@ def test_datamove_gates_on_metadata_only():
     assert impl.supported(aten.cumsum.default, (ids, 0), {}) is None                                  # not the last axis
     assert impl.supported(aten.cumsum.default, (ids, -1), {"dtype": torch.float32}) is None           # converting sum
     assert impl.supported(aten.cumsum.default, (X, -1), {}) is None                                   # 16-bit floats
+    assert impl.supported(aten.sort.default, (F, 0), {}) is None and impl.supported(aten.sort.default, (X,), {}) is None
+    assert impl.supported(aten.sort.stable, (F,), {"stable": False, "dim": 1}) is None
     assert impl.supported(aten.embedding.default, (W, FakeCudaTensor(torch.zeros(3, dtype=torch.int32))), {}) is None
 

@@ -10,6 +10,8 @@
 // tables are then turned into offsets by one thread per digit, and the elements are scattered.
 // Keys and indices ping-pong between two caller-provided buffers; the first pass reads the input
 // itself and the last pass writes the results.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace kuiops {
@@ -23,8 +25,12 @@ constexpr int kSortPasses = 4;
 
 struct SortShared {
   uint32_t hist[kSortPasses][kSortDigits];       // per pass: elements of the row with a smaller digit
-  uint32_t warp_cnt[kSortWarps][kSortDigits];    // per tile: counts, then offsets, per (warp, digit)
+  uint32_t warp_cnt[kSortWarps][kSortDigits];    // per tile: counts, then offsets inside the digit, per (warp, digit)
   uint32_t base[kSortDigits];                    // per pass: where the next element of a digit goes
+  uint32_t tile_start[kSortDigits];              // per tile: first slot of a digit in the tile's sorted order
+  int32_t delta[kSortDigits];                    // per tile: global position minus slot, per digit
+  uint32_t warp_sum[kSortDigits / 32];
+  uint2 slot[kSortTile];                         // the tile in sorted order: (key, index)
 };
 
 // Order-preserving key of a float: ascending keys are ascending values, -0 and +0 share a key and
@@ -43,8 +49,9 @@ __device__ __forceinline__ uint32_t sort_key(float v, bool descending) {
 
 __global__ void __launch_bounds__(kSortThreads)
 sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float* __restrict__ values,
-                 int64_t* __restrict__ indices, uint32_t* key_a, uint32_t* idx_a, uint32_t* key_b, uint32_t* idx_b) {
-  __shared__ SortShared sh;
+                 int64_t* __restrict__ indices, uint2* buf_a, uint2* buf_b) {
+  extern __shared__ __align__(16) unsigned char sort_smem[];
+  SortShared& sh = *reinterpret_cast<SortShared*>(sort_smem);
   const uint32_t row = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const size_t off = size_t(row) * n;
@@ -83,10 +90,8 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
   // ---- four scatter passes ----------------------------------------------------------------------
   for (int pass = 0; pass < kSortPasses; ++pass) {
     const uint32_t shift = 8u * pass;
-    const uint32_t* src_key = (pass == 2 ? key_b : key_a) + off;       // pass 0 reads x instead
-    const uint32_t* src_idx = (pass == 2 ? idx_b : idx_a) + off;
-    uint32_t* dst_key = (pass == 1 ? key_b : key_a) + off;             // pass 3 writes the results instead
-    uint32_t* dst_idx = (pass == 1 ? idx_b : idx_a) + off;
+    const uint2* src = (pass == 2 ? buf_b : buf_a) + off;                // pass 0 reads x instead
+    uint2* dst = (pass == 1 ? buf_b : buf_a) + off;                      // pass 3 writes the results instead
     if (tid < kSortDigits) sh.base[tid] = sh.hist[pass][tid];          // read again by the same thread only
     for (uint32_t tile0 = 0; tile0 < n; tile0 += kSortTile) {
 #pragma unroll
@@ -99,7 +104,7 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
         key[j] = 0; idx[j] = e;
         if (e < n) {
           if (pass == 0) key[j] = sort_key(x[e], desc);
-          else { key[j] = src_key[e]; idx[j] = src_idx[e]; }
+          else { const uint2 kv = src[e]; key[j] = kv.x; idx[j] = kv.y; }
         }
       }
       __syncwarp();                                   // the zeroed counters are visible to the warp
@@ -120,31 +125,60 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
         __syncwarp();                                 // the next step reads the counter this one wrote
       }
       __syncthreads();                                // every warp's counts of this tile are final
+      // One thread per digit: the warps' counts become offsets inside the digit, the digits' totals
+      // become the tile's sorted layout (an exclusive scan over the 256 digits).
+      uint32_t total = 0, incl = 0;
       if (tid < kSortDigits) {
-        uint32_t run = sh.base[tid];
         for (int w = 0; w < kSortWarps; ++w) {
           const uint32_t c = sh.warp_cnt[w][tid];
-          sh.warp_cnt[w][tid] = run;
-          run += c;
+          sh.warp_cnt[w][tid] = total;
+          total += c;
         }
-        sh.base[tid] = run;
+        incl = total;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        if (lane == 31) sh.warp_sum[warp] = incl;
       }
       __syncthreads();
+      if (tid < kSortDigits) {
+        uint32_t start = incl - total;
+        for (int w = 0; w < warp; ++w) start += sh.warp_sum[w];
+        sh.tile_start[tid] = start;
+        const uint32_t b = sh.base[tid];
+        sh.delta[tid] = int32_t(b - start);
+        sh.base[tid] = b + total;
+      }
+      __syncthreads();
+      // into the tile's sorted order in shared memory ...
 #pragma unroll
       for (int j = 0; j < kSortItems; ++j) {
         const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
         if (e < n) {
-          const uint32_t pos = sh.warp_cnt[warp][(key[j] >> shift) & 255u] + rank[j];
+          const uint32_t d = (key[j] >> shift) & 255u;
+          sh.slot[sh.tile_start[d] + sh.warp_cnt[warp][d] + rank[j]] = make_uint2(key[j], idx[j]);
+        }
+      }
+      __syncthreads();
+      // ... and out: neighbouring threads write neighbouring positions of a digit's run
+      const uint32_t in_tile = min(kSortTile, n - tile0);
+#pragma unroll
+      for (int q = 0; q < kSortItems; ++q) {
+        const uint32_t l = uint32_t(q) * kSortThreads + tid;
+        if (l < in_tile) {
+          const uint2 kv = sh.slot[l];
+          const uint32_t pos = uint32_t(int32_t(l) + sh.delta[(kv.x >> shift) & 255u]);
           if (pass == kSortPasses - 1) {
-            values[off + pos] = x[idx[j]];
-            indices[off + pos] = int64_t(idx[j]);
+            values[off + pos] = x[kv.y];
+            indices[off + pos] = int64_t(kv.y);
           } else {
-            dst_key[pos] = key[j];
-            dst_idx[pos] = idx[j];
+            dst[pos] = kv;
           }
         }
       }
-      __syncthreads();                                // offsets consumed before the next tile zeroes them; stores ordered for the next pass
+      __syncthreads();                                // tables and slots consumed before the next tile; stores ordered for the next pass
     }
   }
 }
@@ -162,7 +196,7 @@ int kuiops_sort_f32(uint32_t m, uint32_t n, int descending, const void* X, void*
   if (m == 0 || n == 0 || !X || !values || !indices) return KUIOPS_EINVAL;
   if (uint64_t(m) * n > (1ull << 31) || m > 0x7FFFFFFFu) return KUIOPS_ELIMIT;
   if (!workspace || workspace_bytes < kuiops_sort_workspace_bytes(m, n)) return KUIOPS_EWORKSPACE;
-  if (reinterpret_cast<uintptr_t>(workspace) & 3u) return KUIOPS_EINVAL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 7u) return KUIOPS_EINVAL;
   {
     // the last pass gathers from X while it writes the values: the two must not overlap
     const uintptr_t a = reinterpret_cast<uintptr_t>(X), b = reinterpret_cast<uintptr_t>(values);
@@ -170,10 +204,18 @@ int kuiops_sort_f32(uint32_t m, uint32_t n, int descending, const void* X, void*
     if (a < b + bytes && b < a + bytes) return KUIOPS_EINVAL;
   }
   const size_t cells = size_t(m) * n;
-  uint32_t* w = static_cast<uint32_t*>(workspace);
-  return launch_pdl(sort_rows_kernel, dim3(m), dim3(kSortThreads), 0, as_stream(s), n, descending,
-                    static_cast<const float*>(X), static_cast<float*>(values), indices, w, w + cells, w + 2 * cells,
-                    w + 3 * cells);
+  uint2* w = static_cast<uint2*>(workspace);
+  static std::atomic<uint64_t> configured{0};      // the opt-in for large dynamic shared memory is per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KUIOPS_ELAUNCH;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(configured.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(sort_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(SortShared))) != cudaSuccess)
+      return KUIOPS_ELAUNCH;
+    configured.fetch_or(bit, std::memory_order_release);
+  }
+  return launch_pdl(sort_rows_kernel, dim3(m), dim3(kSortThreads), sizeof(SortShared), as_stream(s), n, descending,
+                    static_cast<const float*>(X), static_cast<float*>(values), indices, w, w + cells);
 }
 
 }  // extern "C"

@@ -10,11 +10,12 @@ same ``supported()`` gates on the nodes' fake-tensor metadata.  Two ways to use 
 * ``install_inductor_pass()`` registers ``lower_graph`` as Inductor's post-grad custom pass, so
   ``torch.compile(model)`` keeps Inductor's fusion for elementwise code and calls kuiops for
   mm / addmm / bmm / attention / softmax / topk / gather / scatter / index / isin / cat / mean /
-  all / any / max.
+  all / any / max / argmax / cumsum / sort.
 * ``backend`` is a ``torch.compile`` backend that lowers and then runs the FX graph as is (no
   Inductor code generation), which is enough to take the Python dispatch out of the loop.
 
-Elementwise maps are left to the compiler on purpose: fusing them is its job.
+Elementwise maps, casts, clones and masked fills are left to the compiler on purpose: fusing
+them is its job.
 """
 import torch
 from torch.utils._pytree import tree_map
@@ -74,6 +75,11 @@ _SCHEMAS = [
     ("all", lambda: aten.all.default, "(Tensor self) -> Tensor"),
     ("any", lambda: aten.any.default, "(Tensor self) -> Tensor"),
     ("max", lambda: aten.max.default, "(Tensor self) -> Tensor"),
+    # row-wise ops of the sampling tail that a compiler does not fuse into its neighbours
+    ("argmax", lambda: aten.argmax.default, "(Tensor self, int? dim=None, bool keepdim=False) -> Tensor"),
+    ("cumsum", lambda: aten.cumsum.default, "(Tensor self, int dim, *, ScalarType? dtype=None) -> Tensor"),
+    ("sort", lambda: aten.sort.default, "(Tensor self, int dim=-1, bool descending=False) -> (Tensor, Tensor)"),
+    ("sort_stable", lambda: aten.sort.stable, "(Tensor self, *, bool? stable, int dim=-1, bool descending=False) -> (Tensor, Tensor)"),
 ]
 _SDPA_ATEN = None
 

@@ -45,6 +45,31 @@ def test_sampling_graph_is_lowered(gates):
     assert outs[0].shape == (8, 4) and outs[1].dtype == torch.bool and outs[2].shape == (8, 1)
 
 
+def test_nucleus_sampling_tail_is_lowered(gates):
+    """sort -> softmax -> cumsum -> argmax of the top-p filter; the mask arithmetic stays with the compiler."""
+    gates("wide")
+
+    def f(logits):
+        s, i = torch.sort(logits, descending=False)
+        c = torch.softmax(s, -1).cumsum(-1)
+        keep = c > 0.1
+        return torch.argmax(torch.where(keep, s, torch.full_like(s, -1e9)), -1), i
+    gm = _trace(f, ((8, 1000), torch.float32))
+    n = inductor.lower_graph(gm.graph)
+    gm.recompile()
+    t = _targets(gm)
+    assert n == 4, t
+    for name in ("kuiops.sort", "kuiops.softmax", "kuiops.cumsum", "kuiops.argmax"):
+        assert any(name in x for x in t), (name, t)
+    assert any("aten.gt" in x for x in t) and any("aten.where" in x for x in t)
+    with FakeTensorMode():
+        tok, perm = gm(torch.empty(8, 1000, device="cuda", dtype=torch.float32))
+    assert tok.shape == (8,) and tok.dtype == torch.int64 and perm.shape == (8, 1000) and perm.dtype == torch.int64
+    # bf16 rows are not sorted by the kernels: the node stays
+    gm = _trace(lambda x: torch.sort(x)[0], ((8, 1000), torch.bfloat16))
+    assert inductor.lower_graph(gm.graph) == 0
+
+
 def test_reference_gates_leave_unsupported_nodes_alone(gates):
     gates("reference")
     gm = _trace(lambda a, b: torch.mm(a, b), ((128, 63), torch.float32), ((63, 128), torch.float32))

@@ -110,3 +110,23 @@ def test_comparator_matches_reference_verify_metric():
         rel = O.rel_frobenius(a.numpy(), b.numpy())
         assert rel == pytest.approx(r["max_rel"], rel=1e-4, abs=1e-9)
         assert (rel > rec["tol"]) == bool(r["fail"])
+
+
+def test_sort_and_cumsum_against_eager():
+    """The sampling-tail restatements against PyTorch eager on CPU (seeded): the stable sort with its
+    NaN / signed-zero / infinity rules in both directions, and the prefix sums."""
+    g = torch.Generator().manual_seed(9)
+    X = (torch.randn(6, 777, generator=g) * 3).bfloat16().float()        # quantised: many exact ties
+    X[0, 3] = X[0, 500] = float("nan")
+    X[1, :] = 0.0
+    X[1, 5] = X[1, 600] = -0.0
+    X[2, 7], X[2, 9] = float("inf"), float("-inf")
+    for desc in (False, True):
+        v, i = O.sort_lastdim(X.numpy(), desc)
+        tv, ti = torch.sort(X, dim=-1, descending=desc, stable=True)
+        assert np.array_equal(i, ti.numpy())
+        assert np.array_equal(v.view(np.uint32), tv.numpy().view(np.uint32))
+    ids = torch.randint(-9, 9, (5, 301), generator=g)
+    assert np.array_equal(O.cumsum_lastdim(ids.numpy()), ids.cumsum(-1).numpy())
+    P = torch.softmax(torch.randn(4, 5000, generator=g), -1)
+    np.testing.assert_allclose(O.cumsum_lastdim(P.numpy()), P.double().cumsum(-1).float().numpy(), rtol=1e-6, atol=1e-7)

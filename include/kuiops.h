@@ -20,6 +20,11 @@
  *   - Nothing here allocates, frees or synchronises.  Work is enqueued on
  *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
  *   - Tensors are dense row-major unless a leading dimension is given.
+ *   - Workspaces are handed over zero-filled once; a kernel that runs to completion
+ *     leaves the ticket / counter words at the head of its workspace zero for the
+ *     next call.  After any error (a negative return code, or a non-zero word from
+ *     kuiops_debug_tc_error) the caller must zero the workspace again before
+ *     reusing it: a kernel that gave up mid-way may have left counters non-zero.
  *   - `status` parameters are optional device int32 words.  A kernel that meets
  *     an out-of-range index skips that access and stores a non-zero code there.
  *   - The library is re-entrant.  The only process-wide state is the driver
@@ -65,6 +70,13 @@ KUIOPS_API const char* kuiops_strerror(int code);
  * device-side error word to *host_out (0 = no wait ever ran out; otherwise the code of the
  * wait that gave up) and optionally clears it.  Synchronises the device. */
 KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
+/* How long kuiops_rmsnorm_gather polls for a peer's arrival flag before it gives up, stores
+ * error word 30 (see kuiops_debug_tc_error), sums whatever the receive slots hold and returns.
+ * Nanoseconds; 0 restores the default of two seconds.  Returns the previous value.  A peer that
+ * died between steps therefore costs one limit per launch instead of a hang; tests use a
+ * millisecond limit with a flag nobody raises.  No counterpart in the reference (it has no
+ * multi-GPU path). */
+KUIOPS_API uint64_t kuiops_debug_set_peer_wait_ns(uint64_t ns);
 /* Programmatic dependent launch for the short kernels of a decode step (GEMM, attention,
  * RMSNorm, RoPE, SwiGLU, embedding, arg-max): when enabled (default; KUIOPS_PDL=0 in the
  * environment or a 0 here turns it off) they are launched so that their set-up overlaps the
@@ -270,10 +282,13 @@ KUIOPS_API int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_
  * the library image (each GPU that loads the library holds one copy until the
  * process exits).  Inputs and outputs are still the caller's.  Arguments and
  * results are those of kuiops_sdpa_varlen (kv_lens may be NULL).
- *   - A problem whose scratch need (kuiops_sdpa_workspace_bytes) exceeds the
- *     array is refused with KUIOPS_ELIMIT; nothing is launched.
- *   - The first call on a device looks up the array's device address; make that
- *     first call before starting any stream capture.
+ *   - A problem whose scratch need exceeds the array is refused with
+ *     KUIOPS_ELIMIT; nothing is launched.  The need is that of the kernel these
+ *     arguments select (never more than kuiops_sdpa_workspace_bytes reports).
+ *   - The array used is the copy on the GPU that holds Q, whichever device the
+ *     calling thread has current; `stream` must belong to that GPU.  The first
+ *     call for a GPU looks up the array's address there; make that first call
+ *     before starting any stream capture.
  *   - All calls share the one array and it keeps the last call's contents; the
  *     entry point clears the ticket words it relies on, on `stream`, before the
  *     kernel.  Two calls that overlap on the GPU (different streams) race on it:

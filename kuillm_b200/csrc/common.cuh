@@ -9,10 +9,34 @@
 
 namespace kuiops {
 
-constexpr int kNumSMs = 148;           // B200: 2 dies x 74 SMs
+constexpr int kDefaultSMs = 148;       // B200: 2 dies x 74 SMs; used only when no device can be queried
+
+// Number of SMs of the current device, asked once per device.  Grid sizes, split-K plans and the
+// workspace sizes derived from them all go through this, so a query and the launch that follows it
+// agree as long as the same device is current for both.
+inline int num_sms() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return kDefaultSMs;
+  }
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+    cudaGetLastError();
+    return kDefaultSMs;
+  }
+  cache[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
 constexpr int kWarp = 32;
 
 extern std::atomic<uint64_t> g_launches;
+// How long a kernel polls a flag that another GPU raises before it gives up, records error word 30
+// and carries on (nanoseconds; kuiops_debug_set_peer_wait_ns).
+constexpr uint64_t kPeerWaitDefaultNs = 2000000000ull;
+extern std::atomic<uint64_t> g_peer_wait_ns;
 
 inline int check_launch() {
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -160,9 +184,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Grid size for grid-stride streaming kernels: whole multiples of the SM count.
 inline unsigned stream_grid(uint64_t work_items, unsigned per_block, unsigned max_waves = 8) {
   uint64_t blocks = (work_items + per_block - 1) / per_block;
-  uint64_t cap = uint64_t(kNumSMs) * max_waves;
+  uint64_t cap = uint64_t(num_sms()) * max_waves;
   if (blocks >= cap) return unsigned(cap);
-  if (blocks > unsigned(kNumSMs)) blocks = ((blocks + kNumSMs - 1) / kNumSMs) * kNumSMs;
+  if (blocks > unsigned(num_sms())) blocks = ((blocks + num_sms() - 1) / num_sms()) * num_sms();
   return unsigned(blocks ? blocks : 1);
 }
 

@@ -237,7 +237,7 @@ __device__ __forceinline__ uint64_t elementwise_global_ns() {
 template <typename T, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned char* recv_base, uint64_t slot_bytes,
-                      uint64_t flags_offset, unsigned int* epoch, unsigned int* ticket, unsigned int* err,
+                      uint64_t flags_offset, unsigned int* epoch, unsigned int* ticket, unsigned int* err, uint64_t wait_ns,
                       const T* residual, const T* __restrict__ w, float eps, T* __restrict__ y, T* residual_out) {
   pdl_wait();
   pdl_trigger();
@@ -252,7 +252,7 @@ rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned c
     for (uint32_t r = 0; r < n_ranks && ok; ++r) {
       while (ld_acquire_sys(flags + r) < e + 1u) {
         if (t0 == 0) t0 = elementwise_global_ns();
-        if (elementwise_global_ns() - t0 > 2000000000ull) { ok = false; break; }
+        if (elementwise_global_ns() - t0 > wait_ns) { ok = false; break; }
       }
     }
     if (!ok) atomicExch(err, 30u);
@@ -563,7 +563,7 @@ static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const
   auto Y = static_cast<T*>(y); auto RO = static_cast<T*>(res_out);
 #define KUIOPS_RG(WPRV, RPBV) \
   return launch_pdl(rmsnorm_gather_kernel<T, WPRV>, dim3(stream_grid(m, RPBV, 16)), dim3(256), 0, st, m, n, n_ranks, B, slot_bytes, \
-                    flags_offset, epoch, ticket, err, R, W, eps, Y, RO)
+                    flags_offset, epoch, ticket, err, g_peer_wait_ns.load(std::memory_order_relaxed), R, W, eps, Y, RO)
   if (nvec <= 128) KUIOPS_RG(1, 8);
   if (nvec <= 256) KUIOPS_RG(2, 4);
   if (nvec <= 512) KUIOPS_RG(4, 2);
@@ -631,7 +631,7 @@ static int rope_launch(uint64_t rows, uint32_t hq, uint32_t hk, uint32_t d, void
     return KUIOPS_EUNSUPPORTED;
   // heads per thread: share the sines and cosines of a row over eight heads once there are rows enough to fill the machine
   const uint32_t heads = hq + 2 * hk;
-  const uint32_t hpt = rows * (heads / 8) * (d / 2 / VN) >= uint64_t(kNumSMs) * 2048 ? 8u : 1u;
+  const uint32_t hpt = rows * (heads / 8) * (d / 2 / VN) >= uint64_t(num_sms()) * 2048 ? 8u : 1u;
   const uint64_t total = rows * ((heads + hpt - 1) / hpt) * (d / 2 / VN);
   unsigned grid = stream_grid(total, 256, 16);
   return launch_pdl(rope_qkv_kernel<T>, dim3(grid), dim3(256), 0, st, rows, hq, hk, d, static_cast<T*>(qkv), row_stride,

@@ -10,6 +10,7 @@ static int pdl_default() {
   return (e && e[0] == '0') ? 0 : 1;
 }
 std::atomic<int> g_pdl_enabled{pdl_default()};
+std::atomic<uint64_t> g_peer_wait_ns{kPeerWaitDefaultNs};
 }
 using namespace kuiops;
 
@@ -19,6 +20,10 @@ int kuiops_abi_version(void) { return KUIOPS_ABI_VERSION; }
 
 int kuiops_set_pdl(int enabled) {
   return g_pdl_enabled.exchange(enabled ? 1 : 0);
+}
+
+uint64_t kuiops_debug_set_peer_wait_ns(uint64_t ns) {
+  return g_peer_wait_ns.exchange(ns ? ns : kPeerWaitDefaultNs);
 }
 
 uint64_t kuiops_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -593,7 +593,7 @@ static TcPlan make_plan(const GemmArgs& a) {
     uint32_t per_sm = (227u * 1024u) / smem_cta;
     if (per_sm > 3) per_sm = 3;
     if (per_sm < 1) per_sm = 1;
-    const uint64_t resident = uint64_t(kNumSMs) * per_sm;
+    const uint64_t resident = uint64_t(num_sms()) * per_sm;
     if (tiles < resident) {
       uint32_t want = uint32_t(resident / tiles);
       uint32_t cap = pl.kblocks / 4;               // keep at least 4 k-blocks (256 of K) per slice
@@ -719,7 +719,7 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
 #undef KUIOPS_SW
     return KUIOPS_EUNSUPPORTED;
   }
-  const unsigned grid = unsigned(units < uint64_t(kNumSMs) ? units : uint64_t(kNumSMs));
+  const unsigned grid = unsigned(units < uint64_t(num_sms()) ? units : uint64_t(num_sms()));
   if (pl.bn == 256)
     return b_mn ? launch_tc<TIN, 256, 4, 2, false, true>(mapA, mapB, p, grid, st)
                 : launch_tc<TIN, 256, 4, 2, false, false>(mapA, mapB, p, grid, st);

@@ -226,7 +226,7 @@ static RowsLaunch rows_launch(uint64_t rows, uint64_t cols_f, uint32_t word) {
   uint64_t per_sm = (220 * 1024) / (bytes + 1024);
   if (per_sm > 2048 / r.threads) per_sm = 2048 / r.threads;
   if (per_sm < 1) per_sm = 1;
-  const uint64_t cap = uint64_t(kNumSMs) * per_sm;
+  const uint64_t cap = uint64_t(num_sms()) * per_sm;
   r.grid = unsigned(rows < cap ? rows : cap);
   return r;
 }
@@ -653,8 +653,8 @@ int kuiops_isin_i64(uint64_t n, const int64_t* elements, uint64_t m, const int64
   // each block rebuilds the hash table, so give a block enough elements to amortise that
   uint64_t per_block = 4096;
   uint64_t blocks = (n + per_block - 1) / per_block;
-  if (blocks > uint64_t(kNumSMs) * 8) {
-    blocks = uint64_t(kNumSMs) * 8;
+  if (blocks > uint64_t(num_sms()) * 8) {
+    blocks = uint64_t(num_sms()) * 8;
     per_block = ((n + blocks - 1) / blocks + 7) / 8 * 8;
     blocks = (n + per_block - 1) / per_block;
   }

@@ -49,6 +49,10 @@ cumsum_rows_kernel(uint32_t m, uint32_t n, const T* __restrict__ X, T* __restric
 
   A carry = 0;
   if (cluster_ctas > 1) {
+    // A CTA's shared memory may only be touched by its cluster peers once that CTA has started: every
+    // CTA arrives here at entry and waits just before its first remote store, so the wait is covered
+    // by the streaming of phase 1.
+    cluster.barrier_arrive();
     // ---- phase 1: the sum of this part ----------------------------------------------------------
     A s = 0;
     const uint32_t nvec = vec_ok ? (hi - lo) / VEC : 0;
@@ -62,6 +66,7 @@ cumsum_rows_kernel(uint32_t m, uint32_t n, const T* __restrict__ X, T* __restric
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (lane == 0) warp_tot[0][warp] = s;
     __syncthreads();
+    cluster.barrier_wait();                // all peers are running: their shared memory exists
     if (tid == 0) {
       A t = 0;
       for (int w = 0; w < kScanThreads / 32; ++w) t += warp_tot[0][w];
@@ -132,7 +137,7 @@ static int cumsum_launch(uint32_t m, uint32_t n, const void* X, void* Y, cudaStr
   if (uint64_t(m) * n > (1ull << 31)) return KUIOPS_ELIMIT;
   // few long rows: a cluster per row, as long as the whole grid is resident (two CTAs per SM)
   uint32_t c = 1;
-  while (c < uint32_t(kScanMaxCluster) && uint64_t(m) * c * 2 <= 2ull * kNumSMs && n / (c * 2) >= kScanChunk) c *= 2;
+  while (c < uint32_t(kScanMaxCluster) && uint64_t(m) * c * 2 <= 2ull * num_sms() && n / (c * 2) >= kScanChunk) c *= 2;
   if (uint64_t(m) * c > 0x7FFFFFFFull) return KUIOPS_ELIMIT;   // one CTA per row part
   return launch_cluster_pdl(cumsum_rows_kernel<T>, dim3(m * c), dim3(kScanThreads), 0, st, c, m, n,
                             static_cast<const T*>(X), static_cast<T*>(Y), c);

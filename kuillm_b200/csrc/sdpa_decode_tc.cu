@@ -399,7 +399,7 @@ bool sdpa_decode_tc_eligible(const SdpaArgs& a) {
 
 static uint32_t decode_tc_splits(const SdpaArgs& a) {
   const uint64_t units = uint64_t(a.n) * a.h_kv;
-  const uint64_t resident = 2 * uint64_t(kNumSMs);          // two CTAs per SM
+  const uint64_t resident = 2 * uint64_t(num_sms());          // two CTAs per SM
   if (units >= resident) return 1;
   uint32_t want = uint32_t(resident / units);               // whole waves only: a partial second wave costs a full one
   uint32_t cap = a.s / (4 * DBN);                           // at least four key tiles per slice

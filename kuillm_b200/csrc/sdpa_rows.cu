@@ -336,8 +336,8 @@ SdpaRowsPlan sdpa_rows_plan(const SdpaArgs& a) {
   pl.units = uint64_t(a.n) * pl.hgroups * pl.lblocks;
   pl.e_pad = (a.e + 7) & ~7u;
   pl.splits = 1;
-  if (pl.units < 2 * uint64_t(kNumSMs)) {
-    uint32_t want = uint32_t((4 * uint64_t(kNumSMs) + pl.units - 1) / pl.units);
+  if (pl.units < 2 * uint64_t(num_sms())) {
+    uint32_t want = uint32_t((4 * uint64_t(num_sms()) + pl.units - 1) / pl.units);
     uint32_t cap = a.s / 512;
     if (cap < 1) cap = 1;
     pl.splits = want < cap ? want : cap;

@@ -204,7 +204,7 @@ static int softmax_launch(uint32_t m, uint32_t n, const void* X, void* Y, cudaSt
   const int vec_ok = aligned16(X) && aligned16(Y) && (n % VN == 0);
   // cluster width: enough CTAs to cover the SMs when rows are few and long
   uint32_t c = 1;
-  while (c < 8 && uint64_t(m) * c < 2 * kNumSMs && n / (c * 2) >= 8192) c *= 2;
+  while (c < 8 && uint64_t(m) * c < 2 * num_sms() && n / (c * 2) >= 8192) c *= 2;
   const uint32_t nv_per = ((n + VN - 1) / VN + c - 1) / c;   // vectors per CTA slice
   // A slice of up to 4 vectors per thread of a 256-thread CTA is kept in registers.  Longer slices
   // are streamed twice by 256-thread CTAs: small CTAs with few registers are all resident at once
@@ -290,7 +290,7 @@ static int mean_launch(uint64_t m, uint64_t n, const void* in, void* out, cudaSt
     mean_warp_rows_kernel<T><<<grid, 256, 0, st>>>(m, n, x, o, vec_ok);
   } else {
     unsigned threads = n >= 8192 ? 1024 : 256;
-    unsigned grid = unsigned(m < uint64_t(kNumSMs) * 8 ? m : uint64_t(kNumSMs) * 8);
+    unsigned grid = unsigned(m < uint64_t(num_sms()) * 8 ? m : uint64_t(num_sms()) * 8);
     mean_block_rows_kernel<T><<<grid, threads, 0, st>>>(m, n, x, o, vec_ok);
   }
   return check_launch();
@@ -536,7 +536,7 @@ static int argmax_launch(uint64_t m, uint64_t n, const void* X, int64_t* out, cu
   unsigned threads = n >= 2048 ? 256 : 64;
   // cluster width: enough CTAs to give every SM two when rows are few and long
   uint32_t c = 1;
-  while (c < 8 && m * c < 2 * uint64_t(kNumSMs) && n / (c * 2) >= 8192) c *= 2;
+  while (c < 8 && m * c < 2 * uint64_t(num_sms()) && n / (c * 2) >= 8192) c *= 2;
   return launch_cluster_pdl(argmax_rows_kernel<T>, dim3(unsigned(m * c)), dim3(threads), 0, st, c, m, n,
                             static_cast<const T*>(X), out, vec_ok, c);
 }

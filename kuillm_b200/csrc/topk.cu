@@ -471,7 +471,7 @@ extern "C" int kuiops_topk_f32(uint32_t m, uint32_t n, uint32_t k, const void* X
   if (k > uint32_t(kTopkMaxK)) return KUIOPS_ELIMIT;
   // a cluster per row when rows are few and long, so that every SM streams part of the input
   uint32_t c = 1;
-  while (c < 4 && uint64_t(m) * c * 2 <= uint64_t(kNumSMs) && n / (c * 2) >= 16384) c *= 2;
+  while (c < 4 && uint64_t(m) * c * 2 <= uint64_t(num_sms()) && n / (c * 2) >= 16384) c *= 2;
   const size_t smem = sizeof(TopkShared);   // ~41 KB, below the 48 KB that needs no opt-in
   // few results per row: the thread-maxima bound is tight (the row has 1024 c thread maxima)
   if (k * 8 <= 1024 * c)

@@ -49,6 +49,7 @@ SIGNATURES = {
     "kuiops_abi_version": (c_int, []),
     "kuiops_strerror": (ctypes.c_char_p, [c_int]),
     "kuiops_debug_tc_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
+    "kuiops_debug_set_peer_wait_ns": (c_u64, [c_u64]),
     "kuiops_launch_count": (c_u64, []),
     "kuiops_set_pdl": (c_int, [c_int]),
     "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),
@@ -161,6 +162,11 @@ def set_pdl(enabled: bool) -> bool:
     return bool(lib().kuiops_set_pdl(1 if enabled else 0))
 
 
+def set_peer_wait_ns(ns: int) -> int:
+    """Limit of the cross-GPU flag wait of rmsnorm_gather (0 = the default two seconds); returns the old limit."""
+    return int(lib().kuiops_debug_set_peer_wait_ns(int(ns)))
+
+
 def launch_count() -> int:
     return int(lib().kuiops_launch_count())
 
@@ -168,11 +174,15 @@ def launch_count() -> int:
 def tc_error(reset=True) -> int:
     v = ctypes.c_uint(0)
     _check(lib().kuiops_debug_tc_error(ctypes.byref(v), 1 if reset else 0), "debug_tc_error")
+    if v.value:
+        drop_workspaces()      # a kernel gave up mid-way: its ticket words may be non-zero
     return int(v.value)
 
 
 def _check(rc, what):
     if rc != OK:
+        if rc in (ELAUNCH, EDRIVER):
+            drop_workspaces()
         raise KuiopsError(rc, what)
 
 
@@ -204,6 +214,13 @@ def _u64arr(vals):
 # keep the leading counter words zero between calls
 # --------------------------------------------------------------------------------------------
 _scratch = {}
+
+
+def drop_workspaces():
+    """Forget every cached scratch buffer.  The kernels only restore "ticket words are zero" when
+    they run to completion; after a timed-out wait or a failed launch the next call gets a fresh,
+    zero-initialised buffer instead of one whose counters may be half-way."""
+    _scratch.clear()
 
 
 def workspace(kind, device, nbytes):

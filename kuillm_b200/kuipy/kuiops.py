@@ -615,6 +615,11 @@ class SdpaImpl(_Family):
         N3, Hv, S2, Ev = _ints(V.shape)
         if (N, E) != (N2, E2) or (N, Hk, S) != (N3, Hv, S2) or min(N, H, L, S, E, Ev) < 1:
             return None
+        if is_causal and not flash and L != S:
+            # the kernels align the causal mask bottom-right (query i sees keys <= i + S - L), which is
+            # the flash overload's rule; ATen's efficient overload aligns it top-left, and the two
+            # differ whenever the query and key counts do
+            return None
         if C.reference_gates():
             if H != Hk or tuple(_ints(bias.shape)) != (N, H, L, S):
                 return None

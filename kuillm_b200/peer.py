@@ -19,7 +19,8 @@ import torch
 class PeerExchange:
     def __init__(self, group, device, max_rows, width, dtype):
         import torch.distributed as dist
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # assigned, not defaulted: an inherited "0" would let the rendezvous bind an NVLink multicast object
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
         import torch.distributed._symmetric_memory as symm
         if group is None:
             group = dist.group.WORLD
@@ -33,6 +34,9 @@ class PeerExchange:
         self.buffer.zero_()
         torch.cuda.synchronize(device)
         self.handle = symm.rendezvous(self.buffer, group)
+        if int(getattr(self.handle, "multicast_ptr", 0) or 0) != 0:
+            raise RuntimeError("kuiops: the symmetric-memory rendezvous bound a multicast object; the fused "
+                               "all-reduce only runs on plain peer mappings")
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(ptrs) != self.n_ranks or ptrs[self.rank] != self.buffer.data_ptr():
             raise RuntimeError("kuiops: symmetric memory rendezvous returned unexpected addresses")

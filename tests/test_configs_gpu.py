@@ -105,20 +105,30 @@ def test_gemm_decode_shapes(cuda, M, N, K):
     assert _ffi.tc_error() == 0
 
 
-@pytest.mark.parametrize("N,K", GEMM_NK[:3])
+@pytest.mark.parametrize("N,K", GEMM_NK)
 def test_gemm_prefill_shape_m4096(cuda, N, K):
     A, W, bias = _gemm_inputs(4096, N, K)
-    rows = torch.randint(0, 4096, (64,), device="cuda", generator=gen(2))
-    cols = torch.randint(0, N, (256,), device="cuda", generator=gen(3))
+    # rows on both sides of every 128-row tile edge region plus random ones; columns likewise
+    rows = torch.cat([torch.tensor([0, 127, 128, 4095], device="cuda"),
+                      torch.randint(0, 4096, (60,), device="cuda", generator=gen(2))])
+    cols = torch.cat([torch.tensor([0, 255, 256, N - 1], device="cuda"),
+                      torch.randint(0, N, (252,), device="cuda", generator=gen(3))])
     C = _ffi.gemm(A, W, trans_b=True)
     _check_sampled(C, A, W, None, rows, cols)
-    # whole-output property: C x 1 == A (W^T x 1) within bf16 rounding of C
-    colsum = f64(A) @ f64(W).sum(0)
-    got = f64(C).sum(1)
-    assert np.abs(got - colsum).max() <= 2e-2 * np.abs(f64(C)).sum(1).max()
-    # row-major [K, N] operand (MN-major tiles) gives the same product
-    C2 = _ffi.gemm(A, W.t().contiguous())
-    assert torch.equal(C, C2)
+    # whole-output property: C x 1 == A (W^T x 1) within bf16 rounding of C (sums taken in fp64 on the device)
+    colsum = (A.double() @ W.double().sum(0)).cpu().numpy()
+    got = C.double().sum(1).cpu().numpy()
+    assert np.abs(got - colsum).max() <= 2e-2 * float(C.double().abs().sum(1).max())
+    # fused bias epilogue at the prefill size (addmm with a length-N bias)
+    Cb = _ffi.gemm(A, W, trans_b=True, Cin=bias)
+    _check_sampled(Cb, A, W, bias, rows, cols)
+    delta = (Cb.double() - C.double()).mean(0).cpu().numpy()              # the bias, up to rounding of both outputs
+    assert np.abs(delta - f64(bias)).max() <= 2e-2 * float(C.double().abs().max())
+    del Cb
+    if N <= 14336:
+        # row-major [K, N] operand (MN-major tiles) gives the same product
+        C2 = _ffi.gemm(A, W.t().contiguous())
+        assert torch.equal(C, C2)
     assert _ffi.tc_error() == 0
 
 
@@ -157,16 +167,26 @@ def _attn_check(Q, K, V, out, pairs, rows):
 
 
 @pytest.mark.parametrize("hkv", [32, 8])
-@pytest.mark.parametrize("S", [1024, 4096])
+@pytest.mark.parametrize("S", [1024, 4096, 16384])
 def test_sdpa_prefill(cuda, S, hkv):
     g = gen(5)
     Q = torch.randn(8, 32, S, 128, device="cuda", generator=g).bfloat16()
     K = torch.randn(8, hkv, S, 128, device="cuda", generator=g).bfloat16()
     V = torch.randn(8, hkv, S, 128, device="cuda", generator=g).bfloat16()
     out, lse = _ffi.sdpa(Q, K, V, is_causal=True)
-    rows = torch.tensor([0, 1, 127, 128, S // 2 + 3, S - 1])
-    _attn_check(Q, K, V, out, [(0, 0), (3, 17), (7, 31)], rows)
+    # first / last rows of query tiles, the middle, and the very last row (the longest key walk and, at
+    # S = 16384, the largest 64-bit offsets)
+    rows = torch.tensor(sorted({0, 1, 127, 128, 255, 256, S // 2 - 1, S // 2 + 3, S - 129, S - 1}))
+    _attn_check(Q, K, V, out, [(0, 0), (3, 17), (5, 8), (7, 31)], rows)
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    # log-sum-exp of sampled rows against the oracle (natural log of the scaled scores)
+    for (b, hh) in ((0, 0), (7, 31)):
+        kv = hh // (32 // hkv)
+        for r in (0, 128, S - 1):
+            s_row = (f64(Q[b, hh, r]) @ f64(K[b, kv, :r + 1]).T) / 128 ** 0.5
+            want = np.log(np.exp(s_row - s_row.max()).sum()) + s_row.max()
+            assert abs(float(lse[b, hh, r]) - want) <= 2e-2 * max(abs(want), 1.0)
+    assert _ffi.tc_error() == 0
 
 
 @pytest.mark.parametrize("hkv", [32, 8])

@@ -55,6 +55,14 @@ def test_decoder_matches_hf_llama(cuda):
         ref2 = twin(nxt[:, None], past_key_values=ref.past_key_values, use_cache=True)
     rel2 = O.rel_frobenius(to_np(step), to_np(ref2.logits[:, -1]))
     assert rel2 < 3e-2, rel2
+    # the element-wise bar, against the same weights evaluated in fp32 by PyTorch eager
+    twin32 = twin.float()
+    with torch.no_grad():
+        r32 = twin32(ids, use_cache=True)
+        r32b = twin32(nxt[:, None], past_key_values=r32.past_key_values, use_cache=True)
+    for got, want in ((logits, r32.logits[:, -1]), (step, r32b.logits[:, -1])):
+        err = O.max_rel_err(to_np(got), to_np(want))
+        assert err <= 2e-2, f"max relative error {err:.3e} against the fp32 model"
 
 
 def test_generate_is_deterministic_and_cache_consistent(cuda):

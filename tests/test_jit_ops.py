@@ -355,6 +355,28 @@ def test_sdpa_causal_grouped_query(cuda, gates, dtype, shape):
         assert_max_rel(res[0], ro, 2e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sdpa_efficient_overload_causal_matches_eager_under_dispatch(cuda, gates, dtype):
+    """The efficient-attention overload with a causal flag, dispatched under the mode, against
+    PyTorch eager: equal counts are offloaded and agree; unequal counts (ATen masks top-left there,
+    the kernels bottom-right) must fall through, so the result is eager's own."""
+    import kuipy
+    gates("wide")
+    func = aten._scaled_dot_product_efficient_attention.default
+    for (L, S) in ((33, 33), (5, 33), (1, 40)):
+        Q, K, V = randn(2, 4, L, 64, dtype=dtype), randn(2, 4, S, 64, dtype=dtype, seed=1), randn(2, 4, S, 64, dtype=dtype, seed=2)
+        ref = func(Q, K, V, None, True, 0.0, True)
+        kuipy.reset_verify()
+        with kuipy.KuiperMode(verify=True):
+            got = func(Q, K, V, None, True, 0.0, True)
+        offloaded = str(func) in kuipy.verify_stats
+        assert offloaded == (L == S)
+        if offloaded:
+            assert_close_ref_bar(got[0], to_np(ref[0]).astype(np.float64), dtype)
+        else:
+            assert torch.equal(got[0], ref[0])
+
+
 def test_sdpa_reference_gates_reject_causal_dropout_and_missing_bias(cuda, gates):
     gates("reference")
     impl = kuiops.SdpaImpl({})

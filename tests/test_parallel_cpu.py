@@ -83,6 +83,30 @@ def test_tensor_parallel_layer_matches_unsplit_layer_world2():
     assert q.get(timeout=10) == 1
 
 
+def _lonely_worker(port, out):
+    """Rank 0 of a group of two whose other rank never starts: the rendezvous must end with an error
+    after its (short) timeout, on the host, and the process must stay in control."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        t = torch.ones(1)
+        dist.all_reduce(t)                  # not reached with a store-based rendezvous; errors out otherwise
+        out.put("joined")
+    except Exception as e:                  # noqa: BLE001 - any rendezvous / collective error is the expected outcome
+        out.put(f"error: {type(e).__name__}")
+
+
+def test_rank_that_never_starts_is_reported_on_the_host():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(_free_port(), q))
+    p.start()
+    p.join(60)
+    assert p.exitcode == 0, "the surviving rank must come back from the failed rendezvous by itself"
+    assert q.get(timeout=10).startswith("error")
+
+
 def test_shards_partition_the_weights():
     w = torch.arange(8 * 6.0).view(8, 6)
     parts = [shard_out_features(w, 4, 2, r, 2) for r in range(2)]          # 4 heads of 2 rows, 2 ranks

@@ -90,7 +90,7 @@ def _tp_worker(rank, size, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("size", [2, 4])
+@pytest.mark.parametrize("size", [2, 4, 8])
 def test_tp_and_dp_match_single_gpu(size):
     if not torch.cuda.is_available() or torch.cuda.device_count() < size:
         pytest.skip(f"needs {size} GPUs")

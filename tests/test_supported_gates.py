@@ -89,7 +89,8 @@ def test_wide_gates_take_the_decode_shapes(gates):
     q, k, v = f((2, 8, 1, 128)), f((2, 2, 77, 128)), f((2, 2, 77, 128))
     sd = kuiops.SdpaImpl({})
     assert sd.supported(aten._scaled_dot_product_flash_attention.default, (q, k, v, 0.0, True), {}) is not None
-    assert sd.supported(aten._scaled_dot_product_efficient_attention.default, (q, k, v, None, True, 0.0, True), {}) is not None
+    # a decode step reaches the efficient overload without a causal flag (one query row sees every key)
+    assert sd.supported(aten._scaled_dot_product_efficient_attention.default, (q, k, v, None, True, 0.0, False), {}) is not None
     assert sd.supported(aten._scaled_dot_product_flash_attention.default, (q, k, v, 0.1, True), {}) is None
 
 
@@ -164,3 +165,19 @@ def test_datamove_gates_on_metadata_only():
     assert impl.supported(aten.sort.stable, (F,), {"stable": False, "dim": 1}) is None
     assert impl.supported(aten.embedding.default, (W, FakeCudaTensor(torch.zeros(3, dtype=torch.int32))), {}) is None
 
+
+
+def test_efficient_attention_causal_needs_square_scores(gates):
+    """ATen masks the efficient overload top-left, the kernels mask bottom-right: with a causal
+    flag the two only agree for equal query and key counts, so other shapes must fall through.
+    The flash overload is bottom-right in ATen too and is taken either way."""
+    gates("wide")
+    aten = torch.ops.aten
+    impl = kuiops.SdpaImpl({})
+    q = lambda l: FakeCudaTensor(torch.zeros((2, 4, l, 64), dtype=torch.bfloat16))
+    eff, fl = aten._scaled_dot_product_efficient_attention.default, aten._scaled_dot_product_flash_attention.default
+    assert impl.supported(eff, (q(8), q(8), q(8), None, True, 0.0, True), {}) is not None
+    assert impl.supported(eff, (q(5), q(8), q(8), None, True, 0.0, True), {}) is None
+    assert impl.supported(eff, (q(1), q(8), q(8), None, True, 0.0, True), {}) is None
+    assert impl.supported(eff, (q(5), q(8), q(8), None, True, 0.0, False), {}) is not None
+    assert impl.supported(fl, (q(5), q(8), q(8), 0.0, True), {}) is not None

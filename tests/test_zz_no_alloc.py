@@ -56,6 +56,53 @@ def test_noalloc_matches_the_caller_scratch_entry_point_twice(cuda):
         assert _max_rel(out, ref_out) <= 2e-2
 
 
+def test_noalloc_alternating_kernels_share_the_array(cuda):
+    """The two split-KV kernels lay out different ticket blocks at the head of the one array: an
+    fp32 call (SIMT rows kernel) and a bf16 call (tensor-core decode kernel) follow each other in
+    both orders, each finding the other's records, and each must agree with ``kuiops_sdpa``."""
+    def case(dtype, seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        mk = lambda *shape: torch.randn(*shape, device="cuda", generator=g).to(dtype)
+        return mk(1, 8, 1, 128), mk(1, 2, 6000, 128), mk(1, 2, 6000, 128)
+    order = [(torch.bfloat16, 0), (torch.float32, 1), (torch.bfloat16, 2), (torch.float32, 3), (torch.float32, 4), (torch.bfloat16, 5)]
+    for dtype, seed in order:
+        Q, K, V = case(dtype, seed)
+        code = _ffi.dtype_code(dtype)
+        assert _ffi.lib().kuiops_sdpa_workspace_bytes(code, 1, 8, 2, 1, 6000, 128, 128) > 0, "must be a split-KV case"
+        ref_out, ref_lse = _ffi.sdpa(Q, K, V, is_causal=True)
+        out, lse = _call_noalloc(Q, K, V, True)
+        torch.cuda.synchronize()
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        assert _max_rel(out, ref_out) <= tol and _max_rel(lse, ref_lse) <= tol, (dtype, seed)
+
+
+def test_noalloc_uses_the_array_of_the_gpu_that_holds_the_inputs(cuda):
+    """With two GPUs visible: inputs on GPU 1 while GPU 0 is the calling thread's current device,
+    after GPU 0 has already been used.  The entry point has to pick GPU 1's copy of the array."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    g = torch.Generator().manual_seed(9)
+    Q, K, V = (torch.randn(s, generator=g).bfloat16() for s in ((2, 32, 1, 128), (2, 8, 8192, 128), (2, 8, 8192, 128)))
+    outs = []
+    for dev in (0, 1):
+        q, k, v = Q.to(f"cuda:{dev}"), K.to(f"cuda:{dev}"), V.to(f"cuda:{dev}")
+        with torch.cuda.device(dev):
+            ref, _ = _ffi.sdpa(q, k, v, is_causal=True)
+        torch.cuda.set_device(0)                        # current device stays GPU 0 for the call itself
+        out = torch.empty_like(ref)
+        rc = _ffi.lib().kuiops_sdpa_noalloc(
+            _ffi.BF16, 2, 32, 8, 1, 8192, 128, 128,
+            q.data_ptr(), q.stride(0), q.stride(1), q.stride(2), k.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
+            v.data_ptr(), v.stride(0), v.stride(1), v.stride(2), None, 1.0 / 128 ** 0.5, 1,
+            out.data_ptr(), out.stride(0), out.stride(1), out.stride(2), None, None,
+            torch.cuda.current_stream(dev).cuda_stream)
+        assert rc == _ffi.OK, _ffi.strerror(rc)
+        torch.cuda.synchronize(dev)
+        assert _max_rel(out, ref) <= 2e-2
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_noalloc_refuses_problems_beyond_its_fixed_scratch(cuda):
     # 295 kv heads x 16 query heads each: the split-KV records need more than the built-in array
     n, hkv, g, s = 1, 295, 16, 4096

@@ -27,18 +27,23 @@ _LIB = None
 _OPS = {}       # aten overload -> kuiops custom op (OpOverload)
 
 
-def _unsupported(name):
-    return RuntimeError(f"kuiops::{name}: the call is not supported by the kernels (gate changed after lowering?)")
+# custom op name -> [calls served by a kuiops kernel, calls handed back to stock PyTorch]
+call_stats = {}
 
 
 def _define_same_schema(lib, name, aten_op, schema):
-    """A custom op with the aten op's own signature: CUDA runs the kuiops kernel, fake runs aten."""
+    """A custom op with the aten op's own signature: CUDA runs the kuiops kernel, fake runs aten.
+    A graph compiled with symbolic sizes is lowered on the sizes seen at compile time; a later call
+    whose actual sizes the gates refuse falls through to the aten op, as the dispatch mode does."""
     lib.define(f"{name}{schema}")
+    stats = call_stats.setdefault(name, [0, 0])
 
     def impl(*args, **kwargs):
         out = registry.try_dispatch(aten_op, args, kwargs)
         if out is None:
-            raise _unsupported(name)
+            stats[1] += 1
+            return aten_op(*args, **kwargs)
+        stats[0] += 1
         return out
     lib.impl(name, impl, "CUDA")
     torch.library.register_fake(f"kuiops::{name}")(lambda *a, **k: aten_op(*a, **k))
@@ -48,8 +53,11 @@ def _define_same_schema(lib, name, aten_op, schema):
 def _define_sdpa(lib):
     lib.define("sdpa(Tensor q, Tensor k, Tensor v, Tensor? bias, float scale, bool causal) -> (Tensor, Tensor)")
 
+    stats = call_stats.setdefault("sdpa", [0, 0])
+
     def impl(q, k, v, bias, scale, causal):
         from . import _ffi
+        stats[0] += 1
         return _ffi.sdpa(q, k, v, bias=bias, scale=scale, is_causal=causal, need_lse=True)
     lib.impl("sdpa", impl, "CUDA")
 
@@ -94,29 +102,62 @@ def register_ops():
         op = get()
         _OPS[op] = _define_same_schema(_LIB, name, op, schema)
     _OPS["sdpa"] = _define_sdpa(_LIB)
-    _SDPA_ATEN = (aten._scaled_dot_product_flash_attention.default, aten._scaled_dot_product_efficient_attention.default)
+    _SDPA_ATEN = (aten._scaled_dot_product_flash_attention.default, aten._scaled_dot_product_efficient_attention.default,
+                  aten._scaled_dot_product_cudnn_attention.default)
     return _OPS
 
 
+_hint_mode = None
+
+
+def _concrete(t):
+    """A fake tensor whose sizes are symbolic -> a fake CUDA tensor with the sizes and strides seen at
+    compile time (the hints), so that the gates can be asked without adding guards to the graph.
+    Returns None when a size has no hint (data-dependent shapes are left to the compiler)."""
+    global _hint_mode
+    if not isinstance(t, torch.Tensor):
+        return t
+    if not any(isinstance(v, torch.SymInt) for v in tuple(t.shape) + tuple(t.stride())):
+        return t
+    from torch.fx.experimental.symbolic_shapes import has_hint, size_hint
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    dims = []
+    for v in tuple(t.shape) + tuple(t.stride()):
+        if isinstance(v, torch.SymInt):
+            if not has_hint(v):
+                return None
+            v = size_hint(v)
+        dims.append(int(v))
+    if _hint_mode is None:
+        _hint_mode = FakeTensorMode()
+    with _hint_mode:
+        return torch.empty_strided(dims[:t.dim()], dims[t.dim():], dtype=t.dtype, device=t.device)
+
+
 def _fake(x):
-    return x.meta.get("val") if isinstance(x, torch.fx.Node) else x
+    return _concrete(x.meta.get("val")) if isinstance(x, torch.fx.Node) else x
 
 
 def _lower_sdpa(graph, node, fam):
     """aten flash / efficient attention node -> kuiops::sdpa; only outputs 0 and 1 may be used."""
     fargs = tree_map(_fake, node.args)
     fkw = tree_map(_fake, dict(node.kwargs))
+    if any(_fake(a) is None for a in node.args[:3]):
+        return False
     spec = fam.supported(node.target, fargs, fkw)
     if spec is None:
         return False
     import operator
+    _, scale, causal, overload, _, _ = spec
+    # outputs a consumer may use: the attention output, and the log-sum-exp where its shape is (N, H, L)
+    # (the cuDNN overload's is (N, H, L, 1))
+    usable = (0,) if overload == "cudnn" else (0, 1)
     for user in node.users:
-        if not (user.op == "call_function" and user.target is operator.getitem and user.args[1] in (0, 1)):
+        if not (user.op == "call_function" and user.target is operator.getitem and user.args[1] in usable):
             if len(user.users):
                 return False
-    _, scale, causal, overload, _, _ = spec
     q, k, v = node.args[0], node.args[1], node.args[2]
-    bias = node.args[3] if overload == "efficient" else None
+    bias = node.args[3] if overload in ("efficient", "cudnn") else None
     with graph.inserting_before(node):
         new = graph.call_function(_OPS["sdpa"], (q, k, v, bias, float(scale), bool(causal)))
     new.meta["val"] = (node.meta["val"][0], node.meta["val"][1]) if "val" in node.meta else None

@@ -576,17 +576,23 @@ _compile.register_binder(TopkImpl.wrapper_template, lambda ctx: (lambda X, k: _f
 class SdpaImpl(_Family):
     """Attention.  "reference" gates: the efficient-attention overload with an explicit additive
     bias, no causal flag, no dropout, equal head counts (kuiops.py:627-660 there, where the family
-    is written but not connected).  "wide" gates add the flash-attention overload, causal masking,
-    a missing bias and grouped-query heads."""
+    is written but not connected).  "wide" gates add the flash-attention and cuDNN-attention
+    overloads, causal masking, a missing bias and grouped-query heads."""
     fst_template = "sdpa/Kuiops.Sdpa.Inst.fst.j2"
     wrapper_template = "sdpa/wrapper_sdpa.cu.j2"
     tune_key = "SDPA"
     tune_params = ()
     overloads = (aten._scaled_dot_product_efficient_attention.default,
-                 aten._scaled_dot_product_flash_attention.default)
+                 aten._scaled_dot_product_flash_attention.default,
+                 aten._scaled_dot_product_cudnn_attention.default)
 
     def supported(self, func, args, kwargs):
         flash = func is aten._scaled_dot_product_flash_attention.default
+        # the cuDNN overload (what ATen picks for bf16 / f16 on this GPU generation) takes the efficient
+        # overload's arguments and returns the flash overload's nine values
+        cudnn = func is aten._scaled_dot_product_cudnn_attention.default
+        if cudnn and C.reference_gates():
+            return None
         if flash:
             if C.reference_gates() or len(args) < 3:
                 return None
@@ -639,8 +645,8 @@ class SdpaImpl(_Family):
         scale = kwargs.get("scale")
         if scale is None:
             scale = 1.0 / math.sqrt(E)
-        return (Q.dtype, float(scale), bool(is_causal), "flash" if flash else "efficient", bool(compute_lse),
-                [Q, K, V, bias])
+        return (Q.dtype, float(scale), bool(is_causal), "flash" if flash else ("cudnn" if cudnn else "efficient"),
+                bool(compute_lse), [Q, K, V, bias])
 
     def run(self, spec, args, kwargs):
         dt, scale, causal, overload, compute_lse, call = spec
@@ -653,6 +659,8 @@ class SdpaImpl(_Family):
             return (out, lse, zero, zero)
         L, S = int(Q.shape[2]), int(K.shape[2])
         # (output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, philox_seed, philox_offset, debug_attn_mask)
+        if overload == "cudnn":
+            return (out, lse.unsqueeze(-1), None, None, L, S, zero, zero, None)     # its log-sum-exp is (N, H, L, 1)
         empty = torch.empty(0, dtype=dt, device=Q.device)
         return (out, lse, None, None, L, S, zero, zero, empty)
 

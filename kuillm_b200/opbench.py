@@ -86,9 +86,9 @@ def variants_for(bytes_per_input):
 
 
 class Table:
-    def __init__(self, out):
+    def __init__(self, out, quiet=False):
         self.hbm, self.tf, self.kind = peaks()
-        self.rows, self.out = [], out
+        self.rows, self.out, self.quiet = [], out, quiet
 
     def add(self, op, shape, us, bytes_=None, flops=None, bound="hbm", note=""):
         if callable(us):
@@ -108,7 +108,8 @@ class Table:
         if note:
             row["note"] = note
         self.rows.append(row)
-        print(json.dumps(row), flush=True)
+        if not self.quiet:
+            print(json.dumps(row), flush=True)
         if self.out:
             with open(self.out, "a") as f:
                 f.write(json.dumps(row) + "\n")
@@ -207,7 +208,7 @@ def bench_gemm(T, iters):
         Ws = [(torch.randn(N, K, device=dev) / K ** 0.5).bfloat16() for _ in range(min(nv, 6 if N > 100000 else nv))]
         bias = torch.zeros(N, device=dev, dtype=torch.bfloat16)
         for M in (1, 8, 16, 32, 128, 4096):
-            if M == 4096 and N > 100000:
+            if not wanted("gemm_bf16_tn", f"M{M} N{N} K{K}") and not wanted("addmm_bias_bf16_tn", f"M{M} N{N} K{K}"):
                 continue
             A = torch.randn(M, K, device=dev).bfloat16()
             C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
@@ -362,6 +363,44 @@ def bench_decode_breakdown(T, iters):
         us = time_us(lambda i: fn(), 1, min(max(2, iters // 4), 16))
         launches = n_layer_launch.get(name, sum(n_layer_launch.values()) + 2)
         T.add("decode_step_part", name, us, bytes_=nbytes, bound="hbm", note=f"{launches} launches per call")
+
+
+def baseline_sweep(iters=10):
+    """The operator sweeps the benchmark configuration names, as rows (no printing): attention
+    prefill (batch 8, 32 query heads, 32 or 8 KV heads, S = 1024 / 4096 / 16384) and decode (batch 64,
+    caches of 4096 and 32768), the GEMM sweep M in {1, 8, 16, 128, 4096} x four (N, K) plus the batched
+    product, and the sampling row ops on the 64 x 128256 logits.  Used by bench.py so that the
+    per-operator fractions of peak are measured in the same run as the end-to-end number."""
+    global MATCH
+    T = Table("", quiet=True)
+    saved = MATCH
+    try:
+        MATCH = "64x128256"
+        bench_stream(T, iters)
+        torch.cuda.empty_cache()
+        MATCH = ""
+        bench_sdpa(T, iters)
+        torch.cuda.empty_cache()
+        for (N, K) in ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)):
+            for M in (1, 8, 16, 128, 4096):
+                MATCH = f"gemm_bf16_tn M{M} N{N} K{K}"
+                bench_gemm(T, iters)
+            torch.cuda.empty_cache()
+        MATCH = "addmm_bias_bf16_tn"
+        bench_gemm(T, iters)
+        MATCH = "bmm_bf16"
+        bench_gemm(T, iters)
+    finally:
+        MATCH = saved
+        torch.cuda.empty_cache()
+    keep = ("op", "shape", "us", "bound", "frac", "frac_nominal")
+    seen, rows = set(), []
+    for r in T.rows:
+        key = (r["op"], r["shape"])
+        if key not in seen and r["op"] not in ("mm_bf16_nn", "mm_f32_simt"):
+            seen.add(key)
+            rows.append({k: r[k] for k in keep})
+    return rows, T.kind
 
 
 def main():

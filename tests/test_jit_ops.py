@@ -377,6 +377,27 @@ def test_sdpa_efficient_overload_causal_matches_eager_under_dispatch(cuda, gates
             assert torch.equal(got[0], ref[0])
 
 
+def test_functional_sdpa_is_offloaded_whichever_backend_aten_picks(cuda, gates):
+    """``F.scaled_dot_product_attention`` on bf16 reaches the dispatcher as the flash, the efficient or
+    (on this GPU generation) the cuDNN overload; whichever it is, the call must be served by the
+    kernels and agree with eager, for a causal prefill block and for a one-token decode step."""
+    import kuipy
+    import torch.nn.functional as F
+    gates("wide")
+    for (L, S, causal) in ((192, 192, True), (1, 300, False)):
+        Q, K, V = randn(2, 8, L, 128, dtype=torch.bfloat16), randn(2, 2, S, 128, dtype=torch.bfloat16, seed=1), randn(2, 2, S, 128, dtype=torch.bfloat16, seed=2)
+        ref = F.scaled_dot_product_attention(Q, K, V, is_causal=causal, enable_gqa=True)
+        kuipy.reset_verify()
+        with kuipy.KuiperMode(verify=True):
+            got = F.scaled_dot_product_attention(Q, K, V, is_causal=causal, enable_gqa=True)
+        served = [k for k in kuipy.verify_stats if "scaled_dot_product" in k]
+        assert served, f"attention was not offloaded: {list(kuipy.verify_stats)}"
+        assert sum(e["fail"] for e in kuipy.verify_stats.values()) == 0
+        ro, _ = O.sdpa(to_np(Q), to_np(K), to_np(V), is_causal=causal)
+        assert_max_rel(got, ro, 2e-2)
+        assert got.shape == ref.shape
+
+
 def test_sdpa_reference_gates_reject_causal_dropout_and_missing_bias(cuda, gates):
     gates("reference")
     impl = kuiops.SdpaImpl({})

@@ -110,6 +110,22 @@ KUIOPS_API uint64_t    kuiops_launch_count(void);
  * and wrapper_bmm.cu.j2:16-20. */
 #define KUIOPS_GEMM_COUNTER_BYTES 16384
 KUIOPS_API size_t kuiops_gemm_workspace_bytes(int dtype, uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
+
+/* Tuned plans of the tcgen05 GEMM.  The kernel chooses its K split (weight-streaming placement,
+ * M <= 128: 1..8 CTAs of a cluster share a tile) and its column tile (normal placement: 128 or
+ * 256) by rule; a tuner that has timed the alternatives of a shape records its choice here and
+ * every later call of that shape (batch 1) uses it.  `epilogue`: 0 plain / bias, 1 SwiGLU, 2 rotary.
+ * splits == 0 keeps the rule for the split, bn == 0 for the tile; both 0 forgets the shape.
+ * Results do not depend on the column tile; a different K split changes the order of the fp32
+ * partial sums (still deterministic for a given plan).  kuiops_gemm_tune_query reports the plan a
+ * shape would run with.  Host-side table, process wide, guarded by a mutex.
+ * Reference: the per-family tune_params hook, kuipy/kuiops.py:27-43 and kuipy/registry.py:62-76
+ * (load / save are stubs there; its tile choosers pick the first fitting tile, kuiops.py:330-394). */
+KUIOPS_API int kuiops_gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K,
+                                    int splits, int bn);
+KUIOPS_API int kuiops_gemm_tune_clear(void);
+KUIOPS_API int kuiops_gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K,
+                                      int* splits, int* bn, int* swapped);
 KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
                 uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, int64_t stride_a,

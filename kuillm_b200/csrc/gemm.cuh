@@ -42,5 +42,9 @@ int gemm_simt(const GemmArgs& a, cudaStream_t st);
 bool gemm_tc_eligible(const GemmArgs& a);
 size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
 int gemm_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+// Tuned-plan table of the tcgen05 kernel (see kuiops_gemm_tune_set).
+int gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int splits, int bn);
+void gemm_tune_clear();
+int gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int* splits, int* bn, int* swapped);
 
 }  // namespace kuiops

@@ -83,6 +83,15 @@ int kuiops_gemm(int dtype, int out_dtype, uint32_t batch, uint32_t M, uint32_t N
   return gemm_simt(a, st);
 }
 
+int kuiops_gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int splits, int bn) {
+  return gemm_tune_set(dtype, epilogue, trans_b, M, N, K, splits, bn);
+}
+int kuiops_gemm_tune_clear(void) { gemm_tune_clear(); return KUIOPS_OK; }
+int kuiops_gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int* splits, int* bn,
+                           int* swapped) {
+  return gemm_tune_query(dtype, epilogue, trans_b, M, N, K, splits, bn, swapped);
+}
+
 int kuiops_gemm_swiglu(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
                        const void* W, int64_t ldw, void* Y, int64_t ldy,
                        void* workspace, size_t workspace_bytes, kuiops_stream_t stream) {

@@ -22,6 +22,9 @@
 #include <cooperative_groups.h>
 #include <mutex>
 #include <type_traits>
+#include <string>
+#include <unordered_map>
+#include <cstdio>
 
 namespace cg = cooperative_groups;
 namespace kuiops {
@@ -571,21 +574,55 @@ struct TcPlan { bool swapped; int bn; uint32_t tilesP, tilesQ, splits, kblocks, 
 // flight, not the depth of one CTA's ring.
 constexpr uint32_t swapped_stages(int bn) { return bn <= 16 ? 4u : 3u; }
 
+// ---- tuned plans ------------------------------------------------------------------------------
+// A tuner (kuipy.tuner, behind KUIPY_RE_TUNE) times the alternatives of a shape and records the best
+// here; make_plan consults the table before its own rule.  Keyed by (dtype, epilogue, transposed B,
+// M, N, K); the value is the K split of the weight-streaming placement or the column tile of the
+// normal one.
+struct TunedPlan { int splits, bn; };
+static std::mutex g_tuned_mu;
+static std::unordered_map<std::string, TunedPlan> g_tuned;
+static std::atomic<int> g_tuned_count{0};
+
+static std::string tuned_key(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K) {
+  char buf[96];
+  snprintf(buf, sizeof buf, "%d/%d/%d/%u/%u/%u", dtype, epilogue, trans_b ? 1 : 0, M, N, K);
+  return buf;
+}
+
+static bool tuned_lookup(const GemmArgs& a, TunedPlan* out) {
+  if (g_tuned_count.load(std::memory_order_acquire) == 0 || a.batch != 1) return false;
+  std::lock_guard<std::mutex> lock(g_tuned_mu);
+  auto it = g_tuned.find(tuned_key(a.dtype, a.epilogue, a.trans_b, a.M, a.N, a.K));
+  if (it == g_tuned.end()) return false;
+  *out = it->second;
+  return true;
+}
+
 static TcPlan make_plan(const GemmArgs& a) {
   TcPlan pl = {};
   pl.kblocks = (a.K + TBK - 1) / TBK;
   pl.swapped = a.M <= 128;
+  TunedPlan tuned = {0, 0};
+  const bool have_tuned = tuned_lookup(a, &tuned);
   if (pl.swapped) {
     pl.bn = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128));
     pl.tilesP = (a.N + TBM - 1) / TBM;
     pl.tilesQ = 1;
   } else {
     pl.bn = a.N > 128 ? 256 : 128;
+    if (have_tuned && (tuned.bn == 128 || tuned.bn == 256)) pl.bn = tuned.bn;
     pl.tilesP = (a.M + TBM - 1) / TBM;
     pl.tilesQ = (a.N + pl.bn - 1) / pl.bn;
   }
   const uint64_t tiles = uint64_t(pl.tilesP) * pl.tilesQ * a.batch;
   pl.splits = 1;
+  if (pl.swapped && have_tuned && tuned.splits >= 1 && tuned.splits <= 8 && uint32_t(tuned.splits) <= pl.kblocks) {
+    pl.splits = uint32_t(tuned.splits);
+    pl.kb_per_split = (pl.kblocks + pl.splits - 1) / pl.splits;
+    pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;   // no empty slice
+    return pl;
+  }
   if (pl.swapped) {
     // Too few output tiles to occupy the machine: split K over the CTAs of a cluster (at most 8, the
     // portable cluster size).  Aim at as many CTAs as can be resident at once.
@@ -611,6 +648,35 @@ static TcPlan make_plan(const GemmArgs& a) {
     pl.splits = (pl.kblocks + pl.kb_per_split - 1) / pl.kb_per_split;
   }
   return pl;
+}
+
+int gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int splits, int bn) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || N == 0 || K == 0 || epilogue < 0 || epilogue > 2) return KUIOPS_EINVAL;
+  if (splits < 0 || splits > 8 || !(bn == 0 || bn == 128 || bn == 256)) return KUIOPS_EINVAL;
+  std::lock_guard<std::mutex> lock(g_tuned_mu);
+  const std::string key = tuned_key(dtype, epilogue, trans_b, M, N, K);
+  if (splits == 0 && bn == 0) g_tuned.erase(key);
+  else g_tuned[key] = TunedPlan{splits, bn};
+  g_tuned_count.store(int(g_tuned.size()), std::memory_order_release);
+  return KUIOPS_OK;
+}
+
+void gemm_tune_clear() {
+  std::lock_guard<std::mutex> lock(g_tuned_mu);
+  g_tuned.clear();
+  g_tuned_count.store(0, std::memory_order_release);
+}
+
+int gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int* splits, int* bn, int* swapped) {
+  if (M == 0 || N == 0 || K == 0) return KUIOPS_EINVAL;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = N; a.K = K; a.trans_b = trans_b; a.epilogue = epilogue;
+  const TcPlan pl = make_plan(a);
+  if (splits) *splits = int(pl.splits);
+  if (bn) *bn = pl.bn;
+  if (swapped) *swapped = pl.swapped ? 1 : 0;
+  return KUIOPS_OK;
 }
 
 // The split-K partials live in shared memory, so the GEMM kernels need no global scratch; the

@@ -13,6 +13,8 @@ from pathlib import Path
 
 import torch
 
+from . import config as _C
+
 _PKG = Path(__file__).resolve().parent.parent
 LIB_PATH = Path(os.environ.get("KUIOPS_LIB", _PKG / "lib" / "libkuiops.so"))
 
@@ -53,6 +55,10 @@ SIGNATURES = {
     "kuiops_launch_count": (c_u64, []),
     "kuiops_set_pdl": (c_int, [c_int]),
     "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),
+    "kuiops_gemm_tune_set": (c_int, [c_int, c_int, c_int, c_u32, c_u32, c_u32, c_int, c_int]),
+    "kuiops_gemm_tune_clear": (c_int, []),
+    "kuiops_gemm_tune_query": (c_int, [c_int, c_int, c_int, c_u32, c_u32, c_u32, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                                       ctypes.POINTER(c_int)]),
     "kuiops_gemm": (c_int, [c_int, c_int, c_u32, c_u32, c_u32, c_u32,
                             c_void_p, c_i64, c_i64, c_void_p, c_i64, c_i64, c_int,
                             c_void_p, c_i64, c_i64, c_float, c_float,
@@ -136,6 +142,12 @@ def lib():
             fn.restype = res
             fn.argtypes = args
         _lib = L
+        try:
+            # tuned GEMM plans: the table shipped with the package, then the user's own (KUIPY_CACHE)
+            from . import tuner
+            tuner.apply(tuner.load_tables(), L)
+        except Exception as e:      # noqa: BLE001 - a damaged table must not make the kernels unavailable
+            _C.log(f"tuned plans not applied: {e}")
         return L
     except (OSError, AttributeError) as e:
         _load_error = RuntimeError(f"kuiops: cannot load the CUDA library: {e}")
@@ -155,6 +167,14 @@ def strerror(code: int) -> str:
         return lib().kuiops_strerror(code).decode()
     except RuntimeError:
         return f"kuiops error {code}"
+
+
+def gemm_plan(dtype, M, N, K, trans_b=True, epilogue=0):
+    """(splits, column tile, swapped placement) the tcgen05 GEMM would run this shape with."""
+    s, b, w = c_int(0), c_int(0), c_int(0)
+    _check(lib().kuiops_gemm_tune_query(dtype_code(dtype), epilogue, 1 if trans_b else 0, M, N, K, ctypes.byref(s), ctypes.byref(b),
+                                        ctypes.byref(w)), "gemm_tune_query")
+    return s.value, b.value, bool(w.value)
 
 
 def set_pdl(enabled: bool) -> bool:
@@ -275,6 +295,9 @@ def gemm(A, B, *, trans_b=False, Cin=None, alpha=1.0, beta=1.0, out=None, out_dt
             scin = Cin.stride(0) if Cin.dim() == 3 else 0
     L = lib()
     code = dtype_code(dt)
+    if _C.RE_TUNE and not batched:
+        from . import tuner
+        tuner.maybe_tune(dt, M, N, K, trans_b, 0)
     wsb = L.kuiops_gemm_workspace_bytes(code, bsz, M, N, K)
     ws = workspace("gemm", A.device, wsb)
     _check(L.kuiops_gemm(code, dtype_code(odt), bsz, M, N, K,
@@ -293,6 +316,9 @@ def gemm_rope_qkv(A, W, hq, hk, d, positions, theta, k_cache=None, v_cache=None,
         return None
     if out is None:
         out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    if _C.RE_TUNE and M <= 128 and d == 128:
+        from . import tuner
+        tuner.maybe_tune(A.dtype, M, N, K, True, 2)
     cap = k_cache.shape[2] if k_cache is not None else 0
     rc = lib().kuiops_gemm_rope_qkv(dtype_code(A.dtype), M, hq, hk, d, K, A.data_ptr(), max(A.stride(0), K), W.data_ptr(), W.stride(0),
                                     out.data_ptr(), max(out.stride(0), N), positions.data_ptr(), float(theta), _ptr(k_cache),
@@ -338,6 +364,9 @@ def gemm_swiglu(A, W_interleaved, out=None):
     if out is None:
         out = torch.empty((M, N), dtype=A.dtype, device=A.device)
     L = lib()
+    if _C.RE_TUNE and A.dtype in (torch.bfloat16, torch.float16):
+        from . import tuner
+        tuner.maybe_tune(A.dtype, M, 2 * N, K, True, 1)
     rc = L.kuiops_gemm_swiglu(dtype_code(A.dtype), M, N, K, A.data_ptr(), max(A.stride(0), K), W_interleaved.data_ptr(),
                               W_interleaved.stride(0), out.data_ptr(), max(out.stride(0), N), None, 0, _stream()) \
         if A.dtype in (torch.bfloat16, torch.float16) and A.stride(1) == 1 and W_interleaved.stride(1) == 1 else EUNSUPPORTED

@@ -306,6 +306,27 @@ class MmImpl(_Family):
         engine = "tcgen05" if A.dtype != torch.float32 else "simt"
         return (engine, A.dtype, [A, B])
 
+    def tune(self, all_tune_params):
+        """Re-time the plans of every GEMM shape recorded so far (``kuipy.tuner``) and hand the table
+        back for saving.  Shapes not seen yet are tuned at their first call while ``KUIPY_RE_TUNE``
+        is on.  Without a GPU the recorded table is passed through unchanged."""
+        from . import tuner
+        params = dict(self.tune_params) if isinstance(self.tune_params, dict) else {"impl": "tc2d"}
+        plans = dict(params.get("plans", {}))
+        if torch.cuda.is_available() and _ffi.is_loadable():
+            for key in list(plans):
+                try:
+                    dt, epi, tb, M, N, K = (int(x) for x in key.split("/"))
+                except ValueError:
+                    continue
+                dtype = {1: torch.bfloat16, 2: torch.float16}.get(dt)
+                if dtype is not None:
+                    plans[key] = tuner.tune_gemm(dtype, M, N, K, bool(tb), epi)
+        params["plans"] = plans
+        self.tune_params = params
+        all_tune_params[self.tune_key] = params
+        return all_tune_params
+
     def run(self, spec, args, kwargs):
         engine, dt, call = spec
         module = f"Kuiops.Mm.{engine.title()}.{_TAG[dt].title()}"

@@ -337,6 +337,20 @@ KUIOPS_API int kuiops_mean_f32 (uint64_t m, uint64_t n, const void* in, void* ou
 KUIOPS_API int kuiops_mean_bf16(uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t stream);
 KUIOPS_API int kuiops_mean_f16 (uint64_t m, uint64_t n, const void* in, void* out, kuiops_stream_t stream);
 
+/* Categorical sampling: out[i, j] = an index of row i of the [m, n] fp32 weight matrix drawn with
+ * probability weights[i, k] / sum_k weights[i, k], num_samples draws per row, independent (with
+ * replacement).  aten.multinomial(probs, num_samples, replacement) for num_samples == 1 or
+ * replacement == True.  No counterpart in the reference beyond the backlog entry (KERNELS.md:68-90).
+ * The random stream is documented so that every draw can be recomputed: u(i, j) = (x0 >> 8) * 2^-24
+ * with (x0, ..) = Philox4x32-10(counter = (offset low, offset high, i, j), key = (seed low, seed
+ * high)), and the index is found by inverting the row's running fp32 sum evaluated in a fixed
+ * order (see csrc/sampling.cu); an element of weight zero is never drawn.  PyTorch's own draws use
+ * a stream private to its kernels, so results agree in distribution, not bit for bit.  A negative,
+ * infinite or NaN weight counts as zero and stores 2 in *status; a row without any weight yields
+ * index 0 and stores 3 (`status` may be NULL). */
+KUIOPS_API int kuiops_multinomial_f32(uint32_t m, uint32_t n, uint32_t num_samples, const void* weights, int64_t* out,
+                                      uint64_t seed, uint64_t offset, int* status, kuiops_stream_t stream);
+
 /* Whole-tensor folds to one device scalar (aten.all / aten.any over bool bytes,
  * aten.max over int64 / fp32).  Reference: Kuiops.HReducePoly.Exact.reduce,
  * kuiops/reduce/Kuiops.HReducePoly.Exact.fsti:26-46 (which mallocs the result

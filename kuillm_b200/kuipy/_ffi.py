@@ -111,6 +111,7 @@ SIGNATURES = {
     "kuiops_cumsum_i64": (c_int, [c_u32, c_u32, c_void_p, c_void_p, c_void_p]),
     "kuiops_sort_workspace_bytes": (c_size_t, [c_u32, c_u32]),
     "kuiops_sort_f32": (c_int, [c_u32, c_u32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "kuiops_multinomial_f32": (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_u64, c_u64, c_void_p, c_void_p]),
     "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
 }
 for _sfx in ("f32", "bf16", "f16"):
@@ -535,6 +536,20 @@ def argmax_lastdim(X):
     m = Xc.numel() // n
     out = torch.empty(tuple(Xc.shape[:-1]), dtype=torch.int64, device=Xc.device)
     _check(lib().kuiops_argmax(dtype_code(Xc.dtype), m, n, Xc.data_ptr(), out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def multinomial(P, num_samples=1, seed=0, offset=0):
+    """One index per (row, sample) of the fp32 weight matrix P ([m, n] or [n]), drawn with replacement from the
+    documented Philox stream (seed, offset); see kuiops_multinomial_f32."""
+    if P.dtype != torch.float32:
+        raise KuiopsError(EUNSUPPORTED, f"multinomial over {P.dtype}")
+    Pc = P.contiguous()
+    n = Pc.shape[-1]
+    m = Pc.numel() // n
+    out = torch.empty(tuple(Pc.shape[:-1]) + (num_samples,), dtype=torch.int64, device=Pc.device)
+    _check(lib().kuiops_multinomial_f32(m, n, num_samples, Pc.data_ptr(), out.data_ptr(), int(seed) & (2 ** 64 - 1),
+                                        int(offset) & (2 ** 64 - 1), _status(Pc.device).data_ptr(), _stream()), "multinomial")
     return out
 
 

@@ -50,20 +50,35 @@ def _define_same_schema(lib, name, aten_op, schema):
     return getattr(torch.ops.kuiops, name).default
 
 
-def _define_sdpa(lib):
-    lib.define("sdpa(Tensor q, Tensor k, Tensor v, Tensor? bias, float scale, bool causal) -> (Tensor, Tensor)")
+def _attention_out(q, ev, blhd):
+    """Output buffer with the memory layout the replaced ATen overload would have produced, because
+    the traced graph was specialised on it (a ``transpose(1, 2).contiguous().view(...)`` behind the
+    attention is traced as a plain view when the transposed output is already dense): the
+    efficient overload always returns (batch, row, head, dim) memory, the flash and cuDNN
+    overloads return the dimension order of the query."""
+    n, h, l, _ = q.shape
+    if blhd:
+        return q.new_empty((n, l, h, ev)).transpose(1, 2)
+    order = sorted(range(3), key=lambda d: -int(q.stride(d)))            # slowest-varying first; dim 3 stays innermost
+    sizes = [(n, h, l)[d] for d in order]
+    buf = q.new_empty((*sizes, ev))
+    return buf.permute(*[order.index(d) for d in range(3)], 3)
 
+
+def _define_sdpa(lib):
+    lib.define("sdpa(Tensor q, Tensor k, Tensor v, Tensor? bias, float scale, bool causal, bool blhd) -> (Tensor, Tensor)")
     stats = call_stats.setdefault("sdpa", [0, 0])
 
-    def impl(q, k, v, bias, scale, causal):
+    def impl(q, k, v, bias, scale, causal, blhd):
         from . import _ffi
         stats[0] += 1
-        return _ffi.sdpa(q, k, v, bias=bias, scale=scale, is_causal=causal, need_lse=True)
+        out = _attention_out(q, v.shape[3], blhd)
+        return _ffi.sdpa(q, k, v, bias=bias, scale=scale, is_causal=causal, need_lse=True, out=out)
     lib.impl("sdpa", impl, "CUDA")
 
     @torch.library.register_fake("kuiops::sdpa")
-    def _(q, k, v, bias, scale, causal):
-        out = q.new_empty((q.shape[0], q.shape[1], q.shape[2], v.shape[3]))
+    def _(q, k, v, bias, scale, causal, blhd):
+        out = _attention_out(q, v.shape[3], blhd)
         return out, q.new_empty((q.shape[0], q.shape[1], q.shape[2]), dtype=torch.float32)
     return torch.ops.kuiops.sdpa.default
 
@@ -159,7 +174,7 @@ def _lower_sdpa(graph, node, fam):
     q, k, v = node.args[0], node.args[1], node.args[2]
     bias = node.args[3] if overload in ("efficient", "cudnn") else None
     with graph.inserting_before(node):
-        new = graph.call_function(_OPS["sdpa"], (q, k, v, bias, float(scale), bool(causal)))
+        new = graph.call_function(_OPS["sdpa"], (q, k, v, bias, float(scale), bool(causal), overload == "efficient"))
     new.meta["val"] = (node.meta["val"][0], node.meta["val"][1]) if "val" in node.meta else None
     for user in list(node.users):
         if user.target is operator.getitem and user.args[1] in (0, 1):

@@ -907,7 +907,8 @@ _compile.register_binder(IsinImpl.wrapper_template, lambda ctx: (lambda E, T, in
 class DataMoveImpl(_Family):
     """The data-movement ops a decoder issues next to its compute on every token: dtype casts
     (aten._to_copy between float types), aten.clone, aten.masked_fill.Scalar, aten.argmax,
-    aten.cumsum and aten.sort over the last axis and aten.embedding.  The reference lists them as backlog without kernels
+    aten.cumsum and aten.sort over the last axis, aten.multinomial (one draw per row, or several with
+    replacement, from a documented Philox stream) and aten.embedding.  The reference lists them as backlog without kernels
     (KERNELS.md:46-48,68-90); dense, contiguous operands only, everything else falls through."""
     fst_template = "datamove/Kuiops.DataMove.Inst.fst.j2"
     wrapper_template = "datamove/wrapper_datamove.cu.j2"
@@ -915,7 +916,7 @@ class DataMoveImpl(_Family):
     tune_params = ()
     _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
     overloads = (aten._to_copy.default, aten.clone.default, aten.masked_fill.Scalar, aten.argmax.default,
-                 aten.cumsum.default, aten.sort.default, aten.sort.stable, aten.embedding.default)
+                 aten.cumsum.default, aten.sort.default, aten.sort.stable, aten.embedding.default, aten.multinomial.default)
 
     @staticmethod
     def _dense(X):
@@ -974,6 +975,16 @@ class DataMoveImpl(_Family):
                     and isinstance(desc, bool) and _wrap_dim(dim, X.dim()) == X.dim() - 1):
                 return ("sort", desc, [X])
             return None
+        if func is aten.multinomial.default:
+            # multinomial(self, num_samples, replacement=False, *, generator=None): one draw per row, or several
+            # independent ones; draws without replacement depend on each other and stay with PyTorch
+            k = args[1] if len(args) > 1 else kwargs.get("num_samples")
+            repl = kwargs.get("replacement", args[2] if len(args) > 2 else False)
+            gen = kwargs.get("generator")
+            if (self._dense(X) and X.dtype == torch.float32 and X.dim() in (1, 2) and isinstance(k, int) and not isinstance(k, bool)
+                    and 1 <= k <= 4096 and (k == 1 or repl) and (gen is None or gen.device.type == "cuda")):
+                return ("multinomial", (k, gen), [X])
+            return None
         if func is aten.embedding.default:
             if len(args) < 2:
                 return None
@@ -1005,6 +1016,17 @@ def _datamove_binder(ctx):
         return lambda X, _=None: _ffi.cumsum_lastdim(X)
     if op == "sort":
         return lambda X, desc: _ffi.sort_lastdim(X, desc)
+    if op == "multinomial":
+        def draw(X, extra):
+            # the stream position comes from (and is advanced in) the CUDA generator the call names, or the
+            # device's default one: seed = its seed, offset = its Philox offset, moved on by 4 per call
+            k, gen = extra
+            if gen is None:
+                gen = torch.cuda.default_generators[X.device.index if X.device.index is not None else torch.cuda.current_device()]
+            off = gen.get_offset()
+            gen.set_offset(off + 4)
+            return _ffi.multinomial(X, k, gen.initial_seed(), off)
+        return draw
     return lambda W, ids, _=None: _ffi.embedding(W, ids)
 
 

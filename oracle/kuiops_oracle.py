@@ -215,6 +215,106 @@ def sort_lastdim(X: np.ndarray, descending: bool = False):
     return vals.reshape(X.shape), idxs.reshape(X.shape)
 
 
+def philox4x32_10(counter, key):
+    """Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11):
+    the published algorithm, restated.  counter: 4 uint32, key: 2 uint32 -> 4 uint32."""
+    c = [int(x) & 0xFFFFFFFF for x in counter]
+    k = [int(x) & 0xFFFFFFFF for x in key]
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * c[0], 0xCD9E8D57 * c[2]
+        c = [((p1 >> 32) ^ c[1] ^ k[0]) & 0xFFFFFFFF, p1 & 0xFFFFFFFF, ((p0 >> 32) ^ c[3] ^ k[1]) & 0xFFFFFFFF, p0 & 0xFFFFFFFF]
+        k = [(k[0] + 0x9E3779B9) & 0xFFFFFFFF, (k[1] + 0xBB67AE85) & 0xFFFFFFFF]
+    return c
+
+
+def multinomial(P: np.ndarray, num_samples: int, seed: int, offset: int) -> np.ndarray:
+    """Categorical draws with replacement from the rows of a non-negative fp32 matrix: the
+    specification the kuiops kernel states for itself (the reference has no multinomial kernel,
+    only the backlog entry KERNELS.md:68-90; PyTorch's draws use a private stream and agree in
+    distribution only).  u(row, j) = (x0 >> 8) * 2^-24 with x = Philox4x32-10((offset_lo,
+    offset_hi, row, j), (seed_lo, seed_hi)); the index inverts the row's running fp32 sum taken in
+    a fixed order: 4 elements per lane left to right, a Hillis-Steele scan over the 32 lanes of a
+    128-element group, groups left to right inside each of 32 segments, segments left to right;
+    at every level the first entry with weight whose running sum exceeds the target, else the last
+    entry with weight."""
+    f32 = np.float32
+    rows = P.reshape(-1, P.shape[-1]).astype(f32)
+    m, n = rows.shape
+    groups = -(-n // 128)
+    gpw = -(-groups // 32)
+    out = np.zeros((m, num_samples), dtype=np.int64)
+    for r in range(m):
+        a = np.zeros(groups * 128, dtype=f32)
+        a[:n] = rows[r]
+        a[~(a >= 0) | np.isinf(a)] = 0
+        a = a.reshape(groups, 32, 4)
+        e = np.empty_like(a)                                  # running sums inside a lane
+        e[..., 0] = a[..., 0]
+        for j in range(1, 4):
+            e[..., j] = e[..., j - 1] + a[..., j]
+        own = e[..., 3]
+        incl = own.copy()                                     # Hillis-Steele over the 32 lanes
+        for o in (1, 2, 4, 8, 16):
+            up = np.zeros_like(incl)
+            up[:, o:] = incl[:, :-o]
+            nxt = incl + up
+            nxt[:, :o] = incl[:, :o]
+            incl = nxt.astype(f32)
+        excl = np.zeros_like(incl)
+        excl[:, 1:] = incl[:, :-1]
+        gsum = incl[:, 31]
+        seg_sum = np.zeros(32, dtype=f32)
+        for w in range(32):
+            s = f32(0)
+            for k in range(min(w * gpw, groups), min(w * gpw + gpw, groups)):
+                s = f32(s + gsum[k])
+            seg_sum[w] = s
+        prefix = np.zeros(33, dtype=f32)
+        for w in range(32):
+            prefix[w + 1] = f32(prefix[w] + seg_sum[w])
+        total = prefix[32]
+        for j in range(num_samples):
+            x = philox4x32_10((offset & 0xFFFFFFFF, (offset >> 32) & 0xFFFFFFFF, r, j), (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+            u = f32(x[0] >> 8) * f32(2.0 ** -24)
+            t = f32(u * total)
+            w, last = -1, -1
+            for q in range(32):
+                if seg_sum[q] > 0:
+                    last = q
+                    if prefix[q + 1] > t:
+                        w = q
+                        break
+            if w < 0:
+                w = last
+            if w < 0:
+                out[r, j] = 0
+                continue
+            tw = f32(t - prefix[w])
+            run, hit, hit_run, lastk, last_run = f32(0), -1, f32(0), -1, f32(0)
+            for k in range(min(w * gpw, groups), min(w * gpw + gpw, groups)):
+                if gsum[k] > 0:
+                    lastk, last_run = k, run
+                    if f32(run + gsum[k]) > tw:
+                        hit, hit_run = k, run
+                        break
+                run = f32(run + gsum[k])
+            if hit < 0:
+                hit, hit_run = lastk, last_run
+            has = own[hit] > 0
+            over = has & ((hit_run + incl[hit]).astype(f32) > tw)
+            lane = int(np.argmax(over)) if over.any() else int(np.nonzero(has)[0][-1])
+            choice, lastnz = -1, -1
+            for i in range(4):
+                if a[hit, lane, i] > 0:
+                    lastnz = i
+                    if choice < 0 and f32(hit_run + f32(excl[hit, lane] + e[hit, lane, i])) > tw:
+                        choice = i
+            if choice < 0:
+                choice = lastnz
+            out[r, j] = hit * 128 + lane * 4 + choice
+    return out.reshape(P.shape[:-1] + (num_samples,))
+
+
 def mean_lastdim(X: np.ndarray) -> np.ndarray:
     """sum_j (x[i,j] / n), keepdim: the division is part of the pre-map
     (kuiops/mean/Kuiops.Mean.fsti:25-32)."""

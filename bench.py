@@ -429,8 +429,7 @@ def time_decoder(dec, cfg, batch, prompt, new, ids_dev, ids_host, dev, steps, wa
         dec.length = 0
         if marks is not None:
             marks[0].record()
-        logits = dec.prefill(ids)
-        tok = _ffi.argmax_lastdim(logits)
+        tok = dec.next_token(dec.prefill(ids, local_logits=True))
         gen_buf[:, 0].copy_(tok)
         if marks is not None:
             marks[1].record()
@@ -439,7 +438,7 @@ def time_decoder(dec, cfg, batch, prompt, new, ids_dev, ids_host, dev, steps, wa
             replays[0] += new - 1
         else:
             for t in range(1, new):
-                tok = _ffi.argmax_lastdim(dec.decode_step(tok))
+                tok = dec.next_token(dec.decode_step(tok, local_logits=True))
                 gen_buf[:, t].copy_(tok)
         if marks is not None:
             marks[2].record()

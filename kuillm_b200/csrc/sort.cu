@@ -3,16 +3,24 @@
 // -0 equals +0, NaN is the largest value.  The reference only lists sort as backlog
 // (KERNELS.md:68-90) and has no kernel.
 //
-// One CTA per row runs a least-significant-digit radix sort on order-preserving 32-bit keys, four
-// passes of eight bits.  The four digit histograms of the row are counted once up front.  A pass
-// walks the row tile by tile; inside a tile the rank of an element among the equal digits before
-// it is found per warp with match.any plus a per-warp counter table in shared memory, the warps'
-// tables are then turned into offsets by one thread per digit, and the elements are scattered.
-// Keys and indices ping-pong between two caller-provided buffers; the first pass reads the input
-// itself and the last pass writes the results.
+// A cluster of 1..8 CTAs per row runs a least-significant-digit radix sort on order-preserving
+// 32-bit keys, four passes of eight bits; every CTA owns one contiguous chunk of the row's
+// positions.  The four digit histograms of the row are counted once up front (each CTA counts
+// its chunk, the chunks' histograms are summed through distributed shared memory).  Before a
+// pass every CTA counts the digits of its chunk in the current arrangement and reads the counts of
+// the chunks before it from its peers: that gives the first output position of each digit for
+// its chunk.  The pass then walks the chunk tile by tile; inside a tile the rank of an element
+// among the equal digits before it is found per warp with match.any plus a per-warp counter table
+// in shared memory, the warps' tables are turned into offsets by one thread per digit, and the
+// elements are scattered.  Keys and indices ping-pong between two caller-provided buffers; the
+// first pass reads the input itself and the last pass writes the results.  Cluster barriers
+// separate the passes (a pass reads what every CTA of the row wrote in the one before).
 #include <atomic>
+#include <cooperative_groups.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace kuiops {
 
@@ -30,6 +38,8 @@ struct SortShared {
   uint32_t tile_start[kSortDigits];              // per tile: first slot of a digit in the tile's sorted order
   int32_t delta[kSortDigits];                    // per tile: global position minus slot, per digit
   uint32_t warp_sum[kSortDigits / 32];
+  uint32_t chunk_hist[kSortPasses][kSortDigits]; // this CTA's chunk: digit counts of the input, per pass (read by the peers once)
+  uint32_t chunk_cnt[kSortDigits];               // this CTA's chunk: digit counts in the arrangement the current pass reads (read by the peers)
   uint2 slot[kSortTile];                         // the tile in sorted order: (key, index)
 };
 
@@ -49,25 +59,40 @@ __device__ __forceinline__ uint32_t sort_key(float v, bool descending) {
 
 __global__ void __launch_bounds__(kSortThreads)
 sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float* __restrict__ values,
-                 int64_t* __restrict__ indices, uint2* buf_a, uint2* buf_b) {
+                 int64_t* __restrict__ indices, uint2* buf_a, uint2* buf_b, uint32_t cluster_ctas) {
   extern __shared__ __align__(16) unsigned char sort_smem[];
   SortShared& sh = *reinterpret_cast<SortShared*>(sort_smem);
-  const uint32_t row = blockIdx.x;
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t part = cluster_ctas > 1 ? cluster.block_rank() : 0;
+  const uint32_t row = blockIdx.x / cluster_ctas;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const size_t off = size_t(row) * n;
   const float* x = X + off;
   const bool desc = descending != 0;
+  // this CTA's chunk of the row's positions
+  const uint32_t chunk = (n + cluster_ctas - 1) / cluster_ctas;
+  const uint32_t lo = min(uint64_t(part) * chunk, uint64_t(n)), hi = min(uint64_t(lo) + chunk, uint64_t(n));
   pdl_wait();
   pdl_trigger();
 
-  // ---- the four digit histograms of the row ---------------------------------------------------
+  // ---- the four digit histograms: of this chunk, then of the row --------------------------------
   static_assert(kSortPasses * kSortDigits == kSortThreads, "one histogram entry per thread");
-  (&sh.hist[0][0])[tid] = 0;
+  (&sh.chunk_hist[0][0])[tid] = 0;
   __syncthreads();
-  for (uint32_t i = tid; i < n; i += kSortThreads) {
+  for (uint32_t i = lo + tid; i < hi; i += kSortThreads) {
     const uint32_t k = sort_key(x[i], desc);
 #pragma unroll
-    for (int p = 0; p < kSortPasses; ++p) atomicAdd(&sh.hist[p][(k >> (8 * p)) & 255u], 1u);
+    for (int p = 0; p < kSortPasses; ++p) atomicAdd(&sh.chunk_hist[p][(k >> (8 * p)) & 255u], 1u);
+  }
+  __syncthreads();
+  if (tid < kSortDigits) sh.chunk_cnt[tid] = sh.chunk_hist[0][tid];      // pass 0 reads the input: its chunk counts are known already
+  if (cluster_ctas > 1) {
+    cluster.sync();                                                       // every chunk's histograms are complete (and every peer is running)
+    uint32_t sum = 0;
+    for (uint32_t r = 0; r < cluster_ctas; ++r) sum += (&cluster.map_shared_rank(&sh.chunk_hist[0][0], r)[0])[tid];
+    (&sh.hist[0][0])[tid] = sum;
+  } else {
+    (&sh.hist[0][0])[tid] = (&sh.chunk_hist[0][0])[tid];
   }
   __syncthreads();
   if (warp < kSortPasses) {
@@ -92,8 +117,21 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
     const uint32_t shift = 8u * pass;
     const uint2* src = (pass == 2 ? buf_b : buf_a) + off;                // pass 0 reads x instead
     uint2* dst = (pass == 1 ? buf_b : buf_a) + off;                      // pass 3 writes the results instead
-    if (tid < kSortDigits) sh.base[tid] = sh.hist[pass][tid];          // read again by the same thread only
-    for (uint32_t tile0 = 0; tile0 < n; tile0 += kSortTile) {
+    if (pass > 0) {
+      // digit counts of this chunk in the arrangement this pass reads
+      if (tid < kSortDigits) sh.chunk_cnt[tid] = 0;
+      __syncthreads();
+      for (uint32_t i = lo + tid; i < hi; i += kSortThreads) atomicAdd(&sh.chunk_cnt[(src[i].x >> shift) & 255u], 1u);
+      __syncthreads();
+    }
+    if (cluster_ctas > 1) cluster.sync();                                 // the peers' counts for this pass are complete
+    if (tid < kSortDigits) {
+      // first output position of a digit for this chunk: the digit's start in the row plus what the chunks before hold
+      uint32_t b = sh.hist[pass][tid];
+      for (uint32_t r = 0; r < part; ++r) b += cluster.map_shared_rank(&sh.chunk_cnt[0], r)[tid];
+      sh.base[tid] = b;                                                   // read again by the same thread only
+    }
+    for (uint32_t tile0 = lo; tile0 < hi; tile0 += kSortTile) {
 #pragma unroll
       for (int q = 0; q < kSortDigits / 32; ++q) sh.warp_cnt[warp][lane + 32 * q] = 0;
       // element order inside the tile: warp, then j, then lane
@@ -102,7 +140,7 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
       for (int j = 0; j < kSortItems; ++j) {
         const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
         key[j] = 0; idx[j] = e;
-        if (e < n) {
+        if (e < hi) {
           if (pass == 0) key[j] = sort_key(x[e], desc);
           else { const uint2 kv = src[e]; key[j] = kv.x; idx[j] = kv.y; }
         }
@@ -111,7 +149,7 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
 #pragma unroll
       for (int j = 0; j < kSortItems; ++j) {
         const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
-        const bool valid = e < n;
+        const bool valid = e < hi;
         const uint32_t d = valid ? ((key[j] >> shift) & 255u) : 0xFFFFFFFFu;   // lanes past the end match only each other
         const uint32_t peers = __match_any_sync(0xffffffffu, d);
         const int leader = __ffs(peers) - 1;
@@ -156,14 +194,14 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
 #pragma unroll
       for (int j = 0; j < kSortItems; ++j) {
         const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
-        if (e < n) {
+        if (e < hi) {
           const uint32_t d = (key[j] >> shift) & 255u;
           sh.slot[sh.tile_start[d] + sh.warp_cnt[warp][d] + rank[j]] = make_uint2(key[j], idx[j]);
         }
       }
       __syncthreads();
       // ... and out: neighbouring threads write neighbouring positions of a digit's run
-      const uint32_t in_tile = min(kSortTile, n - tile0);
+      const uint32_t in_tile = min(kSortTile, hi - tile0);
 #pragma unroll
       for (int q = 0; q < kSortItems; ++q) {
         const uint32_t l = uint32_t(q) * kSortThreads + tid;
@@ -180,6 +218,9 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
       }
       __syncthreads();                                // tables and slots consumed before the next tile; stores ordered for the next pass
     }
+    // the next pass reads what every CTA of the row wrote in this one, and overwrites the counts the
+    // peers have just read
+    if (cluster_ctas > 1) cluster.sync();
   }
 }
 
@@ -214,8 +255,13 @@ int kuiops_sort_f32(uint32_t m, uint32_t n, int descending, const void* X, void*
       return KUIOPS_ELAUNCH;
     configured.fetch_or(bit, std::memory_order_release);
   }
-  return launch_pdl(sort_rows_kernel, dim3(m), dim3(kSortThreads), sizeof(SortShared), as_stream(s), n, descending,
-                    static_cast<const float*>(X), static_cast<float*>(values), indices, w, w + cells);
+  // few long rows: several CTAs per row, as long as the whole grid stays resident (two CTAs per SM) and
+  // every CTA keeps at least two tiles of work
+  uint32_t c = 1;
+  while (c < 8 && uint64_t(m) * c * 2 <= 2ull * num_sms() && n / (c * 2) >= 2 * kSortTile) c *= 2;
+  if (uint64_t(m) * c > 0x7FFFFFFFull) return KUIOPS_ELIMIT;
+  return launch_cluster_pdl(sort_rows_kernel, dim3(m * c), dim3(kSortThreads), sizeof(SortShared), as_stream(s), c, n, descending,
+                            static_cast<const float*>(X), static_cast<float*>(values), indices, w, w + cells, c);
 }
 
 }  // extern "C"

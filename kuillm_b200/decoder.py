@@ -81,6 +81,7 @@ class Decoder:
         self.cfg, self.device = cfg, torch.device(device)
         self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
         assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.d_ff % tp_size == 0
+        assert cfg.vocab % tp_size == 0
         self.hq, self.hk = cfg.n_heads // tp_size, cfg.n_kv_heads // tp_size
         self.ff = cfg.d_ff // tp_size
         g = torch.Generator(device=self.device).manual_seed(seed)
@@ -112,7 +113,12 @@ class Decoder:
             del wq, wk, wv, wo, wg, wu, wd
             self.layers.append(layer)
         self.norm_f = torch.ones(d, device=self.device, dtype=dt)
+        # vocabulary-parallel head: a rank scores vocab / tp consecutive token ids; the greedy step only
+        # exchanges each rank's best (value, id) pair per sequence instead of streaming the whole head on every rank
         self.lm_head = w(cfg.vocab, d)
+        if tp_size > 1:
+            self.lm_head = shard_out_features(self.lm_head, cfg.vocab, 1, tp_rank, tp_size).clone()   # a copy: the slice would keep all rows alive
+        self.vocab_lo = tp_rank * (cfg.vocab // tp_size)
         self.k_cache = self.v_cache = None
         self.cap = 0
         self.length = 0
@@ -207,18 +213,48 @@ class Decoder:
                 x = _ffi.index(x, 0, [last])
                 resid = _ffi.index(resid, 0, [last])
             hf = _ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid)
-        return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab]
+        return _ffi.gemm(hf, self.lm_head, trans_b=True)                 # [B or rows, vocab / tp]: this rank's token ids
 
-    def prefill(self, ids):
+    def _full_logits(self, local):
+        """[rows, vocab] logits on every rank from the ranks' vocabulary shards (tensor parallel only)."""
+        if self.tp_size == 1:
+            return local
+        rows, per = local.shape
+        parts = torch.empty((self.tp_size, rows, per), dtype=local.dtype, device=self.device)
+        torch.distributed.all_gather_into_tensor(parts, local.contiguous(), group=self.tp_group)
+        return parts.permute(1, 0, 2).reshape(rows, self.tp_size * per)
+
+    def next_token(self, local):
+        """Greedy token of every row from this rank's shard of the logits.  Tensor parallel: each rank
+        takes the arg-max of its shard, the ranks exchange (value, token id) pairs - two small
+        all-gathers instead of the whole vocabulary - and every rank picks the largest value, the
+        lowest rank (= lowest token id) winning ties, exactly as the arg-max over the full row does."""
+        idx = _ffi.argmax_lastdim(local)
+        if self.tp_size == 1:
+            return idx
+        B = idx.shape[0]
+        val = _ffi.gather(local, 1, idx.reshape(B, 1)).reshape(B)
+        if self.vocab_lo:
+            _ffi.add_i64_(idx, self.vocab_lo)
+        vals = torch.empty((self.tp_size, B), dtype=val.dtype, device=self.device)
+        idxs = torch.empty((self.tp_size, B), dtype=torch.int64, device=self.device)
+        torch.distributed.all_gather_into_tensor(vals, val, group=self.tp_group)
+        torch.distributed.all_gather_into_tensor(idxs, idx, group=self.tp_group)
+        best = _ffi.argmax_lastdim(vals.t().contiguous())                # [B]: the rank that holds the row's maximum
+        return _ffi.gather(idxs.t().contiguous(), 1, best.reshape(B, 1)).reshape(B)
+
+    def prefill(self, ids, local_logits=False):
         B, S = ids.shape
         assert self.k_cache is not None and S <= self.cap and self.length == 0
         positions = torch.arange(S, device=self.device).repeat(B)
-        return self._forward(ids, positions, S)
+        out = self._forward(ids, positions, S)
+        return out if local_logits else self._full_logits(out)
 
-    def decode_step(self, ids):
+    def decode_step(self, ids, local_logits=False):
         B = ids.shape[0]
         positions = torch.full((B,), self.length, device=self.device, dtype=torch.int64)
-        return self._forward(ids.reshape(B, 1), positions, 1)
+        out = self._forward(ids.reshape(B, 1), positions, 1)
+        return out if local_logits else self._full_logits(out)
 
     # ---- captured decode step -----------------------------------------------------------------
     def _graph_step(self):
@@ -227,7 +263,7 @@ class Decoder:
         B = self._tok.shape[0]
         logits = self._forward(self._tok.reshape(B, 1), self._pos, 1, kv_lens=self._kvlen)
         self.length -= 1                        # the host counter is advanced by the caller per replay
-        nxt = _ffi.argmax_lastdim(logits)
+        nxt = self.next_token(logits)
         self._tok_out.copy_(nxt)
         self._tok.copy_(nxt)
         _ffi.add_i64_(self._pos, 1)
@@ -278,8 +314,7 @@ class Decoder:
 
     def generate(self, ids, new_tokens, use_graph=False):
         """Greedy decoding; returns the [B, new_tokens] generated ids."""
-        logits = self.prefill(ids)
-        tok = _ffi.argmax_lastdim(logits)
+        tok = self.next_token(self.prefill(ids, local_logits=True))
         if use_graph and new_tokens > 1:
             if getattr(self, "_graph", None) is None or self._tok.shape[0] != ids.shape[0]:
                 self.capture_decode(ids.shape[0])
@@ -287,6 +322,6 @@ class Decoder:
             return torch.cat([tok[:, None], rest], 1)
         out = [tok]
         for _ in range(new_tokens - 1):
-            tok = _ffi.argmax_lastdim(self.decode_step(tok))
+            tok = self.next_token(self.decode_step(tok, local_logits=True))
             out.append(tok)
         return torch.stack(out, 1)

@@ -144,14 +144,18 @@ def test_hf_llama_through_the_backend_matches_eager(cuda, gates, monkeypatch):
     monkeypatch.setattr(inductor, "lower_graph", spy)
     with torch.no_grad():
         want = model32(ids).logits
+        eager = model(ids).logits                       # the same bf16 weights through PyTorch's own kernels
         n0 = _ffi.launch_count()
         got = torch.compile(model, backend=inductor.backend)(ids).logits
     assert _ffi.launch_count() - n0 >= layers * 8
     assert seen["kuiops.sdpa.default"] >= layers, seen
     assert seen["kuiops.mm.default"] + seen["kuiops.addmm.default"] >= 4 * layers, seen
     assert inductor.call_stats["sdpa"][0] >= layers and inductor.call_stats["mm"][0] >= 4 * layers
-    err = ((got.float() - want).abs().max() / want.abs().max()).item()
-    assert err <= 2e-2, f"max relative error {err:.3e} against the fp32 model"
+    rel = lambda a, b: ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
+    # within the bf16 bar of eager on the same weights; against the fp32 model no worse than eager bf16 itself
+    # (a whole model's rounding adds up over its layers: eager bf16 is about 2.5e-2 away from fp32 here)
+    assert rel(got, eager) <= 2e-2, f"max relative error {rel(got, eager):.3e} against eager bf16"
+    assert rel(got, want) <= max(2e-2, 1.25 * rel(eager, want)), (rel(got, want), rel(eager, want))
     assert _ffi.tc_error() == 0
 
 

@@ -237,7 +237,7 @@ def test_cumsum_over_the_last_axis(cuda, gates, shape):
     assert torch.equal(got.cpu(), mask.cumsum(-1))
 
 
-@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (5, 4097), (300, 8193), (2, 70001), (64, 128256)])
+@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (5, 4097), (300, 8193), (2, 70001), (3, 300001), (64, 128256)])
 @pytest.mark.parametrize("descending", [False, True])
 def test_sort_over_the_last_axis_is_the_stable_sort(cuda, gates, shape, descending):
     """Radix sort of fp32 rows: many exact ties (bf16-quantised values), NaN largest, -0 == +0, infinities;

@@ -52,7 +52,12 @@ def _tp_worker(rank, size, port, q):
     out2 = tp.decode_step(ref_tok)
     dist.all_reduce = real
     rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
-    ok_tp = rel(out, ref) < 3e-2 and rel(out2, ref2) < 3e-2 and n_calls == 2 * cfg.n_layers
+    # vocabulary-parallel greedy step: best (value, id) pairs exchanged instead of the logits; ties go to the lowest id
+    from kuipy import _ffi as _f
+    per = cfg.vocab // size
+    tok_tp = tp.next_token(out2[:, rank * per:(rank + 1) * per].contiguous())
+    ok_tok = torch.equal(tok_tp, _f.argmax_lastdim(out2))
+    ok_tp = rel(out, ref) < 3e-2 and rel(out2, ref2) < 3e-2 and n_calls == 2 * cfg.n_layers and ok_tok
     # the fused form: row-split GEMMs push their partials into both ranks' memory, the next norm sums
     # them; no NCCL call on that path, and with two ranks the sum rounds exactly as NCCL's does
     from kuipy import _ffi

@@ -70,6 +70,13 @@ KUIOPS_API const char* kuiops_strerror(int code);
  * device-side error word to *host_out (0 = no wait ever ran out; otherwise the code of the
  * wait that gave up) and optionally clears it.  Synchronises the device. */
 KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
+/* Self-timing of the tcgen05 GEMM: while `device_buffer` (>= 16 uint64 on the current device) is set,
+ * CTA 0 of every GEMM launched afterwards stores the global nanosecond timer at the stations of its
+ * critical path: [0] CTA start, [1] predecessor kernel complete, [2] first operand tiles landed,
+ * [3] last MMA issued, [4] accumulator complete, [5] split-K partial parked, [6] cluster met,
+ * [7] tile share reduced and stored, [8] cluster met again.  NULL switches it off (the default).
+ * No counterpart in the reference. */
+KUIOPS_API int kuiops_debug_gemm_trace(uint64_t* device_buffer);
 /* How long kuiops_rmsnorm_gather polls for a peer's arrival flag before it gives up, stores
  * error word 30 (see kuiops_debug_tc_error), sums whatever the receive slots hold and returns.
  * Nanoseconds; 0 restores the default of two seconds.  Returns the previous value.  A peer that

@@ -42,6 +42,7 @@ int gemm_simt(const GemmArgs& a, cudaStream_t st);
 bool gemm_tc_eligible(const GemmArgs& a);
 size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
 int gemm_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+extern std::atomic<unsigned long long*> g_gemm_trace;
 // Tuned-plan table of the tcgen05 kernel (see kuiops_gemm_tune_set).
 int gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int splits, int bn);
 void gemm_tune_clear();

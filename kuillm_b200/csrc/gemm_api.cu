@@ -26,6 +26,11 @@ uint64_t kuiops_debug_set_peer_wait_ns(uint64_t ns) {
   return g_peer_wait_ns.exchange(ns ? ns : kPeerWaitDefaultNs);
 }
 
+int kuiops_debug_gemm_trace(uint64_t* device_buffer) {
+  g_gemm_trace.store(reinterpret_cast<unsigned long long*>(device_buffer), std::memory_order_relaxed);
+  return KUIOPS_OK;
+}
+
 uint64_t kuiops_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* kuiops_strerror(int code) {

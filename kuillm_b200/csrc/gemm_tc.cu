@@ -54,6 +54,7 @@ struct TcParams {
   // "rope" epilogue (epi == 2, swapped placement, split K): the output rows are packed q | k | v heads
   // of 128; q and k heads get the rotary embedding of their row's position, k and v heads are also
   // appended to the caches
+  unsigned long long* trace;          // debug: CTA 0 stores %globaltimer at the stations of its critical path (kuiops_debug_gemm_trace)
   const long long* positions;
   float log2_theta;
   void* k_cache; void* v_cache;
@@ -62,11 +63,16 @@ struct TcParams {
 };
 
 __device__ unsigned int g_tc_error = 0;
+// Debug: device buffer of >= 16 uint64 that CTA 0 of every later tcgen05 GEMM stamps with %globaltimer.
+std::atomic<unsigned long long*> g_gemm_trace{nullptr};
 
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+__device__ __forceinline__ void trace_stamp(const unsigned long long* base, int slot) {
+  if (base != nullptr && blockIdx.x == 0) const_cast<unsigned long long*>(base)[slot] = global_ns();
 }
 // Wait on an mbarrier phase for at most ~2 s of wall time.
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity) {
@@ -166,8 +172,148 @@ __device__ __forceinline__ void store_rope(const TcParams& p, uint32_t lane_row,
   }
 }
 
+// Four consecutive output features n0 .. n0 + 3 of row m (swapped placement), finished: the plain /
+// bias / push epilogue with one 8-byte store per destination where alignment allows.
+template <typename TIN>
+__device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32_t n0, uint32_t m, const float (&acc)[4], uint64_t push_off) {
+  if (m >= p.M || n0 >= p.N) return;
+  const bool full = n0 + 4 <= p.N;
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = p.alpha * acc[i];
+  if (p.n_ranks) {
+    // same four elements of the (epoch & 1, my_rank) slot on every rank, this one included
+    const uint64_t off = push_off + (size_t(m) * p.N + n0) * sizeof(TIN);
+    if (full && (off & 7u) == 0) {
+      const uint2 w = make_uint2(pack2<TIN>(v[0], v[1]), pack2<TIN>(v[2], v[3]));
+#pragma unroll 1
+      for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<uint2*>(p.peer_base[r] + off) = w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n0 + i < p.N) {
+          const TIN val = ElemTraits<TIN>::from_f(v[i]);
+#pragma unroll 1
+          for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<TIN*>(p.peer_base[r] + off + i * sizeof(TIN)) = val;
+        }
+    }
+    return;
+  }
+  if (p.Cin) {
+    const TIN* cin = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin + size_t(m) * p.ldcin + n0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (n0 + i < p.N) v[i] += p.beta * ElemTraits<TIN>::to_f(cin[i]);
+  }
+  const size_t off = size_t(b) * p.stride_c + size_t(m) * p.ldc + n0;
+  if (p.out_f32) {
+    float* dst = static_cast<float*>(p.C) + off;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) if (n0 + i < p.N) dst[i] = v[i];
+    }
+  } else {
+    TIN* dst = static_cast<TIN*>(p.C) + off;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<TIN>(v[0], v[1]), pack2<TIN>(v[2], v[3]));
+    else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) if (n0 + i < p.N) dst[i] = ElemTraits<TIN>::from_f(v[i]);
+    }
+  }
+}
+
+// SwiGLU on four consecutive columns of the fused gate|up product (two (gate, up) pairs) of row m.
+template <typename TIN>
+__device__ __forceinline__ void store_swiglu_quad(const TcParams& p, uint32_t n0, uint32_t m, const float (&acc)[4]) {
+  if (m >= p.M) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (n0 + 2 * i + 1 < p.N) {
+      const float v = silu_mul(acc[2 * i], acc[2 * i + 1]);
+      const size_t off = size_t(m) * p.ldc + ((n0 >> 1) + i);
+      if (p.out_f32) static_cast<float*>(p.C)[off] = v;
+      else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
+    }
+  }
+}
+
+// Split-K reduction of one output tile whose SPLITS K-slices are parked, column-major fp32, in the
+// shared memory of the SPLITS CTAs of a cluster.  CTA `rank` finishes columns rank, rank + SPLITS, ...
+// A warp takes whole columns: lane L reads the four features 4 L .. 4 L + 3 of a column from every
+// slice with one 16-byte distributed-shared-memory load each (a quarter of the requests of a
+// scalar walk; the remote reads are what this phase waits for), sums them and runs the epilogue
+// on the four results.  The loads of a step go to SPLITS different CTAs, starting with the
+// reader's own (CTA r reads slice r, r + 1, ... cyclically), so that the readers do not all queue
+// at the same CTA; a column is summed in that cyclic order, which is fixed by the column alone
+// (its owner is column mod SPLITS): same plan, same bits.
+template <typename TIN, int SPLITS>
+__device__ __forceinline__ void reduce_tile(const TcParams& p, cg::cluster_group& cluster, float* red, uint32_t rank, uint32_t ncols,
+                                            uint32_t warp_in_group, uint32_t lane, uint32_t b, uint32_t tp, uint32_t col0, uint64_t push_off) {
+  constexpr int CW = SPLITS >= 5 ? 1 : (SPLITS >= 3 ? 2 : 4);      // columns a warp has in flight: CW * SPLITS <= 8 loads of 16 bytes
+  const float* peer[SPLITS];
+#pragma unroll
+  for (int s = 0; s < SPLITS; ++s) {
+    uint32_t src = rank + s;
+    if (src >= SPLITS) src -= SPLITS;
+    peer[s] = cluster.map_shared_rank(red, src);
+  }
+  const uint32_t nj = ncols > rank ? (ncols - rank + SPLITS - 1) / SPLITS : 0u;
+  const uint32_t n0 = tp * TBM + lane * 4;                          // first of this lane's four output features
+  for (uint32_t j0 = warp_in_group * CW; j0 < nj; j0 += 4 * CW) {
+    float4 v[CW][SPLITS];
+#pragma unroll
+    for (int j = 0; j < CW; ++j) {
+      const uint32_t c = rank + (j0 + j) * SPLITS;
+#pragma unroll
+      for (int s = 0; s < SPLITS; ++s)
+        v[j][s] = (j0 + j < nj) ? *reinterpret_cast<const float4*>(peer[s] + c * TBM + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float sum[CW][4], psum[CW][4];
+#pragma unroll
+    for (int j = 0; j < CW; ++j) {
+      sum[j][0] = v[j][0].x; sum[j][1] = v[j][0].y; sum[j][2] = v[j][0].z; sum[j][3] = v[j][0].w;
+#pragma unroll
+      for (int s = 1; s < SPLITS; ++s) { sum[j][0] += v[j][s].x; sum[j][1] += v[j][s].y; sum[j][2] += v[j][s].z; sum[j][3] += v[j][s].w; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) psum[j][i] = 0.f;
+    }
+    if (p.epi == 2) {
+      // the rotary partners (features n ^ 64 of the same head), summed the same way
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        const uint32_t c = rank + (j0 + j) * SPLITS;
+#pragma unroll
+        for (int s = 0; s < SPLITS; ++s)
+          v[j][s] = (j0 + j < nj) ? *reinterpret_cast<const float4*>(peer[s] + c * TBM + ((lane * 4) ^ 64u)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        psum[j][0] = v[j][0].x; psum[j][1] = v[j][0].y; psum[j][2] = v[j][0].z; psum[j][3] = v[j][0].w;
+#pragma unroll
+        for (int s = 1; s < SPLITS; ++s) { psum[j][0] += v[j][s].x; psum[j][1] += v[j][s].y; psum[j][2] += v[j][s].z; psum[j][3] += v[j][s].w; }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < CW; ++j) {
+      if (j0 + j < nj) {
+        const uint32_t m = col0 + rank + (j0 + j) * SPLITS;
+        if (p.epi == 2) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) store_rope<TIN>(p, n0 + i, m, sum[j][i], psum[j][i]);
+        } else if (p.epi == 1) {
+          store_swiglu_quad<TIN>(p, n0, m, sum[j]);
+        } else {
+          store_quad<TIN>(p, b, n0, m, sum[j], push_off);
+        }
+      }
+    }
+  }
+}
+
 template <typename TIN, int BN, int STAGES, int ACC_STAGES, bool P_MN, bool Q_MN>
-__global__ void __launch_bounds__(ACC_STAGES == 2 ? kTcThreadsWide : kTcThreads, 1)
+// (the weight-streaming variants are sized for three CTAs per SM: registers included)
+__global__ void __launch_bounds__(ACC_STAGES == 2 ? kTcThreadsWide : kTcThreads, ACC_STAGES == 2 ? 1 : 3)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant__ CUtensorMap tmapQ,
                const TcParams p) {
   constexpr uint32_t P_BYTES = TBM * TBK * 2;
@@ -216,6 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   uint32_t npre = 0;          // stages of the first unit already requested during set-up (thread 0 only)
 
   if (threadIdx.x == 0) {
+    trace_stamp(p.trace, 0);                                    // CTA started
     tc::prefetch_tmap(&tmapP);
     tc::prefetch_tmap(&tmapQ);
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
@@ -225,6 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     // tensor memory is being allocated and the CTA meets below.  (The operands may still be being
     // written by the previous kernel in the stream: wait for it first.)
     pdl_wait();
+    trace_stamp(p.trace, 1);                                    // the previous kernel in the stream has completed
     if (blockIdx.x < units) {
       const uint32_t u = blockIdx.x, split = u % p.splits, tile = u / p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
@@ -293,6 +441,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!bounded_wait(&full_bar[s], ph)) { atomicExch(p.err, 3u); ok = false; break; }
+          if (it == 0) trace_stamp(p.trace, 2);                 // first operand tiles have landed
           tc::tc_fence_after();
           const uint32_t pa = tc::smem_u32(smem + s * STAGE_BYTES);
           const uint32_t qa = pa + P_BYTES;
@@ -310,6 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
           tc::umma_commit(&empty_bar[s]);     // stage may be refilled once these MMAs have read it
         }
         if (ok) tc::umma_commit(&acc_full[as]);
+        if (acc_it == 0) trace_stamp(p.trace, 3);               // every MMA of the first unit issued
       }
     }
   } else {
@@ -333,6 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
         tile_coords(p, t, tp, tq);
       const uint32_t as = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1;
       if (!bounded_wait(&acc_full[as], aph)) { atomicExch(p.err, 4u); ok = false; break; }
+      if (acc_it == group && threadIdx.x == 64) trace_stamp(p.trace, 4);     // accumulator complete
       tc::tc_fence_after();
       const uint32_t taddr = tmem_base + as * BN + ((quarter * 32) << 16);
       const uint32_t row = tp * TBM + lane_in_tile;
@@ -458,38 +609,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     // the producer and issuer lanes ran their loops alone: bring every warp back together first,
     // the cluster barrier instructions are warp-collective
     __syncwarp();
+    if (threadIdx.x == 64) trace_stamp(p.trace, 5);              // partial parked in shared memory
     cluster.sync();
+    if (threadIdx.x == 64) trace_stamp(p.trace, 6);              // all slices of the tile are parked
     if (warp >= 2 && warp < 6 && blockIdx.x < units) {
       const uint32_t quarter = warp & 3, lane_in_tile = quarter * 32 + lane;
       const uint32_t tile = blockIdx.x / p.splits, rank = blockIdx.x % p.splits;
       const uint32_t b = tile / tiles_per_batch, t = tile % tiles_per_batch;
       uint32_t tp, tq;
         tile_coords(p, t, tp, tq);
-      const uint32_t row = tp * TBM + lane_in_tile, col0 = tq * BN;
+      const uint32_t col0 = tq * BN;
       const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
       float* red = reinterpret_cast<float*>(smem);
-      const float* peer[8];
-#pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) peer[s2] = cluster.map_shared_rank(red, s2 < int(p.splits) ? s2 : 0);
-      for (uint32_t c = rank; c < ncols; c += p.splits) {
-        float part[8];
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) part[s2] = s2 < int(p.splits) ? peer[s2][c * TBM + lane_in_tile] : 0.f;
-        float sum = part[0];
-#pragma unroll
-        for (int s2 = 1; s2 < 8; ++s2) sum += part[s2];
-        if (p.epi == 2) {
-          // the rotary partner (feature n ^ 64 of the same head) is summed the same way, slice by slice
-          float psum = peer[0][c * TBM + (lane_in_tile ^ 64u)];
-#pragma unroll
-          for (int s2 = 1; s2 < 8; ++s2) psum += s2 < int(p.splits) ? peer[s2][c * TBM + (lane_in_tile ^ 64u)] : 0.f;
-          store_rope<TIN>(p, row, col0 + c, sum, psum);
-        } else if (p.epi == 1) store_swiglu_swapped<TIN>(p, row, col0 + c, sum);
-        else store_elem<TIN>(p, b, row, col0 + c, sum, push_off);
+      (void)lane_in_tile;
+      switch (p.splits) {
+        case 2: reduce_tile<TIN, 2>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 3: reduce_tile<TIN, 3>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 4: reduce_tile<TIN, 4>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 5: reduce_tile<TIN, 5>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 6: reduce_tile<TIN, 6>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 7: reduce_tile<TIN, 7>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        default: reduce_tile<TIN, 8>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
       }
     }
     __syncwarp();
-    cluster.sync();          // nobody's shared memory goes away while a peer may still read it
+    if (threadIdx.x == 64) trace_stamp(p.trace, 7);              // this CTA's share of the tile reduced and stored
+    // Nobody's shared memory may go away while a peer still reads it: arrive now (this CTA's remote reads
+    // are done), wait at the very end, so that the teardown below overlaps the peers' last reads.
+    cluster.barrier_arrive();
   }
   // ------------------------------ teardown ------------------------------------------------
   tc::tc_fence_before();
@@ -513,6 +660,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     __syncwarp();                      // the allocator instructions want the whole warp converged
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.splits > 1) {
+    cg::this_cluster().barrier_wait();
+    if (threadIdx.x == 64) trace_stamp(p.trace, 8);
   }
 }
 
@@ -757,6 +908,7 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.C = a.C; p.ldc = a.ldc; p.stride_c = a.stride_c;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
+  p.trace = g_gemm_trace.load(std::memory_order_relaxed);
   if (a.epilogue == 2) {
     // needs the swapped placement with K split (the partner feature is read from the parked partials)
     if (!pl.swapped || pl.splits < 2 || a.batch != 1 || !a.rope || a.out_dtype != a.dtype) return KUIOPS_EUNSUPPORTED;

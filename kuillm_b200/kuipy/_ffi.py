@@ -52,6 +52,7 @@ SIGNATURES = {
     "kuiops_strerror": (ctypes.c_char_p, [c_int]),
     "kuiops_debug_tc_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
     "kuiops_debug_set_peer_wait_ns": (c_u64, [c_u64]),
+    "kuiops_debug_gemm_trace": (c_int, [c_void_p]),
     "kuiops_launch_count": (c_u64, []),
     "kuiops_set_pdl": (c_int, [c_int]),
     "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),

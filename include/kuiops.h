@@ -74,14 +74,16 @@ KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
  * CTA 0 of every GEMM launched afterwards stores the global nanosecond timer at the stations of its
  * critical path: [0] CTA start, [1] predecessor kernel complete, [2] first operand tiles landed,
  * [3] last MMA issued, [4] accumulator complete, [5] split-K partial parked, [6] cluster met,
- * [7] tile share reduced and stored, [8] cluster met again.  NULL switches it off (the default).
+ * [7] tile share reduced and stored (with the push epilogue: sent), [8] cluster met again.
+ * kuiops_rmsnorm_gather stamps [12] CTA start, [13] predecessor complete, [14] its cells of every rank
+ * seen, [15] rows stored.  NULL switches it off (the default).
  * No counterpart in the reference. */
 KUIOPS_API int kuiops_debug_gemm_trace(uint64_t* device_buffer);
-/* How long kuiops_rmsnorm_gather polls for a peer's arrival flag before it gives up, stores
+/* How long kuiops_rmsnorm_gather polls for a peer's cells before it gives up, stores
  * error word 30 (see kuiops_debug_tc_error), sums whatever the receive slots hold and returns.
  * Nanoseconds; 0 restores the default of two seconds.  Returns the previous value.  A peer that
  * died between steps therefore costs one limit per launch instead of a hang; tests use a
- * millisecond limit with a flag nobody raises.  No counterpart in the reference (it has no
+ * millisecond limit with cells nobody stamps.  No counterpart in the reference (it has no
  * multi-GPU path). */
 KUIOPS_API uint64_t kuiops_debug_set_peer_wait_ns(uint64_t ns);
 /* Programmatic dependent launch for the short kernels of a decode step (GEMM, attention,
@@ -168,19 +170,21 @@ KUIOPS_API int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t
                 uint32_t rows_per_seq, kuiops_stream_t stream);
 
 /* Tensor-parallel row-split GEMM fused with the first half of its all-reduce (decode shapes,
- * M <= 128, bf16 / f16): rank `rank` of `n_ranks` computes its partial product A x B (B as in
- * kuiops_gemm: [K,N], or [N,K] when trans_b) and the epilogue stores it, through peer pointers,
- * into the receive area of EVERY rank (its own included) instead of a local C:
- *     peer_base[r] + ((epoch & 1) * n_ranks + rank) * slot_bytes      M x N elements, row-major
- * When the last CTA has finished, flag word
- *     peer_base[r] + flags_offset + ((epoch & 1) * n_ranks + rank) * 4
- * of every rank is set to epoch + 1 (release, system scope).  `peer_base` is a HOST array of
+ * M <= 128, N a multiple of 4, bf16 / f16): rank `rank` of `n_ranks` computes its partial product
+ * A x B (B as in kuiops_gemm: [K,N], or [N,K] when trans_b) and the epilogue stores it, through
+ * peer pointers, into the receive area of EVERY rank (its own included) instead of a local C:
+ *     peer_base[r] + ((epoch & 1) * n_ranks + rank) * slot_bytes
+ * as M x N / 2 cells of 8 bytes, row-major: two consecutive elements of a row (4 bytes) and the
+ * 32-bit stamp epoch + 1.  A cell is valid for the consumer the moment it is seen with the
+ * expected stamp, so the exchange needs no fence, no flag word and no completion step: latency is
+ * one NVLink store.  slot_bytes >= 4 * M * N, a multiple of 16.  `peer_base` is a HOST array of
  * n_ranks device addresses: the same symmetric allocation as mapped into this process for each
- * rank (16-byte aligned; flags_offset >= 2 * n_ranks * slot_bytes; zero-filled once before the
- * first launch).  `epoch` is this rank's device word that kuiops_rmsnorm_gather advances after it
- * has consumed the partials; `ticket` a zeroed device word the kernel leaves zero.  Producer and
- * consumer alternate on the stream, so two halves of slots are enough: a rank cannot push epoch
- * e + 2 before it has consumed e + 1, which every peer pushed only after consuming e.
+ * rank (16-byte aligned, 2 * n_ranks * slot_bytes long, zero-filled once before the first
+ * launch).  `epoch` is this rank's device word that kuiops_rmsnorm_gather advances after it has
+ * consumed the partials.  Producer and consumer alternate on the stream, so two halves of slots
+ * are enough: a rank cannot push epoch e + 2 before it has consumed e + 1, which every peer pushed
+ * only after consuming e; a cell left over from epoch e carries the stamp e + 1 and is never taken
+ * for one of epoch e + 2.
  * The collective is plain peer stores over NVLink; no library call, no multicast.
  * No counterpart in the reference (it has no multi-GPU path); the single-rank form is
  * wrapper_mm.cu.j2:15-19. */
@@ -188,20 +192,20 @@ KUIOPS_API int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t
 KUIOPS_API int kuiops_gemm_push(int dtype, uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, const void* B, int64_t ldb, int trans_b,
                 uint32_t n_ranks, uint32_t rank, const uint64_t* peer_base,
-                uint64_t slot_bytes, uint64_t flags_offset,
-                const uint32_t* epoch, uint32_t* ticket, kuiops_stream_t stream);
+                uint64_t slot_bytes, const uint32_t* epoch, kuiops_stream_t stream);
 
 /* Second half of that all-reduce, fused with the residual add and the RMSNorm that follow a
- * row-split projection in a decoder layer: waits until the flags of all `n_ranks` ranks for the
- * current epoch have arrived in this rank's receive area (each wait bounded to about 2 s; on
- * expiry the error word read by kuiops_debug_tc_error is set to 30 and the kernel continues),
- * then   x = sum_r slot(epoch & 1, r)   (fp32, rank order, rounded to dtype),
+ * row-split projection in a decoder layer: every thread polls the cells it is about to sum in the
+ * slots of all `n_ranks` ranks until they carry the stamp of the current epoch (bounded: about
+ * 2 s unless lowered with kuiops_debug_set_peer_wait_ns; on expiry the error word read by
+ * kuiops_debug_tc_error is set to 30 and the kernel continues with what it has), then
+ *        x = sum_r slot(epoch & 1, r)   (fp32, rank order, rounded to dtype),
  *        residual_out = x + residual,   y = rmsnorm(residual_out) * weight,
  * and advances `epoch` by one.  `recv_base` is this rank's own receive area (peer_base[rank] of
- * kuiops_gemm_push), `ticket` a zeroed device word of its own.  bf16 / f16.
+ * kuiops_gemm_push), `ticket` a zeroed device word the kernel leaves zero.  bf16 / f16.
  * No counterpart in the reference. */
 KUIOPS_API int kuiops_rmsnorm_gather(int dtype, uint64_t m, uint32_t n, uint32_t n_ranks,
-                const void* recv_base, uint64_t slot_bytes, uint64_t flags_offset,
+                const void* recv_base, uint64_t slot_bytes,
                 uint32_t* epoch, uint32_t* ticket,
                 const void* residual, const void* weight, float eps,
                 void* y, void* residual_out, kuiops_stream_t stream);

@@ -1,6 +1,7 @@
 // Elementwise maps and the fused decoder-layer helpers built from them.
 // One launch per map, 16-byte accesses, grid sized in whole multiples of the SM count.
 #include "common.cuh"
+#include "gemm.cuh"
 #include "tc_ptx.cuh"
 
 namespace kuiops {
@@ -15,7 +16,7 @@ namespace kuiops {
 template <int OP>
 __device__ __forceinline__ float map_apply(float x, float y, float c1) {
   // y is the second operand (tensor element or the scalar c0); c1 is alpha of add/sub
-  if (OP == KUIOPS_MAP_SILU) return x / (1.f + expf(-x));
+  if (OP == KUIOPS_MAP_SILU) return __fdividef(x, 1.f + __expf(-x));     // special-function unit: exp2 and reciprocal, no division sequence
   if (OP == KUIOPS_MAP_NEG) return -x;
   if (OP == KUIOPS_MAP_RSQRT) return 1.f / sqrtf(x);
   if (OP == KUIOPS_MAP_COS) return cosf(x);
@@ -167,6 +168,13 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row_in_block = warp / WPR, wsub = warp % WPR;
   const uint32_t nvec = n / VN;
+  // the weights are the same for every row: requested once, up front, together with the first row
+  Vec16<T> wv[VECS];
+#pragma unroll
+  for (int i = 0; i < VECS; ++i) {
+    const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+    if (v < nvec) wv[i] = ld16(w + size_t(v) * VN);
+  }
   for (uint64_t base = uint64_t(blockIdx.x) * RPB; base < m; base += uint64_t(gridDim.x) * RPB) {
     const uint64_t row = base + row_in_block;
     const bool valid = row < m;
@@ -203,12 +211,12 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
     for (int i = 0; i < VECS; ++i) {
       const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
       if (valid && v < nvec) {
-        Vec16<T> wv = ld16(w + size_t(v) * VN), o;
+        Vec16<T> o;
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
           // torch's Llama RMSNorm rounds the normalised value to the element type before the weight multiply
           float nx = ElemTraits<T>::to_f(ElemTraits<T>::from_f(ElemTraits<T>::to_f(c[i].v[e]) * r));
-          o.v[e] = ElemTraits<T>::from_f(nx * ElemTraits<T>::to_f(wv.v[e]));
+          o.v[e] = ElemTraits<T>::from_f(nx * ElemTraits<T>::to_f(wv[i].v[e]));
         }
         st16(y + row * n + size_t(v) * VN, o);
       }
@@ -221,11 +229,15 @@ rmsnorm_kernel(uint64_t m, uint32_t n, const T* __restrict__ x, const T* residua
 // with the residual add and the normalisation that follow it.
 //   x[row] = round_T( sum over r of slot(epoch & 1, r)[row] )   (fp32 sum in rank order)
 //   resid_out[row] = x[row] + residual[row];  y[row] = rmsnorm(resid_out[row]) * w
-// Every CTA first waits (at most ~2 s, then the error word is set and the kernel carries on) until
-// flag (epoch & 1, r) of every rank r has reached epoch + 1.  The last CTA advances the epoch.
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// A slot holds 8-byte cells of two elements and a stamp; a cell belongs to the current exchange
+// when its stamp is epoch + 1.  Every thread polls exactly the cells it is about to sum (for at
+// most the wait limit, about 2 s unless lowered; then the error word is set and the kernel carries
+// on with what it has), so there is no separate flag, and data that arrive early are consumed
+// early.  The residual and the norm weights do not depend on the peers and are requested before
+// the polling starts.  The last CTA advances the epoch.
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ uint64_t elementwise_global_ns() {
@@ -237,35 +249,36 @@ __device__ __forceinline__ uint64_t elementwise_global_ns() {
 template <typename T, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned char* recv_base, uint64_t slot_bytes,
-                      uint64_t flags_offset, unsigned int* epoch, unsigned int* ticket, unsigned int* err, uint64_t wait_ns,
-                      const T* residual, const T* __restrict__ w, float eps, T* __restrict__ y, T* residual_out) {
+                      unsigned int* epoch, unsigned int* ticket, unsigned int* err, uint64_t wait_ns,
+                      unsigned long long* trace, const T* residual, const T* __restrict__ w, float eps, T* __restrict__ y, T* residual_out) {
+  static_assert(sizeof(T) == 2, "cells hold two 16-bit elements");
+  if (trace && blockIdx.x == 0 && threadIdx.x == 0) trace[12] = elementwise_global_ns();       // CTA started
   pdl_wait();
   pdl_trigger();
   constexpr int VN = Vec16<T>::N, VECS = 4, RPB = 8 / WPR;
   __shared__ float red[8];
   const unsigned int e = *reinterpret_cast<volatile unsigned int*>(epoch);
-  if (threadIdx.x == 0) {
-    // one thread polls (acquire, system scope); the barrier below hands what it acquired to the CTA
-    const unsigned int* flags = reinterpret_cast<const unsigned int*>(recv_base + flags_offset) + size_t(e & 1u) * n_ranks;
-    bool ok = true;
-    uint64_t t0 = 0;
-    for (uint32_t r = 0; r < n_ranks && ok; ++r) {
-      while (ld_acquire_sys(flags + r) < e + 1u) {
-        if (t0 == 0) t0 = elementwise_global_ns();
-        if (elementwise_global_ns() - t0 > wait_ns) { ok = false; break; }
-      }
-    }
-    if (!ok) atomicExch(err, 30u);
-  }
-  __syncthreads();
+  const unsigned int want = e + 1u;
+  if (trace && blockIdx.x == 0 && threadIdx.x == 0) trace[13] = elementwise_global_ns();       // predecessor complete
   const unsigned char* slots = recv_base + size_t(e & 1u) * n_ranks * slot_bytes;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row_in_block = warp / WPR, wsub = warp % WPR;
   const uint32_t nvec = n / VN;
+  bool timed_out = false;
+  uint64_t t0 = 0;
   for (uint64_t base = uint64_t(blockIdx.x) * RPB; base < m; base += uint64_t(gridDim.x) * RPB) {
     const uint64_t row = base + row_in_block;
     const bool valid = row < m;
-    Vec16<T> c[VECS];
+    Vec16<T> c[VECS], res[VECS], wv[VECS];
+    // what does not come from the peers first: residual and weights
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) {
+      const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
+      if (valid && v < nvec) {
+        res[i] = ld16(residual + row * n + size_t(v) * VN);
+        wv[i] = ld16(w + size_t(v) * VN);
+      }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VECS; ++i) {
@@ -274,24 +287,43 @@ rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned c
         float acc[VN];
 #pragma unroll
         for (int k = 0; k < VN; ++k) acc[k] = 0.f;
-        for (uint32_t r = 0; r < n_ranks; ++r) {
-          // written by another GPU: read through L2, never from a stale L1 line
-          const int4 raw = __ldcg(reinterpret_cast<const int4*>(slots + r * slot_bytes + (row * n + size_t(v) * VN) * sizeof(T)));
-          const Vec16<T>& pv = *reinterpret_cast<const Vec16<T>*>(&raw);
+        // 8 elements = 4 cells = 32 bytes per rank, written by another GPU.  The requests for all ranks go
+        // out together (volatile reads); whatever does not carry the stamp yet is read again until it does.
+        const unsigned char* cell0 = slots + (row * n + size_t(v) * VN) * 4;
+        uint4 a[KUIOPS_MAX_PEERS], b[KUIOPS_MAX_PEERS];
 #pragma unroll
-          for (int k = 0; k < VN; ++k) acc[k] += ElemTraits<T>::to_f(pv.v[k]);
+        for (int r = 0; r < KUIOPS_MAX_PEERS; ++r) {
+          if (uint32_t(r) < n_ranks) { a[r] = ld_volatile_u4(cell0 + r * slot_bytes); b[r] = ld_volatile_u4(cell0 + r * slot_bytes + 16); }
         }
-        const Vec16<T> res = ld16(residual + row * n + size_t(v) * VN);
+#pragma unroll
+        for (int r = 0; r < KUIOPS_MAX_PEERS; ++r) {
+          if (uint32_t(r) < n_ranks) {
+            while ((a[r].y != want || a[r].w != want || b[r].y != want || b[r].w != want) && !timed_out) {
+              if (t0 == 0) t0 = elementwise_global_ns();
+              if (elementwise_global_ns() - t0 > wait_ns) { timed_out = true; break; }
+              a[r] = ld_volatile_u4(cell0 + r * slot_bytes); b[r] = ld_volatile_u4(cell0 + r * slot_bytes + 16);
+            }
+            const uint32_t words[4] = {a[r].x, a[r].z, b[r].x, b[r].z};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const T lo = *reinterpret_cast<const T*>(&words[q]);
+              const T hi = *(reinterpret_cast<const T*>(&words[q]) + 1);
+              acc[2 * q] += ElemTraits<T>::to_f(lo);
+              acc[2 * q + 1] += ElemTraits<T>::to_f(hi);
+            }
+          }
+        }
 #pragma unroll
         for (int k = 0; k < VN; ++k) {
           const float x = ElemTraits<T>::to_f(ElemTraits<T>::from_f(acc[k]));      // the all-reduce result, rounded as a stored tensor would be
-          c[i].v[k] = ElemTraits<T>::from_f(x + ElemTraits<T>::to_f(res.v[k]));
+          c[i].v[k] = ElemTraits<T>::from_f(x + ElemTraits<T>::to_f(res[i].v[k]));
         }
         st16(residual_out + row * n + size_t(v) * VN, c[i]);
 #pragma unroll
         for (int k = 0; k < VN; ++k) { float f = ElemTraits<T>::to_f(c[i].v[k]); ss += f * f; }
       }
     }
+    if (trace && blockIdx.x == 0 && threadIdx.x == 0) trace[14] = elementwise_global_ns();     // this thread's cells of every rank have arrived
     ss = warp_sum(ss);
     if (WPR > 1) {
       if (lane == 0) red[warp] = ss;
@@ -306,18 +338,20 @@ rmsnorm_gather_kernel(uint64_t m, uint32_t n, uint32_t n_ranks, const unsigned c
     for (int i = 0; i < VECS; ++i) {
       const uint32_t v = wsub * 32 + lane + i * (32 * WPR);
       if (valid && v < nvec) {
-        Vec16<T> wv = ld16(w + size_t(v) * VN), o;
+        Vec16<T> o;
 #pragma unroll
         for (int k = 0; k < VN; ++k) {
           float nx = ElemTraits<T>::to_f(ElemTraits<T>::from_f(ElemTraits<T>::to_f(c[i].v[k]) * rs));
-          o.v[k] = ElemTraits<T>::from_f(nx * ElemTraits<T>::to_f(wv.v[k]));
+          o.v[k] = ElemTraits<T>::from_f(nx * ElemTraits<T>::to_f(wv[i].v[k]));
         }
         st16(y + row * n + size_t(v) * VN, o);
       }
     }
   }
+  if (timed_out) atomicExch(err, 30u);
   // every CTA read the epoch before it got here; the last one moves it on for the next exchange
   __syncthreads();
+  if (trace && blockIdx.x == 0 && threadIdx.x == 0) trace[15] = elementwise_global_ns();       // rows summed, normalised, stored
   if (threadIdx.x == 0) {
     const unsigned int t = atomicAdd(ticket, 1u);
     if (t == gridDim.x - 1) {
@@ -343,7 +377,7 @@ swiglu_kernel(uint64_t m, uint32_t n, const T* __restrict__ gu, T* __restrict__ 
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
       float gf = ElemTraits<T>::to_f(g.v[e]);
-      float s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(gf / (1.f + expf(-gf))));   // silu rounded as eager does
+      float s = ElemTraits<T>::to_f(ElemTraits<T>::from_f(__fdividef(gf, 1.f + __expf(-gf))));   // silu rounded as eager does
       o.v[e] = ElemTraits<T>::from_f(s * ElemTraits<T>::to_f(u.v[e]));
     }
     st16(y + row * n + v * VN, o);
@@ -546,14 +580,13 @@ static int rmsnorm_launch(uint64_t m, uint32_t n, const void* x, const void* res
 }
 
 template <typename T>
-static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const void* base, uint64_t slot_bytes, uint64_t flags_offset,
+static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const void* base, uint64_t slot_bytes,
                                  uint32_t* epoch, uint32_t* ticket, const void* res, const void* w, float eps, void* y,
                                  void* res_out, cudaStream_t st) {
   constexpr int VN = Vec16<T>::N;
   if (m == 0 || n == 0 || !base || !epoch || !ticket || !res || !w || !y || !res_out) return KUIOPS_EINVAL;
   if (n_ranks < 2 || n_ranks > KUIOPS_MAX_PEERS) return KUIOPS_EINVAL;
-  if (slot_bytes < m * n * sizeof(T) || (slot_bytes & 15u) || (flags_offset & 3u) || flags_offset < 2ull * n_ranks * slot_bytes)
-    return KUIOPS_EINVAL;
+  if (slot_bytes < m * n * 4 || (slot_bytes & 15u)) return KUIOPS_EINVAL;
   if (n % VN || !aligned16(base) || !aligned16(res) || !aligned16(w) || !aligned16(y) || !aligned16(res_out)) return KUIOPS_EUNSUPPORTED;
   unsigned int* err = tc_error_word_device();
   if (!err) return KUIOPS_ELAUNCH;
@@ -563,7 +596,10 @@ static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const
   auto Y = static_cast<T*>(y); auto RO = static_cast<T*>(res_out);
 #define KUIOPS_RG(WPRV, RPBV) \
   return launch_pdl(rmsnorm_gather_kernel<T, WPRV>, dim3(stream_grid(m, RPBV, 16)), dim3(256), 0, st, m, n, n_ranks, B, slot_bytes, \
-                    flags_offset, epoch, ticket, err, g_peer_wait_ns.load(std::memory_order_relaxed), R, W, eps, Y, RO)
+                    epoch, ticket, err, g_peer_wait_ns.load(std::memory_order_relaxed), \
+                    g_gemm_trace.load(std::memory_order_relaxed), R, W, eps, Y, RO)
+  // decode-sized steps are latency bound: spread a row over as many warps as it has vectors for, one row per CTA
+  if (m <= 128 && nvec > 128 && nvec <= 1024) KUIOPS_RG(8, 1);
   if (nvec <= 128) KUIOPS_RG(1, 8);
   if (nvec <= 256) KUIOPS_RG(2, 4);
   if (nvec <= 512) KUIOPS_RG(4, 2);
@@ -574,12 +610,12 @@ static int rmsnorm_gather_launch(uint64_t m, uint32_t n, uint32_t n_ranks, const
 
 extern "C" {
 int kuiops_rmsnorm_gather(int dtype, uint64_t m, uint32_t n, uint32_t n_ranks, const void* recv_base, uint64_t slot_bytes,
-                          uint64_t flags_offset, uint32_t* epoch, uint32_t* ticket, const void* residual, const void* weight,
+                          uint32_t* epoch, uint32_t* ticket, const void* residual, const void* weight,
                           float eps, void* y, void* residual_out, kuiops_stream_t s) {
   switch (dtype) {
-    case KUIOPS_BF16: return rmsnorm_gather_launch<__nv_bfloat16>(m, n, n_ranks, recv_base, slot_bytes, flags_offset, epoch, ticket,
+    case KUIOPS_BF16: return rmsnorm_gather_launch<__nv_bfloat16>(m, n, n_ranks, recv_base, slot_bytes, epoch, ticket,
                                                                   residual, weight, eps, y, residual_out, as_stream(s));
-    case KUIOPS_F16: return rmsnorm_gather_launch<__half>(m, n, n_ranks, recv_base, slot_bytes, flags_offset, epoch, ticket,
+    case KUIOPS_F16: return rmsnorm_gather_launch<__half>(m, n, n_ranks, recv_base, slot_bytes, epoch, ticket,
                                                           residual, weight, eps, y, residual_out, as_stream(s));
   }
   return KUIOPS_EUNSUPPORTED;

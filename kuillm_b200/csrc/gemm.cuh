@@ -8,9 +8,8 @@ namespace kuiops {
 struct GemmPush {
   uint32_t n_ranks, rank;
   uint64_t peer_base[KUIOPS_MAX_PEERS];
-  uint64_t slot_bytes, flags_offset;
+  uint64_t slot_bytes;
   const unsigned int* epoch;
-  unsigned int* ticket;
 };
 
 // Rotary embedding + KV-cache append fused into the packed QKV projection: see kuiops_gemm_rope_qkv.

@@ -134,23 +134,21 @@ int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32
 
 int kuiops_gemm_push(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, int trans_b, uint32_t n_ranks, uint32_t rank,
-                     const uint64_t* peer_base, uint64_t slot_bytes, uint64_t flags_offset,
-                     const uint32_t* epoch, uint32_t* ticket, kuiops_stream_t stream) {
+                     const uint64_t* peer_base, uint64_t slot_bytes, const uint32_t* epoch, kuiops_stream_t stream) {
   if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
-  if (M == 0 || N == 0 || K == 0 || !A || !B || !peer_base || !epoch || !ticket) return KUIOPS_EINVAL;
+  if (M == 0 || N == 0 || K == 0 || !A || !B || !peer_base || !epoch) return KUIOPS_EINVAL;
   if (n_ranks < 2 || n_ranks > KUIOPS_MAX_PEERS || rank >= n_ranks) return KUIOPS_EINVAL;
-  if (M > 128) return KUIOPS_EUNSUPPORTED;                     // the weight-streaming placement only
+  if (M > 128 || N % 4) return KUIOPS_EUNSUPPORTED;            // the weight-streaming placement only; cells hold element pairs
   if (lda < int64_t(K) || ldb < int64_t(trans_b ? K : N)) return KUIOPS_EINVAL;
-  if (slot_bytes < uint64_t(M) * N * 2 || (slot_bytes & 15u) || (flags_offset & 3u)) return KUIOPS_EINVAL;
-  if (flags_offset < 2ull * n_ranks * slot_bytes) return KUIOPS_EINVAL;   // flags lie behind both halves of the slots
+  if (slot_bytes < uint64_t(M) * N * 4 || (slot_bytes & 15u)) return KUIOPS_EINVAL;   // 4 bytes per element: value + half a stamp
   GemmPush push = {};
   push.n_ranks = n_ranks; push.rank = rank;
   for (uint32_t r = 0; r < n_ranks; ++r) {
     if (!peer_base[r] || (peer_base[r] & 15u)) return KUIOPS_EINVAL;
     push.peer_base[r] = peer_base[r];
   }
-  push.slot_bytes = slot_bytes; push.flags_offset = flags_offset;
-  push.epoch = epoch; push.ticket = ticket;
+  push.slot_bytes = slot_bytes;
+  push.epoch = epoch;
   GemmArgs a = {};
   a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = N; a.K = K;
   a.A = A; a.lda = lda; a.B = B; a.ldb = ldb; a.trans_b = trans_b ? 1 : 0;

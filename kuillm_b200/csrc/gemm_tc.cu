@@ -45,12 +45,13 @@ struct TcParams {
   void* C; int64_t ldc, stride_c;
   unsigned int* err;
   // "push" epilogue (tensor parallel, swapped placement only): the result is a partial sum that
-  // goes into slot (epoch & 1, my_rank) of every rank's receive area instead of C
+  // goes into slot (epoch & 1, my_rank) of every rank's receive area instead of C, as 8-byte cells of
+  // two elements and the stamp epoch + 1: a cell is valid the moment it is seen with the right
+  // stamp, so the exchange needs no fence, no flag and no last-CTA election
   uint32_t n_ranks, my_rank;          // n_ranks == 0: ordinary epilogue
   uint64_t peer_base[KUIOPS_MAX_PEERS];
-  uint64_t slot_bytes, flags_offset;
+  uint64_t slot_bytes;
   const unsigned int* epoch;          // device word, advanced by the consumer of the partials
-  unsigned int* ticket;               // device word, zero between launches
   // "rope" epilogue (epi == 2, swapped placement, split K): the output rows are packed q | k | v heads
   // of 128; q and k heads get the rotary embedding of their row's position, k and v heads are also
   // appended to the caches
@@ -99,20 +100,11 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, uint32_t t, uint3
 }
 
 template <typename TIN>
-__device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32_t lane_row, uint32_t col, float acc,
-                                           uint64_t push_off = 0) {
+__device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32_t lane_row, uint32_t col, float acc) {
   const uint32_t m = p.swapped ? col : lane_row;
   const uint32_t n = p.swapped ? lane_row : col;
   if (m >= p.M || n >= p.N) return;
   float v = p.alpha * acc;
-  if (p.n_ranks) {
-    // same element of the (epoch & 1, my_rank) slot on every rank, this one included
-    const uint64_t off = push_off + (size_t(m) * p.N + n) * sizeof(TIN);
-    const TIN val = ElemTraits<TIN>::from_f(v);
-#pragma unroll 1
-    for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<TIN*>(p.peer_base[r] + off) = val;
-    return;
-  }
   if (p.Cin) {
     const TIN* cin = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin;
     v += p.beta * ElemTraits<TIN>::to_f(cin[size_t(m) * p.ldcin + n]);
@@ -122,7 +114,7 @@ __device__ __forceinline__ void store_elem(const TcParams& p, uint32_t b, uint32
   else static_cast<TIN*>(p.C)[off] = ElemTraits<TIN>::from_f(v);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 // SwiGLU epilogue, swapped placement: lane n holds column n of the fused gate|up product for row
 // `col`; gate and up of one output sit in neighbouring lanes (rows 2j, 2j+1 of the weight).
@@ -175,28 +167,20 @@ __device__ __forceinline__ void store_rope(const TcParams& p, uint32_t lane_row,
 // Four consecutive output features n0 .. n0 + 3 of row m (swapped placement), finished: the plain /
 // bias / push epilogue with one 8-byte store per destination where alignment allows.
 template <typename TIN>
-__device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32_t n0, uint32_t m, const float (&acc)[4], uint64_t push_off) {
+__device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32_t n0, uint32_t m, const float (&acc)[4], uint64_t push_off,
+                                           uint32_t push_stamp) {
   if (m >= p.M || n0 >= p.N) return;
   const bool full = n0 + 4 <= p.N;
   float v[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) v[i] = p.alpha * acc[i];
   if (p.n_ranks) {
-    // same four elements of the (epoch & 1, my_rank) slot on every rank, this one included
-    const uint64_t off = push_off + (size_t(m) * p.N + n0) * sizeof(TIN);
-    if (full && (off & 7u) == 0) {
-      const uint2 w = make_uint2(pack2<TIN>(v[0], v[1]), pack2<TIN>(v[2], v[3]));
+    // the same two cells of the (epoch & 1, my_rank) slot on every rank, this one included: 16 bytes per
+    // destination, each 8-byte half carrying two elements and the stamp (N is a multiple of 4 here)
+    const uint64_t off = push_off + (size_t(m) * p.N + n0) * 4;
+    const uint4 w = make_uint4(pack2<TIN>(v[0], v[1]), push_stamp, pack2<TIN>(v[2], v[3]), push_stamp);
 #pragma unroll 1
-      for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<uint2*>(p.peer_base[r] + off) = w;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (n0 + i < p.N) {
-          const TIN val = ElemTraits<TIN>::from_f(v[i]);
-#pragma unroll 1
-          for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<TIN*>(p.peer_base[r] + off + i * sizeof(TIN)) = val;
-        }
-    }
+    for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<uint4*>(p.peer_base[r] + off) = w;
     return;
   }
   if (p.Cin) {
@@ -249,7 +233,8 @@ __device__ __forceinline__ void store_swiglu_quad(const TcParams& p, uint32_t n0
 // (its owner is column mod SPLITS): same plan, same bits.
 template <typename TIN, int SPLITS>
 __device__ __forceinline__ void reduce_tile(const TcParams& p, cg::cluster_group& cluster, float* red, uint32_t rank, uint32_t ncols,
-                                            uint32_t warp_in_group, uint32_t lane, uint32_t b, uint32_t tp, uint32_t col0, uint64_t push_off) {
+                                            uint32_t warp_in_group, uint32_t lane, uint32_t b, uint32_t tp, uint32_t col0, uint64_t push_off,
+                                            uint32_t push_stamp) {
   constexpr int CW = SPLITS >= 5 ? 1 : (SPLITS >= 3 ? 2 : 4);      // columns a warp has in flight: CW * SPLITS <= 8 loads of 16 bytes
   const float* peer[SPLITS];
 #pragma unroll
@@ -304,7 +289,7 @@ __device__ __forceinline__ void reduce_tile(const TcParams& p, cg::cluster_group
         } else if (p.epi == 1) {
           store_swiglu_quad<TIN>(p, n0, m, sum[j]);
         } else {
-          store_quad<TIN>(p, b, n0, m, sum[j], push_off);
+          store_quad<TIN>(p, b, n0, m, sum[j], push_off, push_stamp);
         }
       }
     }
@@ -491,7 +476,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       // columns beyond the Q extent hold zeros (TMA fill) and are never stored
       const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
       float v[16];
-      if (p.splits == 1) {
+      if (p.splits == 1 && p.n_ranks == 0) {
         uint32_t c = 0;
         if (ACC_STAGES == 2 && p.epi == 0 && c_vec && (!p.Cin || (p.ldcin == 0 && cin_vec))) {
           // 64 columns at a time: a thread owns one row of the accumulator, so direct stores would
@@ -580,14 +565,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
             st16(dst + 8, o1);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j], push_off);
+            for (int j = 0; j < 16; ++j) store_elem<TIN>(p, b, row, col0 + c + j, v[j]);
           }
         }
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&acc_empty[as]);
       } else {
-        // split-K (one unit per CTA): park the fp32 partial in this CTA's shared memory, column-major.
+        // split-K, or the push epilogue (one unit per CTA): park the fp32 partial in this CTA's shared memory, column-major.
         // The pipeline buffers are free: every MMA that read them has completed.
         float* red = reinterpret_cast<float*>(smem);
         for (uint32_t c = 0; c < ncols; c += 16) {
@@ -604,7 +589,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   // The CTAs of a cluster hold the K-slices of one output tile.  After a cluster barrier each CTA
   // sums a share of the tile's columns over all slices, reading its peers' partials through
   // distributed shared memory in slice order (deterministic), and runs the epilogue on them.
-  if (p.splits > 1) {
+  const bool parked = p.splits > 1 || p.n_ranks != 0;
+  if (parked) {
     cg::cluster_group cluster = cg::this_cluster();
     // the producer and issuer lanes ran their loops alone: bring every warp back together first,
     // the cluster barrier instructions are warp-collective
@@ -623,13 +609,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       float* red = reinterpret_cast<float*>(smem);
       (void)lane_in_tile;
       switch (p.splits) {
-        case 2: reduce_tile<TIN, 2>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        case 3: reduce_tile<TIN, 3>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        case 4: reduce_tile<TIN, 4>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        case 5: reduce_tile<TIN, 5>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        case 6: reduce_tile<TIN, 6>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        case 7: reduce_tile<TIN, 7>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
-        default: reduce_tile<TIN, 8>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off); break;
+        case 1: reduce_tile<TIN, 1>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 2: reduce_tile<TIN, 2>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 3: reduce_tile<TIN, 3>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 4: reduce_tile<TIN, 4>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 5: reduce_tile<TIN, 5>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 6: reduce_tile<TIN, 6>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 7: reduce_tile<TIN, 7>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        default: reduce_tile<TIN, 8>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
       }
     }
     __syncwarp();
@@ -641,27 +628,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   // ------------------------------ teardown ------------------------------------------------
   tc::tc_fence_before();
   __syncthreads();
-  if (p.n_ranks && threadIdx.x == 0) {
-    // All threads of the CTA have issued their pushes (the barrier above); one cumulative
-    // system-scope fence by this thread orders them before the CTA's ticket.  The CTA that draws
-    // the last ticket publishes the epoch to every rank (flag (epoch & 1, my_rank) = epoch + 1)
-    // after a fence that orders everything it has observed before the flags.
-    __threadfence_system();
-    const unsigned int t = atomicAdd(p.ticket, 1u);
-    if (t == gridDim.x - 1) {
-      atomicExch(p.ticket, 0u);
-      __threadfence_system();
-      const uint64_t foff = p.flags_offset + (uint64_t(push_epoch & 1u) * p.n_ranks + p.my_rank) * sizeof(unsigned int);
-      for (uint32_t r = 0; r < p.n_ranks; ++r)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_base[r] + foff), "r"(push_epoch + 1u) : "memory");
-    }
-  }
   if (warp == 1) {
     __syncwarp();                      // the allocator instructions want the whole warp converged
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (p.splits > 1) {
+  if (parked) {
     cg::this_cluster().barrier_wait();
     if (threadIdx.x == 64) trace_stamp(p.trace, 8);
   }
@@ -917,11 +889,11 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
     p.hq = a.rope->hq; p.hk = a.rope->hk; p.rows_per_seq = a.rope->rows_per_seq ? a.rope->rows_per_seq : 1u;
   }
   if (a.push) {
-    if (!pl.swapped || a.epilogue != 0 || a.batch != 1) return KUIOPS_EUNSUPPORTED;
+    if (!pl.swapped || a.epilogue != 0 || a.batch != 1 || a.N % 4) return KUIOPS_EUNSUPPORTED;
     p.n_ranks = a.push->n_ranks; p.my_rank = a.push->rank;
     for (uint32_t r = 0; r < p.n_ranks; ++r) p.peer_base[r] = a.push->peer_base[r];
-    p.slot_bytes = a.push->slot_bytes; p.flags_offset = a.push->flags_offset;
-    p.epoch = a.push->epoch; p.ticket = a.push->ticket;
+    p.slot_bytes = a.push->slot_bytes;
+    p.epoch = a.push->epoch;
   }
   const uint64_t units = uint64_t(pl.tilesP) * pl.tilesQ * a.batch * pl.splits;
   if (units >= (1ull << 31)) return KUIOPS_EUNSUPPORTED;

@@ -69,8 +69,8 @@ SIGNATURES = {
     "kuiops_gemm_rope_qkv": (c_int, [c_int, c_u32, c_u32, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
                                      c_void_p, c_float, c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
     "kuiops_gemm_push": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_int, c_u32, c_u32, _P64,
-                                 c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
-    "kuiops_rmsnorm_gather": (c_int, [c_int, c_u64, c_u32, c_u32, c_void_p, c_u64, c_u64, c_void_p, c_void_p, c_void_p,
+                                 c_u64, c_void_p, c_void_p]),
+    "kuiops_rmsnorm_gather": (c_int, [c_int, c_u64, c_u32, c_u32, c_void_p, c_u64, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
     "kuiops_sdpa_workspace_bytes": (c_size_t, [c_int] + [c_u32] * 7),
     "kuiops_sdpa": (c_int, [c_int] + [c_u32] * 7 +
@@ -337,22 +337,22 @@ def gemm_push(A, B, *, trans_b, exchange):
     M, K = A.shape
     N = B.shape[0] if trans_b else B.shape[1]
     x = exchange
-    if M * N * A.element_size() > x.slot_bytes:
+    if M * N * 4 > x.slot_bytes:
         raise ValueError("kuiops: partial product larger than the exchange slots")
     _check(lib().kuiops_gemm_push(dtype_code(A.dtype), M, N, K, A.data_ptr(), max(A.stride(0), K), B.data_ptr(), B.stride(0),
-                                  1 if trans_b else 0, x.n_ranks, x.rank, x.peer_array, x.slot_bytes, x.flags_offset,
-                                  x.epoch.data_ptr(), x.ticket_push.data_ptr(), _stream()), "gemm_push")
+                                  1 if trans_b else 0, x.n_ranks, x.rank, x.peer_array, x.slot_bytes,
+                                  x.epoch.data_ptr(), _stream()), "gemm_push")
 
 
 def rmsnorm_gather(exchange, rows, weight, eps, residual, out=None):
     """residual += sum of the ranks' partials; returns rmsnorm(residual) * weight (the consumer of gemm_push)."""
     x = exchange
     n = weight.shape[0]
-    if residual.numel() != rows * n or not residual.is_contiguous() or rows * n * weight.element_size() > x.slot_bytes:
+    if residual.numel() != rows * n or not residual.is_contiguous() or rows * n * 4 > x.slot_bytes:
         raise ValueError("kuiops: rmsnorm_gather needs a contiguous [rows, n] residual that fits the exchange slots")
     if out is None:
         out = torch.empty((rows, n), dtype=weight.dtype, device=weight.device)
-    _check(lib().kuiops_rmsnorm_gather(dtype_code(weight.dtype), rows, n, x.n_ranks, x.local_base, x.slot_bytes, x.flags_offset,
+    _check(lib().kuiops_rmsnorm_gather(dtype_code(weight.dtype), rows, n, x.n_ranks, x.local_base, x.slot_bytes,
                                        x.epoch.data_ptr(), x.ticket_gather.data_ptr(), residual.data_ptr(), weight.data_ptr(),
                                        float(eps), out.data_ptr(), residual.data_ptr(), _stream()), "rmsnorm_gather")
     return out

@@ -3,10 +3,10 @@ row-split GEMM + all-reduce of the decode step (``kuiops_gemm_push`` / ``kuiops_
 
 Each rank owns one symmetric allocation laid out as
 
-    [2 halves][n_ranks sources][slot_bytes]   partial products, one slot per (epoch parity, source)
-    [2 halves][n_ranks sources] uint32        arrival flags (value: epoch + 1)
+    [2 halves][n_ranks sources][slot_bytes]   partial products, one slot per (epoch parity, source),
 
-and holds the device address of every rank's allocation (``torch.distributed._symmetric_memory``
+a slot being rows x width / 2 cells of 8 bytes: two 16-bit elements and the 32-bit stamp epoch + 1
+(a cell is valid as soon as it is seen with the expected stamp: no flags, no fences).  The rank holds the device address of every rank's allocation (``torch.distributed._symmetric_memory``
 does the handle exchange).  Pushes are plain stores through those peer addresses over NVLink; no
 multicast object is bound (it is switched off before the first rendezvous).
 """
@@ -26,10 +26,10 @@ class PeerExchange:
             group = dist.group.WORLD
         self.n_ranks = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        item = torch.empty((), dtype=dtype).element_size()
-        self.slot_bytes = (max_rows * width * item + 255) // 256 * 256
-        self.flags_offset = 2 * self.n_ranks * self.slot_bytes
-        total = self.flags_offset + 2 * self.n_ranks * 4 + 256
+        if torch.empty((), dtype=dtype).element_size() != 2:
+            raise ValueError("kuiops: the exchange cells hold 16-bit elements")
+        self.slot_bytes = (max_rows * width * 4 + 255) // 256 * 256
+        total = 2 * self.n_ranks * self.slot_bytes + 256
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self.buffer.zero_()
         torch.cuda.synchronize(device)
@@ -42,9 +42,8 @@ class PeerExchange:
             raise RuntimeError("kuiops: symmetric memory rendezvous returned unexpected addresses")
         self.peer_array = (ctypes.c_uint64 * self.n_ranks)(*ptrs)
         self.local_base = self.buffer.data_ptr()
-        # device words: the exchange counter and the two kernels' tickets
+        # device words: the exchange counter and the gathering kernel's ticket
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
-        self.ticket_push = torch.zeros(1, dtype=torch.int32, device=device)
         self.ticket_gather = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group)          # nobody pushes before every area is zeroed and mapped

@@ -69,27 +69,28 @@ def test_tensor_parallel_push_and_gather_contracts():
     import ctypes
     L = _ffi.lib()
     peers = (ctypes.c_uint64 * 2)(0x1000, 0x2000)
-    slot, flags = 32 * 4096 * 2, 2 * 2 * 32 * 4096 * 2
+    slot = 32 * 4096 * 4                                                 # 4 bytes per element: value + half a stamp
     ok = dict(M=32, N=4096, K=2048)
 
-    def push(dtype=_ffi.BF16, M=32, n_ranks=2, rank=0, peer_array=peers, slot_bytes=slot, flags_offset=flags, epoch=P, ticket=P):
-        return L.kuiops_gemm_push(dtype, M, ok["N"], ok["K"], P, ok["K"], P, ok["K"], 1, n_ranks, rank, peer_array,
-                                  slot_bytes, flags_offset, epoch, ticket, None)
+    def push(dtype=_ffi.BF16, M=32, N=4096, n_ranks=2, rank=0, peer_array=peers, slot_bytes=slot, epoch=P):
+        return L.kuiops_gemm_push(dtype, M, N, ok["K"], P, ok["K"], P, ok["K"], 1, n_ranks, rank, peer_array,
+                                  slot_bytes, epoch, None)
     assert push(dtype=_ffi.F32) == _ffi.EUNSUPPORTED                     # 16-bit operands only
     assert push(M=256) == _ffi.EUNSUPPORTED                              # decode-sized steps only
+    assert push(N=4098, slot_bytes=32 * 4098 * 4) == _ffi.EUNSUPPORTED   # cells hold element pairs, stored two at a time
     assert push(n_ranks=1) == _ffi.EINVAL and push(n_ranks=9) == _ffi.EINVAL and push(rank=2) == _ffi.EINVAL
-    assert push(slot_bytes=slot - 16) == _ffi.EINVAL                     # a slot must hold the M x N partial
-    assert push(flags_offset=flags - 4) == _ffi.EINVAL                   # flags lie behind both halves of the slots
+    assert push(slot_bytes=slot - 16) == _ffi.EINVAL                     # a slot must hold the M x N partial with its stamps
+    assert push(slot_bytes=32 * 4096 * 2) == _ffi.EINVAL                 # ... which is twice the bytes of the bare elements
     assert push(peer_array=(ctypes.c_uint64 * 2)(0x1000, 0)) == _ffi.EINVAL
     assert push(peer_array=(ctypes.c_uint64 * 2)(0x1000, 0x2008)) == _ffi.EINVAL     # 16-byte alignment
-    assert push(epoch=None) == _ffi.EINVAL and push(ticket=None) == _ffi.EINVAL
+    assert push(epoch=None) == _ffi.EINVAL
 
-    def gather(dtype=_ffi.BF16, m=32, n=4096, n_ranks=2, slot_bytes=slot, flags_offset=flags, residual=P):
-        return L.kuiops_rmsnorm_gather(dtype, m, n, n_ranks, P, slot_bytes, flags_offset, P, P, residual, P, 1e-5, P, P, None)
+    def gather(dtype=_ffi.BF16, m=32, n=4096, n_ranks=2, slot_bytes=slot, residual=P):
+        return L.kuiops_rmsnorm_gather(dtype, m, n, n_ranks, P, slot_bytes, P, P, residual, P, 1e-5, P, P, None)
     assert gather(dtype=_ffi.F32) == _ffi.EUNSUPPORTED
     assert gather(m=0) == _ffi.EINVAL and gather(n_ranks=1) == _ffi.EINVAL and gather(residual=None) == _ffi.EINVAL
-    assert gather(slot_bytes=slot - 16) == _ffi.EINVAL and gather(flags_offset=flags - 4) == _ffi.EINVAL
-    assert gather(n=4100, slot_bytes=32 * 4100 * 2, flags_offset=4 * 32 * 4100 * 2) == _ffi.EUNSUPPORTED   # rows must be whole 16-byte vectors
+    assert gather(slot_bytes=slot - 16) == _ffi.EINVAL
+    assert gather(n=4100, slot_bytes=32 * 4100 * 4) == _ffi.EUNSUPPORTED   # rows must be whole 16-byte vectors
 
 
 def test_qkv_projection_with_rope_epilogue_contracts():

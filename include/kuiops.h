@@ -169,6 +169,32 @@ KUIOPS_API int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t
                 const int64_t* positions, float theta, void* k_cache, void* v_cache, uint64_t cache_cap,
                 uint32_t rows_per_seq, kuiops_stream_t stream);
 
+/* RMSNorm folded into the two GEMMs around it (decode-sized steps, M <= 128, bf16 / f16, weights [N, K]).
+ * In a decoder layer  r' = r + A W^T ;  h = rmsnorm(r') * g ;  y = h V^T  costs three launches.  Folded:
+ *   kuiops_gemm_residual_ssq:  resid[m, :] += A[m, :] W^T in place (one rounding), and
+ *       ssq_out[t * M + m] = sum over the 128 features n of tile t of resid[m, n]^2 as stored
+ *       (t < ceil(N / 128); fp32; every entry is written, no zeroing needed);
+ *   kuiops_gemm_swiglu_rms / kuiops_gemm_rope_qkv_rms: kuiops_gemm_swiglu / kuiops_gemm_rope_qkv on the
+ *       UN-normalised rows A = resid, with row m of the product multiplied by
+ *       rsqrt(sum_t ssq[t * M + m] / K + eps) before the epilogue.  The norm weight g must have been
+ *       multiplied into the columns of V beforehand (V'[n, k] = V[n, k] * g[k]).
+ * The partials are summed per row in tile order, so the result is deterministic.  Against the
+ * three-launch form the normalised rows are no longer rounded to the element type before the
+ * product (results agree within the bf16 bar, not bit for bit).  KUIOPS_EUNSUPPORTED for shapes
+ * outside the weight-streaming placement: run the unfused calls.  The dispatcher sees this as
+ * add, pow, mean, add, rsqrt, mul, mul, mm (kuipy/kuiops.py:116-121,397-469 of the reference); no
+ * reference counterpart. */
+KUIOPS_API int kuiops_gemm_residual_ssq(int dtype, uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, const void* W, int64_t ldw,
+                void* resid, int64_t ldr, float* ssq_out, kuiops_stream_t stream);
+KUIOPS_API int kuiops_gemm_swiglu_rms(int dtype, uint32_t M, uint32_t N, uint32_t K,
+                const void* A, int64_t lda, const void* W, int64_t ldw, void* Y, int64_t ldy,
+                const float* ssq, uint32_t ssq_tiles, float eps, kuiops_stream_t stream);
+KUIOPS_API int kuiops_gemm_rope_qkv_rms(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32_t d, uint32_t K,
+                const void* A, int64_t lda, const void* W, int64_t ldw, void* qkv, int64_t ldq,
+                const int64_t* positions, float theta, void* k_cache, void* v_cache, uint64_t cache_cap,
+                uint32_t rows_per_seq, const float* ssq, uint32_t ssq_tiles, float eps, kuiops_stream_t stream);
+
 /* Tensor-parallel row-split GEMM fused with the first half of its all-reduce (decode shapes,
  * M <= 128, N a multiple of 4, bf16 / f16): rank `rank` of `n_ranks` computes its partial product
  * A x B (B as in kuiops_gemm: [K,N], or [N,K] when trans_b) and the epilogue stores it, through

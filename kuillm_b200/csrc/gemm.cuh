@@ -29,6 +29,10 @@ struct GemmArgs {
   const void* Cin; int64_t ldcin, stride_cin;
   float alpha, beta;
   void* C; int64_t ldc, stride_c;
+  float* ssq_out;            // producer half of a folded RMSNorm: per (128-feature tile, row) sums of squares of C as stored
+  const float* ssq_in;       // consumer half: those partials for the rows of A; row m of the product is scaled by rsqrt(sum / K + eps)
+  uint32_t ssq_tiles;
+  float ssq_eps;
   const GemmRope* rope;   // epilogue 2 only
   const GemmPush* push;   // non-null: partial sums go to every rank's receive area instead of C
   int epilogue;   // 0: C = alpha*acc + beta*Cin;  1: C[m, j] = silu(acc[m, 2j]) * acc[m, 2j+1] (gate/up rows interleaved in B);  2: rotary embedding + cache append (rope)

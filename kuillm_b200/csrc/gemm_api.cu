@@ -132,6 +132,60 @@ int kuiops_gemm_rope_qkv(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32
   return gemm_tc(a, nullptr, 0, as_stream(stream));
 }
 
+int kuiops_gemm_residual_ssq(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda, const void* W, int64_t ldw,
+                             void* resid, int64_t ldr, float* ssq_out, kuiops_stream_t stream) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || N == 0 || K == 0 || !A || !W || !resid || !ssq_out) return KUIOPS_EINVAL;
+  if (M > 128) return KUIOPS_EUNSUPPORTED;
+  if (lda < int64_t(K) || ldw < int64_t(K) || ldr < int64_t(N)) return KUIOPS_EINVAL;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = N; a.K = K;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
+  a.Cin = resid; a.ldcin = ldr; a.alpha = 1.f; a.beta = 1.f; a.C = resid; a.ldc = ldr; a.epilogue = 0;
+  a.ssq_out = ssq_out;
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  return gemm_tc(a, nullptr, 0, as_stream(stream));
+}
+
+int kuiops_gemm_swiglu_rms(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
+                           const void* W, int64_t ldw, void* Y, int64_t ldy, const float* ssq, uint32_t ssq_tiles, float eps,
+                           kuiops_stream_t stream) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || N == 0 || K == 0 || !A || !W || !Y || !ssq || ssq_tiles == 0 || !(eps >= 0.f)) return KUIOPS_EINVAL;
+  if (M > 128) return KUIOPS_EUNSUPPORTED;
+  if (lda < int64_t(K) || ldw < int64_t(K) || ldy < int64_t(N) || N > 0x7FFFFFFFu) return KUIOPS_EINVAL;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = 2 * N; a.K = K;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
+  a.alpha = 1.f; a.beta = 0.f; a.C = Y; a.ldc = ldy; a.epilogue = 1;
+  a.ssq_in = ssq; a.ssq_tiles = ssq_tiles; a.ssq_eps = eps;
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  return gemm_tc(a, nullptr, 0, as_stream(stream));
+}
+
+int kuiops_gemm_rope_qkv_rms(int dtype, uint32_t M, uint32_t hq, uint32_t hk, uint32_t d, uint32_t K,
+                             const void* A, int64_t lda, const void* W, int64_t ldw, void* qkv, int64_t ldq,
+                             const int64_t* positions, float theta, void* k_cache, void* v_cache, uint64_t cache_cap,
+                             uint32_t rows_per_seq, const float* ssq, uint32_t ssq_tiles, float eps, kuiops_stream_t stream) {
+  if (dtype != KUIOPS_BF16 && dtype != KUIOPS_F16) return KUIOPS_EUNSUPPORTED;
+  if (M == 0 || hq == 0 || K == 0 || !A || !W || !qkv || !positions || !(theta > 0.f)) return KUIOPS_EINVAL;
+  if (!ssq || ssq_tiles == 0 || !(eps >= 0.f)) return KUIOPS_EINVAL;
+  if ((k_cache == nullptr) != (v_cache == nullptr) || (k_cache && cache_cap == 0)) return KUIOPS_EINVAL;
+  if (d != 128 || M > 128) return KUIOPS_EUNSUPPORTED;
+  const uint64_t N = uint64_t(hq + 2 * hk) * d;
+  if (N > 0x7FFFFFFFull || lda < int64_t(K) || ldw < int64_t(K) || ldq < int64_t(N)) return KUIOPS_EINVAL;
+  GemmRope rope = {};
+  rope.positions = positions; rope.theta = theta; rope.k_cache = k_cache; rope.v_cache = v_cache;
+  rope.cache_cap = cache_cap; rope.hq = hq; rope.hk = hk; rope.rows_per_seq = rows_per_seq ? rows_per_seq : 1u;
+  GemmArgs a = {};
+  a.dtype = dtype; a.out_dtype = dtype; a.batch = 1; a.M = M; a.N = uint32_t(N); a.K = K;
+  a.A = A; a.lda = lda; a.B = W; a.ldb = ldw; a.trans_b = 1;
+  a.alpha = 1.f; a.beta = 0.f; a.C = qkv; a.ldc = ldq; a.epilogue = 2; a.rope = &rope;
+  a.ssq_in = ssq; a.ssq_tiles = ssq_tiles; a.ssq_eps = eps;
+  if (!gemm_tc_eligible(a)) return KUIOPS_EUNSUPPORTED;
+  return gemm_tc(a, nullptr, 0, as_stream(stream));
+}
+
 int kuiops_gemm_push(int dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, int trans_b, uint32_t n_ranks, uint32_t rank,
                      const uint64_t* peer_base, uint64_t slot_bytes, const uint32_t* epoch, kuiops_stream_t stream) {

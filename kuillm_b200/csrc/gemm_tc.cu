@@ -55,6 +55,13 @@ struct TcParams {
   // "rope" epilogue (epi == 2, swapped placement, split K): the output rows are packed q | k | v heads
   // of 128; q and k heads get the rotary embedding of their row's position, k and v heads are also
   // appended to the caches
+  // RMSNorm folded into a pair of GEMMs (swapped placement): a producer leaves, per 128-feature tile and
+  // row, the sum of squares of what it stored (ssq_out[tile * M + m]); a consumer whose A operand is
+  // that output multiplies row m of its product by rsqrt(sum over tiles / K + eps)
+  float* ssq_out;
+  const float* ssq_in;
+  uint32_t ssq_tiles;
+  float ssq_eps;
   unsigned long long* trace;          // debug: CTA 0 stores %globaltimer at the stations of its critical path (kuiops_debug_gemm_trace)
   const long long* positions;
   float log2_theta;
@@ -166,10 +173,11 @@ __device__ __forceinline__ void store_rope(const TcParams& p, uint32_t lane_row,
 
 // Four consecutive output features n0 .. n0 + 3 of row m (swapped placement), finished: the plain /
 // bias / push epilogue with one 8-byte store per destination where alignment allows.
+// Returns the sum of squares of the values as stored (rounded to the output type; 0 where nothing is stored).
 template <typename TIN>
-__device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32_t n0, uint32_t m, const float (&acc)[4], uint64_t push_off,
-                                           uint32_t push_stamp) {
-  if (m >= p.M || n0 >= p.N) return;
+__device__ __forceinline__ float store_quad(const TcParams& p, uint32_t b, uint32_t n0, uint32_t m, const float (&acc)[4], uint64_t push_off,
+                                            uint32_t push_stamp) {
+  if (m >= p.M || n0 >= p.N) return 0.f;
   const bool full = n0 + 4 <= p.N;
   float v[4];
 #pragma unroll
@@ -181,7 +189,7 @@ __device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32
     const uint4 w = make_uint4(pack2<TIN>(v[0], v[1]), push_stamp, pack2<TIN>(v[2], v[3]), push_stamp);
 #pragma unroll 1
     for (uint32_t r = 0; r < p.n_ranks; ++r) *reinterpret_cast<uint4*>(p.peer_base[r] + off) = w;
-    return;
+    return 0.f;
   }
   if (p.Cin) {
     const TIN* cin = static_cast<const TIN*>(p.Cin) + size_t(b) * p.stride_cin + size_t(m) * p.ldcin + n0;
@@ -190,8 +198,11 @@ __device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32
       if (n0 + i < p.N) v[i] += p.beta * ElemTraits<TIN>::to_f(cin[i]);
   }
   const size_t off = size_t(b) * p.stride_c + size_t(m) * p.ldc + n0;
+  float ss = 0.f;
   if (p.out_f32) {
     float* dst = static_cast<float*>(p.C) + off;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) if (n0 + i < p.N) ss += v[i] * v[i];
     if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
     else {
 #pragma unroll
@@ -199,12 +210,20 @@ __device__ __forceinline__ void store_quad(const TcParams& p, uint32_t b, uint32
     }
   } else {
     TIN* dst = static_cast<TIN*>(p.C) + off;
+    TIN r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[i] = ElemTraits<TIN>::from_f(v[i]);
+      const float f = ElemTraits<TIN>::to_f(r[i]);
+      if (n0 + i < p.N) ss += f * f;
+    }
     if (full && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<TIN>(v[0], v[1]), pack2<TIN>(v[2], v[3]));
     else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) if (n0 + i < p.N) dst[i] = ElemTraits<TIN>::from_f(v[i]);
+      for (int i = 0; i < 4; ++i) if (n0 + i < p.N) dst[i] = r[i];
     }
   }
+  return ss;
 }
 
 // SwiGLU on four consecutive columns of the fused gate|up product (two (gate, up) pairs) of row m.
@@ -234,7 +253,7 @@ __device__ __forceinline__ void store_swiglu_quad(const TcParams& p, uint32_t n0
 template <typename TIN, int SPLITS>
 __device__ __forceinline__ void reduce_tile(const TcParams& p, cg::cluster_group& cluster, float* red, uint32_t rank, uint32_t ncols,
                                             uint32_t warp_in_group, uint32_t lane, uint32_t b, uint32_t tp, uint32_t col0, uint64_t push_off,
-                                            uint32_t push_stamp) {
+                                            uint32_t push_stamp, const float* row_scale) {
   constexpr int CW = SPLITS >= 5 ? 1 : (SPLITS >= 3 ? 2 : 4);      // columns a warp has in flight: CW * SPLITS <= 8 loads of 16 bytes
   const float* peer[SPLITS];
 #pragma unroll
@@ -283,13 +302,24 @@ __device__ __forceinline__ void reduce_tile(const TcParams& p, cg::cluster_group
     for (int j = 0; j < CW; ++j) {
       if (j0 + j < nj) {
         const uint32_t m = col0 + rank + (j0 + j) * SPLITS;
+        if (row_scale != nullptr) {
+          // the folded RMSNorm of the A operand: one factor per output row
+          const float rs = row_scale[rank + (j0 + j) * SPLITS];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { sum[j][i] *= rs; psum[j][i] *= rs; }
+        }
         if (p.epi == 2) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) store_rope<TIN>(p, n0 + i, m, sum[j][i], psum[j][i]);
         } else if (p.epi == 1) {
           store_swiglu_quad<TIN>(p, n0, m, sum[j]);
         } else {
-          store_quad<TIN>(p, b, n0, m, sum[j], push_off, push_stamp);
+          float ss = store_quad<TIN>(p, b, n0, m, sum[j], push_off, push_stamp);
+          if (p.ssq_out != nullptr) {
+            // this warp holds all 128 features of tile tp for row m: their sum of squares, for the norm of the consumer
+            ss = warp_sum(ss);
+            if (lane == 0 && m < p.M) p.ssq_out[size_t(tp) * p.M + m] = ss;
+          }
         }
       }
     }
@@ -318,6 +348,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
   // normal placement only: 4 KB per epilogue warp (8 warps) to turn row-per-thread results into row-contiguous stores
   unsigned char* epi_stage = smem + STAGES * STAGE_BYTES + 256;
+  // swapped placement: per-row factors of a folded RMSNorm (at most 128 rows)
+  float* rs_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -451,6 +483,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
     // ------------------------------ epilogue ----------------------------------------------
     const uint32_t quarter = warp & 3;                    // TMEM lanes this warp may touch
     const uint32_t lane_in_tile = quarter * 32 + lane;
+    if (ACC_STAGES == 1 && p.ssq_in != nullptr) {
+      // folded RMSNorm: thread t adds up the tile partials of row t in tile order and keeps the row's factor;
+      // this runs while the main loop streams, the four epilogue warps meet on their own barrier
+      const uint32_t t = threadIdx.x - 64;
+      if (t < p.M) {
+        float ssq = 0.f;
+        for (uint32_t q = 0; q < p.ssq_tiles; ++q) ssq += p.ssq_in[size_t(q) * p.M + t];
+        rs_s[t] = rsqrtf(ssq / float(p.K) + p.ssq_eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     // facts that allow 16-byte stores of 8 consecutive outputs of a row (normal placement only)
     const bool c_vec = !p.swapped && !p.out_f32 && (p.ldc % 8 == 0) && (p.stride_c % 8 == 0) &&
                        ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
@@ -476,7 +519,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       // columns beyond the Q extent hold zeros (TMA fill) and are never stored
       const uint32_t ncols = min(uint32_t(BN), p.rowsQ > col0 ? p.rowsQ - col0 : 0u);
       float v[16];
-      if (p.splits == 1 && p.n_ranks == 0) {
+      if (p.splits == 1 && p.n_ranks == 0 && p.ssq_out == nullptr) {
         uint32_t c = 0;
         if (ACC_STAGES == 2 && p.epi == 0 && c_vec && (!p.Cin || (p.ldcin == 0 && cin_vec))) {
           // 64 columns at a time: a thread owns one row of the accumulator, so direct stores would
@@ -522,7 +565,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
           if (p.epi == 1) {
             if (p.swapped) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) store_swiglu_swapped<TIN>(p, row, col0 + c + j, v[j]);
+              for (int j = 0; j < 16; ++j)
+                store_swiglu_swapped<TIN>(p, row, col0 + c + j, (ACC_STAGES == 1 && p.ssq_in != nullptr) ? v[j] * rs_s[min(c + j, uint32_t(TBM - 1))] : v[j]);
             } else if (row < p.M) {
               // 16 consecutive columns = 8 (gate, up) pairs of one row -> 8 outputs
               const uint32_t oc = (col0 + c) >> 1;
@@ -589,7 +633,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
   // The CTAs of a cluster hold the K-slices of one output tile.  After a cluster barrier each CTA
   // sums a share of the tile's columns over all slices, reading its peers' partials through
   // distributed shared memory in slice order (deterministic), and runs the epilogue on them.
-  const bool parked = p.splits > 1 || p.n_ranks != 0;
+  const bool parked = p.splits > 1 || p.n_ranks != 0 || p.ssq_out != nullptr;
   if (parked) {
     cg::cluster_group cluster = cg::this_cluster();
     // the producer and issuer lanes ran their loops alone: bring every warp back together first,
@@ -609,14 +653,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmapP, const __grid_constant_
       float* red = reinterpret_cast<float*>(smem);
       (void)lane_in_tile;
       switch (p.splits) {
-        case 1: reduce_tile<TIN, 1>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 2: reduce_tile<TIN, 2>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 3: reduce_tile<TIN, 3>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 4: reduce_tile<TIN, 4>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 5: reduce_tile<TIN, 5>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 6: reduce_tile<TIN, 6>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        case 7: reduce_tile<TIN, 7>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
-        default: reduce_tile<TIN, 8>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u); break;
+        case 1: reduce_tile<TIN, 1>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 2: reduce_tile<TIN, 2>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 3: reduce_tile<TIN, 3>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 4: reduce_tile<TIN, 4>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 5: reduce_tile<TIN, 5>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 6: reduce_tile<TIN, 6>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        case 7: reduce_tile<TIN, 7>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
+        default: reduce_tile<TIN, 8>(p, cluster, red, rank, ncols, quarter, uint32_t(lane), b, tp, col0, push_off, push_epoch + 1u, p.ssq_in ? rs_s : nullptr); break;
       }
     }
     __syncwarp();
@@ -811,7 +855,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
   static_assert(size_t(BN) * TBM * sizeof(float) <= size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2),
                 "the split-K partial is parked in the pipeline buffers");
   // pipeline stages + alignment slack + barriers + (normal placement) the epilogue's staging blocks
-  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256 + (ACC_STAGES == 2 ? 32768 : 0);
+  constexpr size_t smem = size_t(STAGES) * (TBM * TBK * 2 + BN * TBK * 2) + 1024 + 256 + (ACC_STAGES == 2 ? 32768 : 512);
   static_assert(smem <= 227 * 1024, "shared memory budget of one CTA");
   auto kern = gemm_tc_kernel<TIN, BN, STAGES, ACC_STAGES, P_MN, Q_MN>;
   // the opt-in for large dynamic shared memory is per device: do it once per (kernel, device)
@@ -881,6 +925,11 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
   p.trace = g_gemm_trace.load(std::memory_order_relaxed);
+  if (a.ssq_out || a.ssq_in) {
+    // both halves of the folded norm live in the weight-streaming placement, one row factor per MMA column
+    if (!pl.swapped || a.batch != 1 || (a.ssq_out && a.epilogue != 0) || (a.ssq_in && a.ssq_tiles == 0)) return KUIOPS_EUNSUPPORTED;
+    p.ssq_out = a.ssq_out; p.ssq_in = a.ssq_in; p.ssq_tiles = a.ssq_tiles; p.ssq_eps = a.ssq_eps;
+  }
   if (a.epilogue == 2) {
     // needs the swapped placement with K split (the partner feature is read from the parked partials)
     if (!pl.swapped || pl.splits < 2 || a.batch != 1 || !a.rope || a.out_dtype != a.dtype) return KUIOPS_EUNSUPPORTED;

@@ -123,6 +123,23 @@ class Decoder:
         self.cap = 0
         self.length = 0
         self.exchange, self.exchange_rows = None, 0
+        # decode-sized steps on one GPU run the RMSNorms inside the GEMMs around them (kuiops_gemm_residual_ssq /
+        # *_rms): the norm weights live in the columns of the consuming projections
+        self.fold_norm = True
+        self.fold_norm_weights()
+
+    def fold_norm_weights(self):
+        """Multiply each layer's norm weights into the columns of the projection that consumes the
+        normalised rows (n1 into the packed QKV weight, n2 into gate|up) and leave unit norm weights
+        behind: the same function, in the form the folded-norm GEMMs need.  Idempotent; to be called
+        again after norm weights have been assigned (a checkpoint loader)."""
+        with torch.no_grad():
+            for L in self.layers:
+                for norm, weight in (("n1", "wqkv"), ("n2", "wgu")):
+                    g = L[norm]
+                    if not bool((g == 1).all()):
+                        L[weight] = (L[weight].float() * g.float()[None, :]).to(L[weight].dtype).contiguous()
+                        g.fill_(1.0)
 
     # ---- state ---------------------------------------------------------------------------
     def alloc_cache(self, batch, capacity):
@@ -161,8 +178,24 @@ class Decoder:
         # decode-sized steps of a tensor-parallel group: the row-split projections push their partial
         # products straight into every rank's receive area and the norm that follows sums them
         ex = self.exchange if (self.tp_size > 1 and self.exchange is not None and rows <= self.exchange_rows) else None
+        # one GPU, decode-sized step: both norms of a layer run inside the GEMMs around them (five launches per
+        # layer instead of seven).  ssq_a / ssq_b hold the per-tile sums of squares of the residual rows that the
+        # O and down projections leave for the projections that follow them.
+        fold = (self.fold_norm and self.tp_size == 1 and rows <= 128 and hd == 128 and cfg.dtype in (torch.bfloat16, torch.float16)
+                and cfg.d_model % 8 == 0)
+        if fold:
+            tiles = _ffi.ssq_tiles(cfg.d_model)
+            ssq_a = torch.empty((tiles, rows), dtype=torch.float32, device=self.device)
+            ssq_b = torch.empty((tiles, rows), dtype=torch.float32, device=self.device)
+        folded_resid = False                    # True once resid holds the running sum and ssq_a its squares
         for li, L in enumerate(self.layers):
-            if resid is None:
+            qkv = None
+            if folded_resid:
+                qkv = _ffi.gemm_rope_qkv_rms(resid, L["wqkv"], hq, hk, hd, positions, cfg.rope_theta, ssq_a, cfg.eps,
+                                             self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
+                if qkv is None:
+                    raise RuntimeError("kuiops: the folded-norm QKV projection refused a shape its producer accepted")
+            elif resid is None:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps)
                 resid = x
             elif ex is not None:
@@ -170,8 +203,9 @@ class Decoder:
             else:
                 h = _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)      # resid += x ; h = norm(resid)
             # decode-sized steps: projection, rotary embedding and cache append in one launch
-            qkv = _ffi.gemm_rope_qkv(h, L["wqkv"], hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li],
-                                     rows_per_seq=seq) if rows <= 128 and hd == 128 else None
+            if qkv is None:
+                qkv = _ffi.gemm_rope_qkv(h, L["wqkv"], hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li],
+                                         rows_per_seq=seq) if rows <= 128 and hd == 128 else None
             if qkv is None:
                 qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)              # [rows, (hq + 2 hk) * hd]
                 _ffi.rope_qkv(qkv, hq, hk, hd, positions, cfg.rope_theta, self.k_cache[li], self.v_cache[li], rows_per_seq=seq)
@@ -189,6 +223,15 @@ class Decoder:
                 k4 = self.k_cache[li][:, :, :end]
                 v4 = self.v_cache[li][:, :, :end]
             _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4, kv_lens=kv_lens)
+            if fold and (folded_resid or _ffi.gemm_residual_ssq(attn, L["wo"], resid, ssq_b)):
+                if folded_resid:
+                    _ffi.gemm_residual_ssq(attn, L["wo"], resid, ssq_b)          # resid += attn Wo^T, squares -> ssq_b
+                act = _ffi.gemm_swiglu_rms(resid, L["wgu"], ssq_b, cfg.eps)      # norm 2 inside the gate|up projection
+                if act is None or not _ffi.gemm_residual_ssq(act, L["wd"], resid, ssq_a):
+                    raise RuntimeError("kuiops: the folded-norm MLP refused a shape its attention half accepted")
+                folded_resid = True
+                continue
+            fold = False                         # the shape does not suit the folded kernels: plain sequence from here on
             if ex is not None:
                 _ffi.gemm_push(attn, L["wo"], trans_b=True, exchange=ex)
                 h2 = _ffi.rmsnorm_gather(ex, rows, L["n2"], cfg.eps, resid)
@@ -207,6 +250,10 @@ class Decoder:
             hf = _ffi.rmsnorm_gather(ex, rows, self.norm_f, cfg.eps, resid)
             if last is not None:
                 hf = _ffi.index(hf, 0, [last])
+        elif folded_resid:
+            if last is not None:
+                resid = _ffi.index(resid, 0, [last])                     # only the last position of each sequence feeds the vocabulary GEMM
+            hf = _ffi.rmsnorm(resid, self.norm_f, cfg.eps)               # resid already holds the last projection's sum
         else:
             if last is not None:
                 # only the last position of each sequence feeds the vocabulary GEMM

@@ -68,6 +68,11 @@ SIGNATURES = {
                                    c_void_p, c_size_t, c_void_p]),
     "kuiops_gemm_rope_qkv": (c_int, [c_int, c_u32, c_u32, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
                                      c_void_p, c_float, c_void_p, c_void_p, c_u64, c_u32, c_void_p]),
+    "kuiops_gemm_residual_ssq": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p]),
+    "kuiops_gemm_swiglu_rms": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
+                                       c_void_p, c_u32, c_float, c_void_p]),
+    "kuiops_gemm_rope_qkv_rms": (c_int, [c_int, c_u32, c_u32, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_i64,
+                                         c_void_p, c_float, c_void_p, c_void_p, c_u64, c_u32, c_void_p, c_u32, c_float, c_void_p]),
     "kuiops_gemm_push": (c_int, [c_int, c_u32, c_u32, c_u32, c_void_p, c_i64, c_void_p, c_i64, c_int, c_u32, c_u32, _P64,
                                  c_u64, c_void_p, c_void_p]),
     "kuiops_rmsnorm_gather": (c_int, [c_int, c_u64, c_u32, c_u32, c_void_p, c_u64, c_void_p, c_void_p, c_void_p,
@@ -328,6 +333,63 @@ def gemm_rope_qkv(A, W, hq, hk, d, positions, theta, k_cache=None, v_cache=None,
     if rc == EUNSUPPORTED:
         return None
     _check(rc, "gemm_rope_qkv")
+    return out
+
+
+def ssq_tiles(n):
+    """Number of 128-feature tiles a row of n features is cut into by the folded-norm GEMMs."""
+    return (int(n) + 127) // 128
+
+
+def gemm_residual_ssq(A, W, resid, ssq):
+    """resid += A @ W.T in place, and ssq[t, m] = sum of squares of tile t of row m as stored (the
+    producer half of a folded RMSNorm).  Returns False when the shape does not suit the kernel."""
+    M, K = A.shape
+    N = W.shape[0]
+    if (A.dtype not in (torch.bfloat16, torch.float16) or A.stride(1) != 1 or W.stride(1) != 1 or resid.stride(1) != 1
+            or ssq.dtype != torch.float32 or ssq.numel() < ssq_tiles(N) * M or not ssq.is_contiguous()):
+        return False
+    rc = lib().kuiops_gemm_residual_ssq(dtype_code(A.dtype), M, N, K, A.data_ptr(), max(A.stride(0), K), W.data_ptr(), W.stride(0),
+                                        resid.data_ptr(), max(resid.stride(0), N), ssq.data_ptr(), _stream())
+    if rc == EUNSUPPORTED:
+        return False
+    _check(rc, "gemm_residual_ssq")
+    return True
+
+
+def gemm_swiglu_rms(A, W_interleaved, ssq, eps, out=None):
+    """gemm_swiglu on un-normalised rows A, with row m scaled by rsqrt(sum_t ssq[t, m] / K + eps);
+    None when the shape does not suit the kernel."""
+    M, K = A.shape
+    N = W_interleaved.shape[0] // 2
+    if A.dtype not in (torch.bfloat16, torch.float16) or A.stride(1) != 1 or W_interleaved.stride(1) != 1:
+        return None
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    rc = lib().kuiops_gemm_swiglu_rms(dtype_code(A.dtype), M, N, K, A.data_ptr(), max(A.stride(0), K), W_interleaved.data_ptr(),
+                                      W_interleaved.stride(0), out.data_ptr(), max(out.stride(0), N), ssq.data_ptr(), ssq_tiles(K),
+                                      float(eps), _stream())
+    if rc == EUNSUPPORTED:
+        return None
+    _check(rc, "gemm_swiglu_rms")
+    return out
+
+
+def gemm_rope_qkv_rms(A, W, hq, hk, d, positions, theta, ssq, eps, k_cache=None, v_cache=None, rows_per_seq=1, out=None):
+    """gemm_rope_qkv on un-normalised rows A, with row m scaled by rsqrt(sum_t ssq[t, m] / K + eps)."""
+    M, K = A.shape
+    N = (hq + 2 * hk) * d
+    if A.dtype not in (torch.bfloat16, torch.float16) or A.stride(1) != 1 or W.stride(1) != 1 or W.shape[0] != N:
+        return None
+    if out is None:
+        out = torch.empty((M, N), dtype=A.dtype, device=A.device)
+    cap = k_cache.shape[2] if k_cache is not None else 0
+    rc = lib().kuiops_gemm_rope_qkv_rms(dtype_code(A.dtype), M, hq, hk, d, K, A.data_ptr(), max(A.stride(0), K), W.data_ptr(), W.stride(0),
+                                        out.data_ptr(), max(out.stride(0), N), positions.data_ptr(), float(theta), _ptr(k_cache),
+                                        _ptr(v_cache), cap, rows_per_seq, ssq.data_ptr(), ssq_tiles(K), float(eps), _stream())
+    if rc == EUNSUPPORTED:
+        return None
+    _check(rc, "gemm_rope_qkv_rms")
     return out
 
 

@@ -118,7 +118,7 @@ class Table:
 def bench_stream(T, iters):
     dev = "cuda"
     m, n = 64, 128256
-    if any(wanted(o, f"{m}x{n}") for o in ("softmax_f32", "topk_f32_k50", "argmax_f32", "cumsum_f32", "sort_f32")):
+    if any(wanted(o, f"{m}x{n}") for o in ("softmax_f32", "topk_f32_k50", "argmax_f32", "cumsum_f32", "sort_f32", "multinomial_f32")):
         nv = variants_for(m * n * 4)
         xs = [torch.randn(m, n, device=dev) * 3 for _ in range(nv)]
         y = torch.empty_like(xs[0])
@@ -128,8 +128,13 @@ def bench_stream(T, iters):
             T.add("topk_f32_k50", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.topk(ps[i], 50), nv, iters)), bytes_=m * n * 4 + m * 50 * 12)
             del ps
         T.add("argmax_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.argmax_lastdim(xs[i]), nv, iters)), bytes_=m * n * 4)
+        if wanted("multinomial_f32", f"{m}x{n}"):
+            pm = [_ffi.softmax(x) for x in xs]
+            T.add("multinomial_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.multinomial(pm[i], 1, seed=1, offset=4 * i), nv, iters)), bytes_=m * n * 4,
+                  note="one draw per row; one CTA per row")
+            del pm
         T.add("sort_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.sort_lastdim(xs[i]), nv, max(2, iters // 4))), bytes_=m * n * 16,
-              note="values + int64 permutation; one CTA per row")
+              note="values + int64 permutation; a cluster of 4 CTAs per row")
         T.add("cumsum_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.cumsum_lastdim(xs[i], out=y), nv, iters)), bytes_=2 * m * n * 4)
         del xs
     if wanted("reduce_max_f32", "8208384"):

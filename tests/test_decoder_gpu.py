@@ -135,3 +135,102 @@ def test_qkv_projection_with_rope_epilogue_equals_two_kernels(cuda, M, hq, hk, K
     small = _ffi.gemm_rope_qkv(A[:, :128].contiguous(), W[:, :128].contiguous(), hq, hk, d, pos, 5e5, kc2, vc2, rows_per_seq=1)
     assert small is None
 
+
+
+def _fold_config():
+    from kuillm_b200.decoder import DecoderConfig
+    # head dimension 128 and a model width of 512: the shapes the fused projections (rotary epilogue, folded norms) take
+    return DecoderConfig.tiny(d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=1024)
+
+
+def test_folded_norms_match_the_unfused_layer_sequence(cuda):
+    """Decode steps with both RMSNorms of a layer folded into the GEMMs around them (five launches per
+    layer) against the plain sequence norm -> projection on the same weights, with norm weights that
+    are not all ones (folded into the projection columns first): logits within the bf16 bar, the same
+    launch count difference the fold promises, and deterministic."""
+    from kuipy import _ffi
+    from kuillm_b200.decoder import Decoder
+    cfg = _fold_config()
+    g = torch.Generator().manual_seed(5)
+    decs = []
+    for fold in (True, False):
+        dec = Decoder(cfg, device="cuda", seed=3, init_std=0.05)
+        gw = torch.Generator().manual_seed(9)
+        for L in dec.layers:
+            L["n1"].copy_((1 + 0.2 * torch.randn(cfg.d_model, generator=gw)).to(cfg.dtype))
+            L["n2"].copy_((1 + 0.2 * torch.randn(cfg.d_model, generator=gw)).to(cfg.dtype))
+        if fold:
+            dec.fold_norm_weights()
+            assert all(bool((L["n1"] == 1).all()) and bool((L["n2"] == 1).all()) for L in dec.layers)
+        else:
+            dec.fold_norm = False                          # norm weights stay in the norm kernels, projections unchanged
+        dec.alloc_cache(4, 48)
+        decs.append(dec)
+    ids = torch.randint(0, cfg.vocab, (4, 20), generator=g).cuda()
+    # The judge of both forms is the same model in fp32 (PyTorch eager, the unfolded weights): the folded form
+    # may not be further from it than the plain sequence is (it skips one rounding; its folded weights round
+    # differently), and both stay within the bf16 bar of a whole model.
+    twin32 = _hf_twin(decs[1]).float()
+    lf, lu = decs[0].prefill(ids), decs[1].prefill(ids)
+    with torch.no_grad():
+        ref = twin32(ids, use_cache=True)
+    want = ref.logits[:, -1]
+    e_f, e_u = O.max_rel_err(to_np(lf), to_np(want)), O.max_rel_err(to_np(lu), to_np(want))
+    assert e_f <= max(2e-2, 1.25 * e_u), (e_f, e_u)
+    tok = want.argmax(-1)
+    past = ref.past_key_values
+    for _ in range(3):
+        n0 = _ffi.launch_count()
+        a = decs[0].decode_step(tok)
+        n_fold = _ffi.launch_count() - n0
+        n0 = _ffi.launch_count()
+        b = decs[1].decode_step(tok)
+        n_plain = _ffi.launch_count() - n0
+        with torch.no_grad():
+            ref = twin32(tok[:, None], past_key_values=past, use_cache=True)
+        want, past = ref.logits[:, -1], ref.past_key_values
+        e_f, e_u = O.max_rel_err(to_np(a), to_np(want)), O.max_rel_err(to_np(b), to_np(want))
+        assert e_f <= max(2e-2, 1.25 * e_u), (e_f, e_u)
+        assert O.rel_frobenius(to_np(a), to_np(want)) < 3e-2
+        assert n_plain - n_fold == 2 * cfg.n_layers - 1, (n_plain, n_fold)      # every norm but the first and the final one is gone
+        tok = want.argmax(-1)
+    # same step twice from the same state: same bits (the tile partials are summed in a fixed order)
+    first = decs[0].decode_step(tok)
+    decs[0].length -= 1                                    # rewind: the same position again rewrites the same cache row
+    assert torch.equal(first, decs[0].decode_step(tok))
+    assert _ffi.tc_error() == 0
+
+
+def test_folded_norm_gemm_pair_against_the_oracle(cuda):
+    """kuiops_gemm_residual_ssq + kuiops_gemm_swiglu_rms against the fp64 oracle of
+    r' = r + A W^T;  y = swiglu(rmsnorm(r') V^T): the residual as stored, the per-tile sums of squares,
+    and the activation within the bf16 bar; ragged row counts and a width that is not a whole tile."""
+    from kuipy import _ffi
+    g = torch.Generator().manual_seed(11)
+    for (M, K, N, F) in ((32, 1024, 512, 768), (5, 512, 320, 256), (128, 2048, 1024, 512)):
+        A = torch.randn(M, K, generator=g).bfloat16().cuda()
+        W = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16().cuda()
+        r = torch.randn(M, N, generator=g).bfloat16().cuda()
+        V = (torch.randn(2 * F, N, generator=g) / N ** 0.5).bfloat16().cuda()       # gate / up rows interleaved
+        resid = r.clone()
+        tiles = _ffi.ssq_tiles(N)
+        ssq = torch.full((tiles, M), float("nan"), device="cuda")
+        assert _ffi.gemm_residual_ssq(A, W, resid, ssq)
+        want_r = to_np(r).astype(np.float64) + to_np(A).astype(np.float64) @ to_np(W).astype(np.float64).T
+        assert O.max_rel_err(to_np(resid), want_r) <= 2e-2
+        stored = to_np(resid).astype(np.float64)
+        pad = np.zeros((M, tiles * 128))
+        pad[:, :N] = stored ** 2
+        want_ssq = pad.reshape(M, tiles, 128).sum(-1).T
+        np.testing.assert_allclose(to_np(ssq), want_ssq, rtol=1e-5)
+        act = _ffi.gemm_swiglu_rms(resid, V, ssq, 1e-5)
+        assert act is not None
+        h = stored / np.sqrt((stored ** 2).mean(-1, keepdims=True) + 1e-5)
+        gu = h @ to_np(V).astype(np.float64).T
+        gate, up = gu[:, 0::2], gu[:, 1::2]
+        want = gate / (1 + np.exp(-gate)) * up
+        assert O.max_rel_err(to_np(act), want) <= 2e-2
+        # the same through the plain kernels: norm, then the fused gate|up projection
+        plain = _ffi.gemm_swiglu(_ffi.rmsnorm(resid, torch.ones(N, device="cuda", dtype=torch.bfloat16), 1e-5), V)
+        assert O.max_rel_err(to_np(act), to_np(plain).astype(np.float64)) <= 2e-2
+    assert _ffi.tc_error() == 0

@@ -70,13 +70,15 @@ KUIOPS_API const char* kuiops_strerror(int code);
  * device-side error word to *host_out (0 = no wait ever ran out; otherwise the code of the
  * wait that gave up) and optionally clears it.  Synchronises the device. */
 KUIOPS_API int kuiops_debug_tc_error(unsigned int* host_out, int reset);
-/* Self-timing of the tcgen05 GEMM: while `device_buffer` (>= 16 uint64 on the current device) is set,
+/* Self-timing of the tcgen05 GEMM: while `device_buffer` (>= 32 uint64 on the current device) is set,
  * CTA 0 of every GEMM launched afterwards stores the global nanosecond timer at the stations of its
  * critical path: [0] CTA start, [1] predecessor kernel complete, [2] first operand tiles landed,
  * [3] last MMA issued, [4] accumulator complete, [5] split-K partial parked, [6] cluster met,
  * [7] tile share reduced and stored (with the push epilogue: sent), [8] cluster met again.
  * kuiops_rmsnorm_gather stamps [12] CTA start, [13] predecessor complete, [14] its cells of every rank
- * seen, [15] rows stored.  NULL switches it off (the default).
+ * seen, [15] rows stored.  The split-KV decode attention stamps [16] CTA start, [17] predecessor
+ * complete, [18] first scores ready, [19] all tiles accumulated, [20] record parked, [21] merged (by
+ * the last slice), [22] epilogue done.  NULL switches it off (the default).
  * No counterpart in the reference. */
 KUIOPS_API int kuiops_debug_gemm_trace(uint64_t* device_buffer);
 /* How long kuiops_rmsnorm_gather polls for a peer's cells before it gives up, stores
@@ -323,6 +325,11 @@ KUIOPS_API int kuiops_sdpa_varlen(int dtype, uint32_t n, uint32_t h, uint32_t h_
                 void* out, int64_t o_sn, int64_t o_sh, int64_t o_sl,
                 float* lse, const int64_t* kv_lens,
                 void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
+/* Debug: force the number of key slices of the split-KV decode kernel (0 restores its rule); the
+ * workspace query follows the override.  Used to sweep the split count of a shape.  No counterpart
+ * in the reference. */
+KUIOPS_API int kuiops_debug_sdpa_splits(int splits);
 
 /* Attention for callers that must not allocate device memory.
  * Has no counterpart in the reference.

@@ -41,5 +41,6 @@ bool sdpa_decode_tc_eligible(const SdpaArgs& a);
 size_t sdpa_decode_tc_workspace_bytes(const SdpaArgs& a);
 size_t sdpa_decode_tc_counter_bytes(const SdpaArgs& a);
 int sdpa_decode_tc(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
+void sdpa_decode_tc_force_splits(int splits);   // debug: 0 restores the rule
 
 }  // namespace kuiops

@@ -74,6 +74,11 @@ static int check_and_fill_ptrs(SdpaArgs& a,
 
 extern "C" {
 
+int kuiops_debug_sdpa_splits(int splits) {
+  sdpa_decode_tc_force_splits(splits);
+  return KUIOPS_OK;
+}
+
 size_t kuiops_sdpa_workspace_bytes(int dtype, uint32_t n, uint32_t h, uint32_t h_kv, uint32_t l, uint32_t s,
                                    uint32_t e, uint32_t ev) {
   SdpaArgs a = {};

@@ -12,6 +12,7 @@
 // Replaces the lane-per-key SIMT kernel for these shapes; the reference has no counterpart
 // (its only attention kernel is the naive biased one, kuiops/sdpa/Kuiops.Sdpa.fst.1).
 #include "sdpa.cuh"
+#include "gemm.cuh"
 #include "tc_ptx.cuh"
 #include <type_traits>
 
@@ -39,12 +40,16 @@ struct DecParams {
   float* lse;
   float* partials; int* counters;
   unsigned int* err;
+  unsigned long long* trace;          // debug: CTA 0 stamps the stations of its critical path (kuiops_debug_gemm_trace, slots 16..23)
 };
 
 __device__ __forceinline__ uint64_t dec_global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+__device__ __forceinline__ void dec_stamp(unsigned long long* t, int slot) {
+  if (t != nullptr && blockIdx.x == 0) t[slot] = dec_global_ns();
 }
 __device__ __forceinline__ bool dec_wait(uint64_t* bar, uint32_t parity) {
   if (tc::mbar_try_wait(bar, parity)) return true;
@@ -75,22 +80,26 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr uint32_t Q_HALF = SMALL ? 1024u : uint32_t(DBM) * 128u;   // bytes of one 64-column half of Q
   constexpr uint32_t Q_BYTES = 2 * Q_HALF;
   constexpr uint32_t P_BYTES = SMALL ? 1024u : D_P_BYTES;
+  // SMALL: two P buffers, so that the softmax of tile j + 1 does not wait for the P V product of tile j
+  // (with one buffer a tile costs a softmax plus an MMA round trip; the large form has no room for a second)
+  constexpr uint32_t PBUF = SMALL ? 2u : 1u;
   constexpr uint32_t ROW_GROUP_STRIDE = SMALL ? 0u : 1024u;      // SBO of the Q and P descriptors
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + Q_BYTES;                         // slot i: K at kv_s + i*32K, V right after K
   unsigned char* p_s = kv_s + NSLOT * (D_K_BYTES + D_V_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + PBUF * P_BYTES);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // NSLOT (room for 3)
   uint64_t* v_full = bars + 4;      // NSLOT
   uint64_t* kv_empty = bars + 7;    // NSLOT
   uint64_t* s_full = bars + 10;     // 2: S is double buffered so that Q K^T of the next tile overlaps this tile's softmax
   uint64_t* p_ready = bars + 12;    // 1
-  uint64_t* o_done = bars + 13;     // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* o_done = bars + 13;     // 2: P V of tile j arrives on o_done[j & 1] (SMALL) or o_done[0] (one P buffer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) dec_stamp(p.trace, 16);                 // CTA started
   // unit = (batch, KV head); blockIdx.x = unit * splits + split
   const uint32_t split = blockIdx.x % p.splits;
   const uint32_t unit = blockIdx.x / p.splits;
@@ -105,8 +114,12 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (uint32_t i = 0; i < NSLOT; ++i) { tc::mbar_init(&k_full[i], 1); tc::mbar_init(&v_full[i], 1); tc::mbar_init(&kv_empty[i], 1); }
     tc::mbar_init(&s_full[0], 1);
     tc::mbar_init(&s_full[1], 1);
-    tc::mbar_init(p_ready, 4);
-    tc::mbar_init(o_done, 1);
+    // SMALL: only the warp that holds the (at most 8) query rows takes part in the tile loop.  With two P
+    // buffers a warp is no longer held back by the previous tile's product, so a warp without rows could run
+    // ahead and its arrival for tile j + 1 would be counted for tile j; the others skip the loop instead.
+    tc::mbar_init(p_ready, SMALL ? 1 : 4);
+    tc::mbar_init(&o_done[0], 1);
+    tc::mbar_init(&o_done[1], 1);
     tc::fence_barrier_init();
     tc::prefetch_tmap(&tmQ); tc::prefetch_tmap(&tmK); tc::prefetch_tmap(&tmV);
   }
@@ -121,6 +134,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
   pdl_wait();          // Q, the cache and the key counts may still be being written by earlier kernels
   pdl_trigger();
+  if (threadIdx.x == 0) dec_stamp(p.trace, 17);                 // predecessor complete
   // keys of this batch entry, optionally counted on the device
   uint32_t S = p.s;
   if (p.kv_lens) {
@@ -194,12 +208,12 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t da = tc::make_smem_desc(pa + kk * 32, 16, ROW_GROUP_STRIDE);
+          const uint64_t da = tc::make_smem_desc(pa + (j % PBUF) * P_BYTES + kk * 32, 16, ROW_GROUP_STRIDE);
           const uint64_t db = tc::make_smem_desc(va + kk * 2048, DBN * 128, 1024);
           tc::umma_f16(tmem_O, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc::umma_commit(&kv_empty[slot]);
-        tc::umma_commit(o_done);
+        tc::umma_commit(&o_done[j % PBUF]);
       }
     }
   } else {
@@ -218,8 +232,10 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (!row_valid) row_lim = -1;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (uint32_t j = 0; j < n_tiles && ok; ++j) {
+    const bool in_loop = !SMALL || warp_active;
+    for (uint32_t j = 0; j < n_tiles && ok && in_loop; ++j) {
       if (!dec_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      if (j == 0 && (warp & 3) == 0 && lane == 0) dec_stamp(p.trace, 18);       // first scores ready (Q, K landed, first MMA done)
       tc::tc_fence_after();
       float sv[DBN];
       float corr = 1.f;
@@ -238,7 +254,9 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mx *= p.scale_log2;                       // scale > 0: the max commutes with the scaling
         if (mx > m_used + kDecRescale || m_used == -INFINITY) {
           const float m_new = fmaxf(mx, m_used);
-          corr = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+          // a row that has not seen a key yet has nothing accumulated: no rescale (a factor other than 1 would make
+          // the whole warp wait for the previous product for nothing)
+          corr = (m_used == -INFINITY) ? ((m_new == -INFINITY || j == 0) ? 1.f : 0.f) : exp2f(m_used - m_new);
           m_used = m_new;
         }
         const float mm = (m_used == -INFINITY) ? 0.f : m_used;
@@ -247,10 +265,28 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int c = 0; c < DBN; ++c) { sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -mm)); rs += sv[c]; }
         l_run = l_run * corr + rs;
       }
+      // O may only be rescaled once every earlier P V product has landed in it, and the P buffer of this
+      // tile may only be overwritten once the product that read it last (tile j - PBUF) has completed.
+      // One buffer: both are "tile j - 1 done".  Two buffers: the rescale (rare after the first tiles, the
+      // running maximum is only raised by steps of 2^8) waits for tile j - 1, everything else for tile j - 2.
+      const bool rescale = warp_active && __any_sync(0xffffffffu, corr != 1.f);
+      if (PBUF == 1) {
+        if (j > 0) {
+          if (!dec_wait(&o_done[0], (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+          tc::tc_fence_after();
+        }
+      } else {
+        if (j > 1) {
+          if (!dec_wait(&o_done[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+          tc::tc_fence_after();
+        }
+        if (j > 0 && rescale) {
+          if (!dec_wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicExch(p.err, 19u); ok = false; break; }
+          tc::tc_fence_after();
+        }
+      }
       if (j > 0) {
-        if (!dec_wait(o_done, (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
-        tc::tc_fence_after();
-        if (warp_active && __any_sync(0xffffffffu, corr != 1.f)) {
+        if (rescale) {
 #pragma unroll
           for (int c0 = 0; c0 < DD; c0 += 32) {
             float ov[32];
@@ -265,7 +301,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
       }
       if (warp_active && (!SMALL || r < 8)) {
-        unsigned char* prow = p_s + (SMALL ? 0u : (r >> 3) * 1024) + (r & 7) * 128;
+        unsigned char* prow = p_s + (j % PBUF) * P_BYTES + (SMALL ? 0u : (r >> 3) * 1024) + (r & 7) * 128;
 #pragma unroll
         for (int c = 0; c < DBN / 8; ++c) {
           uint4 pk;
@@ -286,10 +322,14 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(p_ready);
     }
-    if (ok && n_tiles > 0) {
-      if (!dec_wait(o_done, (n_tiles - 1) & 1)) { atomicExch(p.err, 18u); ok = false; }
+    if (ok && n_tiles > 0 && in_loop) {
+      // products complete in issue order: the last one's arrival covers them all
+      const uint32_t jl = n_tiles - 1;
+      const bool done = PBUF == 1 ? dec_wait(&o_done[0], jl & 1) : dec_wait(&o_done[jl & 1], (jl >> 1) & 1);
+      if (!done) { atomicExch(p.err, 18u); ok = false; }
     }
     tc::tc_fence_after();
+    if ((warp & 3) == 0 && lane == 0) dec_stamp(p.trace, 19);    // every tile of this slice accumulated (the warp that holds row 0)
     if (p.splits == 1) {
       if (ok && warp_active) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -345,31 +385,44 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         *last_flag = (old == int(p.splits) - 1) ? 1 : 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (epi_tid == 0) dec_stamp(p.trace, 20);                 // record parked, ticket drawn
       if (*last_flag) {
         __threadfence();
-        // thread d merges column d of every row: coalesced over the 128 threads
-        const uint32_t d = epi_tid;
+        // The four epilogue warps take the rows in turn (row rr goes to warp rr mod 4), a lane four columns of a
+        // row: the rows of a unit are merged side by side instead of one after another, every slice's record is
+        // fetched with one 16-byte load per lane, and the loads of several slices are in flight together.  The
+        // slices are still added in slice order, so the result does not depend on which slice arrived last.
+        const uint32_t wq = epi_tid >> 5, ln = epi_tid & 31;
         const float* base = p.partials + size_t(unit) * p.splits * p.rows * D_REC;
-        for (uint32_t rr = 0; rr < p.rows; ++rr) {
+        for (uint32_t rr = wq; rr < p.rows; rr += 4) {
           float mm = -INFINITY;
-          for (uint32_t s2 = 0; s2 < p.splits; ++s2) mm = fmaxf(mm, __ldcg(base + (size_t(s2) * p.rows + rr) * D_REC + DD));
-          float acc = 0.f, den = 0.f;
+          for (uint32_t s2 = ln; s2 < p.splits; s2 += 32) mm = fmaxf(mm, __ldcg(base + (size_t(s2) * p.rows + rr) * D_REC + DD));
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+          float acc[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+#pragma unroll 4
           for (uint32_t s2 = 0; s2 < p.splits; ++s2) {
             const float* rc = base + (size_t(s2) * p.rows + rr) * D_REC;
             const float mw = __ldcg(rc + DD);
+            const float lw = __ldcg(rc + DD + 1);
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(rc + ln * 4));
             const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-            acc += f * __ldcg(rc + d);
-            den += f * __ldcg(rc + DD + 1);
+            acc[0] += f * x.x; acc[1] += f * x.y; acc[2] += f * x.z; acc[3] += f * x.w;
+            den += f * lw;
           }
           const uint32_t hh = kvh * p.G + rr / p.l, ll = rr % p.l;
-          static_cast<T*>(p.out)[size_t(b) * p.o_sn + size_t(hh) * p.o_sh + size_t(ll) * p.o_sl + d] =
-              ElemTraits<T>::from_f(den > 0.f ? acc / den : 0.f);
-          if (p.lse && d == 0)
+          T* orow = static_cast<T*>(p.out) + size_t(b) * p.o_sn + size_t(hh) * p.o_sh + size_t(ll) * p.o_sl + ln * 4;
+          // (o_sl, o_sh, o_sn are multiples of 8 elements and the base is 16-byte aligned: an 8-byte store is aligned)
+          *reinterpret_cast<uint2*>(orow) = make_uint2(pack2<T>(den > 0.f ? acc[0] / den : 0.f, den > 0.f ? acc[1] / den : 0.f),
+                                                       pack2<T>(den > 0.f ? acc[2] / den : 0.f, den > 0.f ? acc[3] / den : 0.f));
+          if (p.lse && ln == 0)
             p.lse[(size_t(b) * p.h + hh) * p.l + ll] = den > 0.f ? (mm + log2f(den)) * 0.6931471805599453f : -INFINITY;
         }
         if (epi_tid == 0) p.counters[unit] = 0;
+        if (epi_tid == 0 && p.trace != nullptr) p.trace[21] = dec_global_ns();     // merged (whichever CTA was last; unit 0 only when CTA 0's)
       }
     }
+    if (epi_tid == 0) dec_stamp(p.trace, 22);                   // epilogue done
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -397,8 +450,17 @@ bool sdpa_decode_tc_eligible(const SdpaArgs& a) {
   return uint64_t(a.n) * a.h_kv * 64 < (1ull << 31);
 }
 
+// Debug override of the split count (0 = the rule below); see kuiops_debug_sdpa_splits.
+std::atomic<int> g_sdpa_splits_override{0};
+
 static uint32_t decode_tc_splits(const SdpaArgs& a) {
   const uint64_t units = uint64_t(a.n) * a.h_kv;
+  const int forced = g_sdpa_splits_override.load(std::memory_order_relaxed);
+  if (forced > 0) {
+    const uint32_t tiles = (a.s + DBN - 1) / DBN;
+    const uint32_t f = uint32_t(forced) < tiles ? uint32_t(forced) : (tiles ? tiles : 1u);
+    return f > 64 ? 64 : f;
+  }
   const uint64_t resident = 2 * uint64_t(num_sms());          // two CTAs per SM
   if (units >= resident) return 1;
   uint32_t want = uint32_t(resident / units);               // whole waves only: a partial second wave costs a full one
@@ -475,11 +537,14 @@ static int decode_tc_launch(const SdpaArgs& a, void* workspace, size_t workspace
   p.out = a.out; p.o_sn = a.o_sn; p.o_sh = a.o_sh; p.o_sl = a.o_sl; p.lse = a.lse;
   p.err = tc_error_word_device();
   if (!p.err) return KUIOPS_ELAUNCH;
+  p.trace = g_gemm_trace.load(std::memory_order_relaxed);
   const unsigned grid = unsigned(uint64_t(a.n) * a.h_kv * p.splits);
   if (p.rows <= 8)
-    return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 1024 + 128, st);
+    return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 2 * 1024 + 128, st);
   return decode_tc_launch_variant<T, false>(mq, mk, mv, p, grid, D_SMEM + 128, st);
 }
+
+void sdpa_decode_tc_force_splits(int splits) { g_sdpa_splits_override.store(splits > 0 ? splits : 0, std::memory_order_relaxed); }
 
 int sdpa_decode_tc(const SdpaArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (a.dtype == KUIOPS_BF16) return decode_tc_launch<__nv_bfloat16>(a, workspace, workspace_bytes, st);

@@ -77,6 +77,7 @@ SIGNATURES = {
                                  c_u64, c_void_p, c_void_p]),
     "kuiops_rmsnorm_gather": (c_int, [c_int, c_u64, c_u32, c_u32, c_void_p, c_u64, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
+    "kuiops_debug_sdpa_splits": (c_int, [c_int]),
     "kuiops_sdpa_workspace_bytes": (c_size_t, [c_int] + [c_u32] * 7),
     "kuiops_sdpa": (c_int, [c_int] + [c_u32] * 7 +
                     [c_void_p, c_i64, c_i64, c_i64] * 3 +

@@ -324,27 +324,31 @@ def bench_decode_breakdown(T, iters):
     o4 = attn.as_strided((B, hq, 1, hd), (hq * hd, hd, hq * hd, 1))
     tok = torch.zeros(B, dtype=torch.int64, device=dev)
 
+    tiles = _ffi.ssq_tiles(d)
+    ssq_a = torch.rand(tiles, B, device=dev) * 128 + 64
+    ssq_b = torch.rand(tiles, B, device=dev) * 128 + 64
+
     def gemms():
+        # the four projections of a layer as the step launches them: both RMSNorms are folded in
         for li, L in enumerate(dec.layers):
-            _ffi.gemm_rope_qkv(x, L["wqkv"], hq, hk, hd, pos, cfg.rope_theta, dec.k_cache[li], dec.v_cache[li],
-                               rows_per_seq=1, out=qkv)
-            _ffi.gemm(attn, L["wo"], trans_b=True)
-            _ffi.gemm_swiglu(x, L["wgu"])
-            _ffi.gemm(act, L["wd"], trans_b=True)
+            _ffi.gemm_rope_qkv_rms(resid, L["wqkv"], hq, hk, hd, pos, cfg.rope_theta, ssq_a, cfg.eps, dec.k_cache[li], dec.v_cache[li],
+                                   rows_per_seq=1, out=qkv)
+            _ffi.gemm_residual_ssq(attn, L["wo"], resid, ssq_b)
+            _ffi.gemm_swiglu_rms(resid, L["wgu"], ssq_b, cfg.eps)
+            _ffi.gemm_residual_ssq(act, L["wd"], resid, ssq_a)       # (the running sum grows over the replays; timing does not depend on values)
 
     def attention():
         for li in range(cfg.n_layers):
             _ffi.sdpa(q4, dec.k_cache[li], dec.v_cache[li], is_causal=True, need_lse=False, out=o4, kv_lens=kvlen)
 
     def small():
-        for L in dec.layers:
-            _ffi.rmsnorm(x, L["n1"], cfg.eps, residual=resid)
-            _ffi.rmsnorm(x, L["n2"], cfg.eps, residual=resid)
+        # the norms the fold leaves: the first layer's and the final one
+        _ffi.rmsnorm(x, dec.layers[0]["n1"], cfg.eps)
+        _ffi.rmsnorm(x, dec.norm_f, cfg.eps)
 
     def head():
         h = _ffi.embedding(dec.embed, tok)
-        hf = _ffi.rmsnorm(h, dec.norm_f, cfg.eps, residual=resid)
-        logits = _ffi.gemm(hf, dec.lm_head, trans_b=True)
+        logits = _ffi.gemm(h, dec.lm_head, trans_b=True)
         _ffi.argmax_lastdim(logits)
 
     def step():
@@ -355,11 +359,11 @@ def bench_decode_breakdown(T, iters):
     dec._tok_out = torch.zeros_like(tok)
     dec._pos = pos.clone()
     dec._kvlen = kvlen.clone()
-    n_layer_launch = {"gemm": 4 * cfg.n_layers, "attention": cfg.n_layers, "norm": 2 * cfg.n_layers, "embed_head_argmax": 4}
+    n_layer_launch = {"gemm": 4 * cfg.n_layers, "attention": cfg.n_layers, "norm": 2, "embed_head_argmax": 3}
     weights = cfg.n_layers * (W * d + hq * hd * d + 2 * dec.ff * d + dec.ff * d) * 2
     kv = 2 * cfg.n_layers * B * hk * ctx * hd * 2
     head_b = cfg.vocab * d * 2
-    small_b = cfg.n_layers * 2 * 4 * B * d * 2
+    small_b = 2 * 2 * B * d * 2
     for name, fn, nbytes in (("gemm", gemms, weights), ("attention", attention, kv), ("norm", small, small_b),
                              ("embed_head_argmax", head, head_b), ("whole_step", step, weights + kv + head_b)):
         if not wanted("decode_step_part", name):

@@ -563,8 +563,9 @@ def run_ours(args):
         ids_dev = ids_host.to(dev)
         sampler = ClockSampler(local) if rank == 0 else None
         t = time_decoder(dec, cfg, batch, prompt, new, ids_dev, ids_host, dev, args.steps, args.warmup, use_graph, barrier, sampler)
-        if _ffi.tc_error() != 0:
-            raise SystemExit("a tensor-core pipeline wait timed out during the bench; numbers discarded")
+        word = _ffi.tc_error()
+        if word != 0:
+            raise SystemExit(f"a tensor-core pipeline wait timed out during the bench (error word {word}); numbers discarded")
         roofline = gateup_roofline(dec, cfg, batch, dev, 1)
         total_ms, e2e_ms, prefill_ms, decode_ms = max_over_ranks([t["total_ms"], t["e2e_ms"], t["prefill_ms"], t["decode_ms"]])
         gen_tokens = batch * new * world * args.steps

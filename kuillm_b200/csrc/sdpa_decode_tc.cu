@@ -27,6 +27,7 @@ constexpr uint32_t D_K_BYTES = DBN * DD * 2;
 constexpr uint32_t D_V_BYTES = DBN * DD * 2;
 constexpr uint32_t D_P_BYTES = DBM * DBN * 2;
 constexpr uint32_t D_SMEM = D_Q_BYTES + 2 * (D_K_BYTES + D_V_BYTES) + D_P_BYTES;   // 112 KB: two CTAs per SM
+constexpr uint32_t D_BAR_BYTES = 160;      // 16 mbarriers, the TMEM slot word and the merge flag behind the tiles
 constexpr uint32_t D_TMEM_COLS = 256;
 constexpr float kDecRescale = 8.0f;
 constexpr int D_REC = DD + 4;  // floats per parked row: 128 accumulators, max, sum, 2 pad (keeps rows 16-byte aligned)
@@ -73,7 +74,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // (two CTAs must fit one SM), so a misaligned base is reported instead of worked around.
   extern __shared__ __align__(1024) unsigned char smem[];
   if ((tc::smem_u32(smem) & 1023u) != 0) {
-    if (threadIdx.x == 0) atomicExch(p.err, 10u);
+    if (threadIdx.x == 0) atomicCAS(p.err, 0u, 10u);
     return;
   }
   constexpr uint32_t NSLOT = SMALL ? 3 : 2;                    // K/V ring depth
@@ -93,9 +94,14 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint64_t* v_full = bars + 4;      // NSLOT
   uint64_t* kv_empty = bars + 7;    // NSLOT
   uint64_t* s_full = bars + 10;     // 2: S is double buffered so that Q K^T of the next tile overlaps this tile's softmax
-  uint64_t* p_ready = bars + 12;    // 1
-  uint64_t* o_done = bars + 13;     // 2: P V of tile j arrives on o_done[j & 1] (SMALL) or o_done[0] (one P buffer)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  // One barrier per P buffer.  A waiter must never fall two phases behind its barrier (the parity test cannot
+  // tell "not yet" from "twice since"): with two P buffers the softmax of tile j + 1 does not depend on the
+  // issuer having seen tile j's arrival, so both arrivals on ONE barrier could pass between two polls of the
+  // issuer.  On p_ready[j & 1] the next phase (tile j + 2) needs scores that are only issued after the issuer
+  // has seen tile j.
+  uint64_t* p_ready = bars + 12;    // PBUF (room for 2): P of tile j arrives on p_ready[j % PBUF]
+  uint64_t* o_done = bars + 14;     // 2: P V of tile j arrives on o_done[j & 1] (SMALL) or o_done[0] (one P buffer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -117,7 +123,8 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // SMALL: only the warp that holds the (at most 8) query rows takes part in the tile loop.  With two P
     // buffers a warp is no longer held back by the previous tile's product, so a warp without rows could run
     // ahead and its arrival for tile j + 1 would be counted for tile j; the others skip the loop instead.
-    tc::mbar_init(p_ready, SMALL ? 1 : 4);
+    tc::mbar_init(&p_ready[0], SMALL ? 1 : 4);
+    tc::mbar_init(&p_ready[1], SMALL ? 1 : 4);
     tc::mbar_init(&o_done[0], 1);
     tc::mbar_init(&o_done[1], 1);
     tc::fence_barrier_init();
@@ -157,7 +164,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc::tma_load_4d(q_s + Q_HALF, &tmQ, q_full, 64, 0, int(kvh * p.G), int(b));
       for (uint32_t j = 0; j < n_tiles; ++j) {
         const uint32_t slot = j % NSLOT, ph = (j / NSLOT) & 1;
-        if (!dec_wait(&kv_empty[slot], ph ^ 1)) { atomicExch(p.err, 11u); break; }
+        if (!dec_wait(&kv_empty[slot], ph ^ 1)) { atomicCAS(p.err, 0u, 11u); break; }
         unsigned char* ks = kv_s + slot * (D_K_BYTES + D_V_BYTES);
         unsigned char* vs = ks + D_K_BYTES;
         const int key0 = int(s_lo + j * DBN);
@@ -176,13 +183,13 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       constexpr uint32_t idesc_qk = tc::make_idesc(is_bf16, 0, 0, DBM, DBN);
       constexpr uint32_t idesc_pv = tc::make_idesc(is_bf16, 0, 1, DBM, DD);
       bool ok = dec_wait(q_full, 0);
-      if (!ok) atomicExch(p.err, 12u);
+      if (!ok) atomicCAS(p.err, 0u, 12u);
       const uint32_t qa = tc::smem_u32(q_s), pa = tc::smem_u32(p_s);
       // S = Q K^T of tile j into S buffer j & 1: two 64-wide halves of the head dim x four 16-wide steps
       auto issue_qk = [&](uint32_t j) -> bool {
         const uint32_t slot = j % NSLOT, ph = (j / NSLOT) & 1, sbuf = j & 1;
         const uint32_t ka = tc::smem_u32(kv_s + slot * (D_K_BYTES + D_V_BYTES));
-        if (!dec_wait(&k_full[slot], ph)) { atomicExch(p.err, 13u); return false; }
+        if (!dec_wait(&k_full[slot], ph)) { atomicCAS(p.err, 0u, 13u); return false; }
         tc::tc_fence_after();
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh)
@@ -202,8 +209,8 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // the next tile's scores are computed while the softmax warps work on this one; their S
         // buffer was released when p_ready of tile j - 1 arrived
         if (j + 1 < n_tiles && !issue_qk(j + 1)) { ok = false; break; }
-        if (!dec_wait(p_ready, j & 1)) { atomicExch(p.err, 14u); ok = false; break; }
-        if (!dec_wait(&v_full[slot], ph)) { atomicExch(p.err, 15u); ok = false; break; }
+        if (!dec_wait(&p_ready[j % PBUF], (j / PBUF) & 1)) { atomicCAS(p.err, 0u, 14u); ok = false; break; }
+        if (!dec_wait(&v_full[slot], ph)) { atomicCAS(p.err, 0u, 15u); ok = false; break; }
         tc::tc_fence_after();
         // O += P V over the 64 keys of the tile: four 16-key steps; V is MN-major (head dim contiguous)
 #pragma unroll
@@ -234,7 +241,7 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     bool ok = true;
     const bool in_loop = !SMALL || warp_active;
     for (uint32_t j = 0; j < n_tiles && ok && in_loop; ++j) {
-      if (!dec_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(p.err, 16u); ok = false; break; }
+      if (!dec_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicCAS(p.err, 0u, 16u); ok = false; break; }
       if (j == 0 && (warp & 3) == 0 && lane == 0) dec_stamp(p.trace, 18);       // first scores ready (Q, K landed, first MMA done)
       tc::tc_fence_after();
       float sv[DBN];
@@ -272,16 +279,16 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const bool rescale = warp_active && __any_sync(0xffffffffu, corr != 1.f);
       if (PBUF == 1) {
         if (j > 0) {
-          if (!dec_wait(&o_done[0], (j - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+          if (!dec_wait(&o_done[0], (j - 1) & 1)) { atomicCAS(p.err, 0u, 17u); ok = false; break; }
           tc::tc_fence_after();
         }
       } else {
         if (j > 1) {
-          if (!dec_wait(&o_done[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(p.err, 17u); ok = false; break; }
+          if (!dec_wait(&o_done[j & 1], ((j >> 1) - 1) & 1)) { atomicCAS(p.err, 0u, 17u); ok = false; break; }
           tc::tc_fence_after();
         }
         if (j > 0 && rescale) {
-          if (!dec_wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicExch(p.err, 19u); ok = false; break; }
+          if (!dec_wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicCAS(p.err, 0u, 19u); ok = false; break; }
           tc::tc_fence_after();
         }
       }
@@ -320,13 +327,13 @@ sdpa_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc::fence_proxy_async();
       tc::tc_fence_before();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(p_ready);
+      if (lane == 0) tc::mbar_arrive(&p_ready[j % PBUF]);
     }
     if (ok && n_tiles > 0 && in_loop) {
       // products complete in issue order: the last one's arrival covers them all
       const uint32_t jl = n_tiles - 1;
       const bool done = PBUF == 1 ? dec_wait(&o_done[0], jl & 1) : dec_wait(&o_done[jl & 1], (jl >> 1) & 1);
-      if (!done) { atomicExch(p.err, 18u); ok = false; }
+      if (!done) { atomicCAS(p.err, 0u, 18u); ok = false; }
     }
     tc::tc_fence_after();
     if ((warp & 3) == 0 && lane == 0) dec_stamp(p.trace, 19);    // every tile of this slice accumulated (the warp that holds row 0)
@@ -540,8 +547,8 @@ static int decode_tc_launch(const SdpaArgs& a, void* workspace, size_t workspace
   p.trace = g_gemm_trace.load(std::memory_order_relaxed);
   const unsigned grid = unsigned(uint64_t(a.n) * a.h_kv * p.splits);
   if (p.rows <= 8)
-    return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 2 * 1024 + 128, st);
-  return decode_tc_launch_variant<T, false>(mq, mk, mv, p, grid, D_SMEM + 128, st);
+    return decode_tc_launch_variant<T, true>(mq, mk, mv, p, grid, 2048 + 3 * (D_K_BYTES + D_V_BYTES) + 2 * 1024 + D_BAR_BYTES, st);
+  return decode_tc_launch_variant<T, false>(mq, mk, mv, p, grid, D_SMEM + D_BAR_BYTES, st);
 }
 
 void sdpa_decode_tc_force_splits(int splits) { g_sdpa_splits_override.store(splits > 0 ? splits : 0, std::memory_order_relaxed); }

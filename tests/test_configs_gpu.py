@@ -203,6 +203,34 @@ def test_sdpa_decode_batch64(cuda, S, hkv):
     assert (o1.float() - out[5:6].float()).abs().max() <= 2e-2 * out[5:6].float().abs().max()
 
 
+def test_sdpa_decode_many_launches_never_time_out(cuda):
+    """The decode step's own attention shape (4 query heads per KV head, two P buffers), launched as
+    often as a few generations do: no pipeline wait may run out (an issuer that falls two phases behind
+    the barrier it polls did so about once per 40 000 launches) and every launch gives the same bits."""
+    g = gen(11)
+    B, S = 32, 2304
+    Q = torch.randn(B, 32, 1, 128, device="cuda", generator=g).bfloat16()
+    K = torch.randn(B, 8, S, 128, device="cuda", generator=g).bfloat16()
+    V = torch.randn(B, 8, S, 128, device="cuda", generator=g).bfloat16()
+    first, _ = _ffi.sdpa(Q, K, V, is_causal=True, need_lse=False)
+    first = first.clone()
+    out = torch.empty_like(first)
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        _ffi.sdpa(Q, K, V, is_causal=True, need_lse=False, out=out)
+        with torch.cuda.graph(graph, stream=s):
+            for _ in range(100):
+                _ffi.sdpa(Q, K, V, is_causal=True, need_lse=False, out=out)
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(600):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert _ffi.tc_error() == 0
+    assert torch.equal(out, first)
+
+
 def test_gpt2_small_shape_fp32_matches_cpu_eager(cuda, gates):
     """The reference's own CPU-runnable case: a GPT-2-small-shaped decoder (12 layers, d 768, 12 heads
     of 64, GELU MLP 3072, vocabulary 50257, learned positions), random N(0, 0.02) weights, fp32,

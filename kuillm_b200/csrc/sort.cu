@@ -10,7 +10,7 @@
 // pass every CTA counts the digits of its chunk in the current arrangement and reads the counts of
 // the chunks before it from its peers: that gives the first output position of each digit for
 // its chunk.  The pass then walks the chunk tile by tile; inside a tile the rank of an element
-// among the equal digits before it is found per warp with match.any plus a per-warp counter table
+// among the equal digits before it is found per warp with lane votes plus a per-warp counter table
 // in shared memory, the warps' tables are turned into offsets by one thread per digit, and the
 // elements are scattered.  Keys and indices ping-pong between two caller-provided buffers; the
 // first pass reads the input itself and the last pass writes the results.  Cluster barriers
@@ -79,10 +79,22 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
   static_assert(kSortPasses * kSortDigits == kSortThreads, "one histogram entry per thread");
   (&sh.chunk_hist[0][0])[tid] = 0;
   __syncthreads();
-  for (uint32_t i = lo + tid; i < hi; i += kSortThreads) {
-    const uint32_t k = sort_key(x[i], desc);
+  for (uint32_t i0 = lo; i0 < hi; i0 += kSortTile) {
+    // all loads of a tile in flight before the first shared-memory atomic
+    float v[kSortItems];
 #pragma unroll
-    for (int p = 0; p < kSortPasses; ++p) atomicAdd(&sh.chunk_hist[p][(k >> (8 * p)) & 255u], 1u);
+    for (int j = 0; j < kSortItems; ++j) {
+      const uint32_t i = i0 + uint32_t(j) * kSortThreads + tid;
+      v[j] = i < hi ? x[i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kSortItems; ++j) {
+      if (i0 + uint32_t(j) * kSortThreads + tid < hi) {
+        const uint32_t k = sort_key(v[j], desc);
+#pragma unroll
+        for (int p = 0; p < kSortPasses; ++p) atomicAdd(&sh.chunk_hist[p][(k >> (8 * p)) & 255u], 1u);
+      }
+    }
   }
   __syncthreads();
   if (tid < kSortDigits) sh.chunk_cnt[tid] = sh.chunk_hist[0][tid];      // pass 0 reads the input: its chunk counts are known already
@@ -117,11 +129,22 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
     const uint32_t shift = 8u * pass;
     const uint2* src = (pass == 2 ? buf_b : buf_a) + off;                // pass 0 reads x instead
     uint2* dst = (pass == 1 ? buf_b : buf_a) + off;                      // pass 3 writes the results instead
-    if (pass > 0) {
-      // digit counts of this chunk in the arrangement this pass reads
+    if (pass > 0 && cluster_ctas > 1) {
+      // digit counts of this chunk in the arrangement this pass reads (a row with one CTA needs none:
+      // nothing comes before its only chunk)
       if (tid < kSortDigits) sh.chunk_cnt[tid] = 0;
       __syncthreads();
-      for (uint32_t i = lo + tid; i < hi; i += kSortThreads) atomicAdd(&sh.chunk_cnt[(src[i].x >> shift) & 255u], 1u);
+      for (uint32_t i0 = lo; i0 < hi; i0 += kSortTile) {
+        uint32_t k[kSortItems];
+#pragma unroll
+        for (int j = 0; j < kSortItems; ++j) {
+          const uint32_t i = i0 + uint32_t(j) * kSortThreads + tid;
+          k[j] = i < hi ? src[i].x : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kSortItems; ++j)
+          if (i0 + uint32_t(j) * kSortThreads + tid < hi) atomicAdd(&sh.chunk_cnt[(k[j] >> shift) & 255u], 1u);
+      }
       __syncthreads();
     }
     if (cluster_ctas > 1) cluster.sync();                                 // the peers' counts for this pass are complete
@@ -150,8 +173,18 @@ sort_rows_kernel(uint32_t n, int descending, const float* __restrict__ X, float*
       for (int j = 0; j < kSortItems; ++j) {
         const uint32_t e = tile0 + uint32_t(warp) * (32 * kSortItems) + uint32_t(j) * 32 + lane;
         const bool valid = e < hi;
-        const uint32_t d = valid ? ((key[j] >> shift) & 255u) : 0xFFFFFFFFu;   // lanes past the end match only each other
-        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        const uint32_t d = (key[j] >> shift) & 255u;
+        // the lanes that hold the same digit: nine votes instead of match.any, whose cost grows with
+        // the number of distinct values in the warp (nearly 32 for random digits); lanes past the end
+        // match only each other
+        uint32_t peers = __ballot_sync(0xffffffffu, valid);
+        if (!valid) peers = ~peers;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const bool bit = (d >> b) & 1u;
+          const uint32_t vote = __ballot_sync(0xffffffffu, bit);
+          peers &= bit ? vote : ~vote;
+        }
         const int leader = __ffs(peers) - 1;
         uint32_t before = 0;
         if (lane == leader && valid) {

@@ -127,6 +127,9 @@ class Decoder:
         # *_rms): the norm weights live in the columns of the consuming projections
         self.fold_norm = True
         self.fold_norm_weights()
+        # tensor-parallel prefills of at least this many rows hide their all-reduces behind compute (two halves
+        # of the batch walk the layers in lockstep)
+        self.overlap_min_rows = 4096
 
     def fold_norm_weights(self):
         """Multiply each layer's norm weights into the columns of the projection that consumes the
@@ -290,11 +293,67 @@ class Decoder:
         best = _ffi.argmax_lastdim(vals.t().contiguous())                # [B]: the rank that holds the row's maximum
         return _ffi.gather(idxs.t().contiguous(), 1, best.reshape(B, 1)).reshape(B)
 
+    def _forward_tp_overlap(self, ids, positions, seq):
+        """Prefill of a tensor-parallel group with the sums over ranks hidden behind compute.  The batch
+        is cut into two halves of sequences that walk the layers in lockstep: while one half's partial
+        products are being summed (NCCL, asynchronously, on the library's own stream) the other half
+        computes its attention or MLP block.  Same kernels and the same two all-reduces per layer and
+        half as the plain form; only the order of launches differs."""
+        import torch.distributed as dist
+        cfg = self.cfg
+        B = ids.shape[0]
+        hd, hq, hk = cfg.head_dim, self.hq, self.hk
+        hb = B // 2
+        pos2 = positions.view(B, seq)
+        halves = []
+        for h in range(2):
+            sl = slice(h * hb, (h + 1) * hb)
+            halves.append(dict(sl=sl, rows=hb * seq, pos=pos2[sl].reshape(-1).contiguous(), resid=None, work=None,
+                               x=_ffi.embedding(self.embed, ids[sl].reshape(-1))))
+        for li, L in enumerate(self.layers):
+            for st in halves:                                   # attention block; ends with an asynchronous sum over ranks
+                if st["work"] is not None:
+                    st["work"].wait()                            # the previous layer's down projection, summed
+                if st["resid"] is None:
+                    h = _ffi.rmsnorm(st["x"], L["n1"], cfg.eps)
+                    st["resid"] = st["x"]
+                else:
+                    h = _ffi.rmsnorm(st["x"], L["n1"], cfg.eps, residual=st["resid"])
+                qkv = _ffi.gemm(h, L["wqkv"], trans_b=True)
+                _ffi.rope_qkv(qkv, hq, hk, hd, st["pos"], cfg.rope_theta, self.k_cache[li][st["sl"]], self.v_cache[li][st["sl"]],
+                              rows_per_seq=seq)
+                W = qkv.shape[1]
+                q4 = qkv.as_strided((hb, hq, seq, hd), (seq * W, hd, W, 1))
+                k4 = qkv.as_strided((hb, hk, seq, hd), (seq * W, hd, W, 1), hq * hd)
+                v4 = qkv.as_strided((hb, hk, seq, hd), (seq * W, hd, W, 1), (hq + hk) * hd)
+                attn = torch.empty((st["rows"], hq * hd), device=self.device, dtype=cfg.dtype)
+                o4 = attn.as_strided((hb, hq, seq, hd), (seq * hq * hd, hd, hq * hd, 1))
+                _ffi.sdpa(q4, k4, v4, is_causal=True, need_lse=False, out=o4)
+                st["o"] = _ffi.gemm(attn, L["wo"], trans_b=True)
+                st["work"] = dist.all_reduce(st["o"], group=self.tp_group, async_op=True)
+            for st in halves:                                   # MLP block; ends the same way
+                st["work"].wait()
+                h2 = _ffi.rmsnorm(st["o"], L["n2"], cfg.eps, residual=st["resid"])
+                act = _ffi.gemm_swiglu(h2, L["wgu"])
+                st["x"] = _ffi.gemm(act, L["wd"], trans_b=True)
+                st["work"] = dist.all_reduce(st["x"], group=self.tp_group, async_op=True)
+        outs = []
+        for st in halves:
+            st["work"].wait()
+            last = torch.arange(seq - 1, st["rows"], seq, device=self.device)
+            x, resid = _ffi.index(st["x"], 0, [last]), _ffi.index(st["resid"], 0, [last])
+            outs.append(_ffi.gemm(_ffi.rmsnorm(x, self.norm_f, cfg.eps, residual=resid), self.lm_head, trans_b=True))
+        self.length += seq
+        return torch.cat(outs, 0)
+
     def prefill(self, ids, local_logits=False):
         B, S = ids.shape
         assert self.k_cache is not None and S <= self.cap and self.length == 0
         positions = torch.arange(S, device=self.device).repeat(B)
-        out = self._forward(ids, positions, S)
+        if self.tp_size > 1 and B % 2 == 0 and B * S >= self.overlap_min_rows and B * S > self.exchange_rows:
+            out = self._forward_tp_overlap(ids, positions, S)
+        else:
+            out = self._forward(ids, positions, S)
         return out if local_logits else self._full_logits(out)
 
     def decode_step(self, ids, local_logits=False):

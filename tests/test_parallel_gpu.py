@@ -58,6 +58,18 @@ def _tp_worker(rank, size, port, q):
     tok_tp = tp.next_token(out2[:, rank * per:(rank + 1) * per].contiguous())
     ok_tok = torch.equal(tok_tp, _f.argmax_lastdim(out2))
     ok_tp = rel(out, ref) < 3e-2 and rel(out2, ref2) < 3e-2 and n_calls == 2 * cfg.n_layers and ok_tok
+    # the same prefill with its all-reduces hidden behind the other half of the batch: same logits (the sums are
+    # element-wise, whatever the message size), same caches (the next decode step agrees), twice the calls
+    tpo = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
+    tpo.alloc_cache(4, 24)
+    tpo.overlap_min_rows = 1
+    calls[0] = 0
+    dist.all_reduce = counted
+    outo = tpo.prefill(ids)
+    n_over = calls[0]
+    dist.all_reduce = real
+    outo2 = tpo.decode_step(ref_tok)
+    ok_tp = ok_tp and rel(outo, out) < 1e-2 and rel(outo2, out2) < 1e-2 and n_over == 4 * cfg.n_layers
     # the fused form: row-split GEMMs push their partials into both ranks' memory, the next norm sums
     # them; no NCCL call on that path, and with two ranks the sum rounds exactly as NCCL's does
     from kuipy import _ffi

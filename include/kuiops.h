@@ -395,6 +395,24 @@ KUIOPS_API int kuiops_mean_f16 (uint64_t m, uint64_t n, const void* in, void* ou
 KUIOPS_API int kuiops_multinomial_f32(uint32_t m, uint32_t n, uint32_t num_samples, const void* weights, int64_t* out,
                                       uint64_t seed, uint64_t offset, int* status, kuiops_stream_t stream);
 
+/* One token per row of an [m, n] fp32 logit matrix: temperature, top-k filter, top-p (nucleus) filter and the
+ * draw in two launches that read the logits once (the selection's second look comes from L2), instead of the
+ * separate div / topk / sort / softmax / cumsum / scatter / multinomial calls a sampling loop makes
+ * (infer.py:139-143 samples with temperature 0.7 through HuggingFace's warpers).  No counterpart in the
+ * reference.  The set kept is the one those warpers keep: the top_k largest logits (equal values: lowest index
+ * first), weights e_r = exp((v_r - v_max) / temperature) taken largest first, rank r kept while the running sum
+ * before it is below top_p times the sum of all top_k weights (rank 0 always).  The draw is
+ * u = (x0 >> 8) * 2^-24, (x0, ..) = Philox4x32-10(counter = (offset low, offset high, row, 0), key = (seed low,
+ * seed high)); the token is the first kept rank whose running sum exceeds u times the kept sum (running sums in
+ * the fixed order csrc/sampling.cu states).  out[row] = the token id; out_prob (nullable) [m] fp32 = its
+ * probability under the filtered distribution.  temperature > 0, 0 < top_p <= 1, 1 <= top_k (min(top_k, n)
+ * <= 1024, else KUIOPS_ELIMIT).  workspace: kuiops_sample_workspace_bytes(m, min(top_k, n)) bytes, 16-byte
+ * aligned, no initial contents required. */
+KUIOPS_API size_t kuiops_sample_workspace_bytes(uint32_t m, uint32_t top_k);
+KUIOPS_API int kuiops_sample_topk_topp_f32(uint32_t m, uint32_t n, const void* logits, float temperature, uint32_t top_k,
+                                           float top_p, uint64_t seed, uint64_t offset, int64_t* out, float* out_prob,
+                                           void* workspace, size_t workspace_bytes, kuiops_stream_t stream);
+
 /* Whole-tensor folds to one device scalar (aten.all / aten.any over bool bytes,
  * aten.max over int64 / fp32).  Reference: Kuiops.HReducePoly.Exact.reduce,
  * kuiops/reduce/Kuiops.HReducePoly.Exact.fsti:26-46 (which mallocs the result

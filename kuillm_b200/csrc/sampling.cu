@@ -171,6 +171,101 @@ multinomial_rows_kernel(uint32_t n, uint32_t num_samples, const float* __restric
   }
 }
 
+// ---- fused sampler: temperature, top-k, top-p and the draw ------------------------------------------------------
+// The k largest logits of every row (largest first, from topk_f32) are turned into weights
+// e_r = exp((v_r - v_0) / T); rank r is kept while the running sum BEFORE it stays below top_p times the sum
+// of all k (the set HuggingFace's temperature -> top-k -> top-p warpers keep, ranks taken largest first; rank 0
+// is always kept); one Philox draw u (counter = (offset, row, 0), key = seed) picks the first kept rank whose
+// running sum exceeds u times the kept sum.  Running sums are taken in a fixed order so that a CPU restatement
+// reproduces them: 4 ranks per lane left to right, an inclusive Hillis-Steele scan over the lanes of a 128-rank
+// group, groups added left to right; incl_r = (base of the group + sum of the lanes before) + sum inside the lane.
+constexpr int kPickThreads = 256;                 // 8 groups of 128 ranks: k <= 1024
+
+__global__ void __launch_bounds__(kPickThreads)
+sample_pick_kernel(uint32_t k, const float* __restrict__ vals, const int64_t* __restrict__ idx, float inv_t, float top_p,
+                   int64_t* __restrict__ out, float* __restrict__ out_prob, uint32_t seed_lo, uint32_t seed_hi, uint32_t off_lo,
+                   uint32_t off_hi) {
+  __shared__ float group_sum[kPickThreads / 32];
+  __shared__ float group_base[kPickThreads / 32 + 1];
+  __shared__ unsigned int kept_n, pick_r, last_r;
+  __shared__ float kept_sum;
+  const uint32_t row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_trigger();
+  const float* v = vals + size_t(row) * k;
+  const float v0 = v[0];
+  if (tid == 0) { kept_n = 0; pick_r = 0xFFFFFFFFu; last_r = 0; }
+  float a[4], run[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t r = uint32_t(tid) * 4 + j;
+    float e = 0.f;
+    if (r < k) {
+      const float x = v[r];
+      // the largest logit itself weighs 1 whatever it is (an infinite or NaN maximum would give inf - inf)
+      e = (r == 0) ? 1.f : expf((x - v0) * inv_t);
+      if (!(e >= 0.f) || e > 3.402823466e38f) e = 0.f;
+    }
+    a[j] = e;
+    run[j] = j == 0 ? e : run[j - 1] + e;
+  }
+  float incl = run[3];
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  const float prev = __shfl_up_sync(0xffffffffu, incl, 1);
+  const float lane_excl = lane == 0 ? 0.f : prev;
+  if (lane == 31) group_sum[warp] = incl;
+  __syncthreads();
+  if (tid == 0) {
+    float b = 0.f;
+    for (int g = 0; g < kPickThreads / 32; ++g) { group_base[g] = b; b += group_sum[g]; }
+    group_base[kPickThreads / 32] = b;
+  }
+  __syncthreads();
+  const float total = group_base[kPickThreads / 32];
+  const float before = group_base[warp] + lane_excl;            // running sum before this lane's first rank
+  const float cut = __fmul_rn(top_p, total);
+  // the kept ranks are a prefix: count them
+  unsigned int mine = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t r = uint32_t(tid) * 4 + j;
+    const float excl_r = j == 0 ? before : before + run[j - 1];
+    if (r < k && (r == 0 || excl_r < cut)) ++mine;
+  }
+  if (mine) atomicAdd(&kept_n, mine);
+  __syncthreads();
+  const uint32_t R = kept_n;                                    // >= 1
+  if ((R - 1) / 4 == uint32_t(tid)) kept_sum = before + run[(R - 1) & 3];
+  __syncthreads();
+  const float K = kept_sum;
+  uint32_t x[4];
+  philox4x32_10(off_lo, off_hi, row, 0u, seed_lo, seed_hi, x);
+  const float u = float(x[0] >> 8) * 5.9604644775390625e-08f;
+  const float t = __fmul_rn(u, K);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t r = uint32_t(tid) * 4 + j;
+    if (r < R && a[j] > 0.f) {
+      atomicMax(&last_r, r);
+      if (before + run[j] > t) atomicMin(&pick_r, r);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t r = pick_r != 0xFFFFFFFFu ? pick_r : last_r;
+    out[row] = idx[size_t(row) * k + r];
+  }
+  if (out_prob != nullptr) {
+    const uint32_t r = pick_r != 0xFFFFFFFFu ? pick_r : last_r;
+    if (r / 4 == uint32_t(tid)) out_prob[row] = K > 0.f ? a[r & 3] / K : 1.f;
+  }
+}
+
 }  // namespace kuiops
 
 using namespace kuiops;
@@ -184,6 +279,27 @@ int kuiops_multinomial_f32(uint32_t m, uint32_t n, uint32_t num_samples, const v
   return launch_pdl(multinomial_rows_kernel, dim3(m), dim3(kSampThreads), 0, as_stream(s), n, num_samples,
                     static_cast<const float*>(probs), out, uint32_t(seed), uint32_t(seed >> 32), uint32_t(offset),
                     uint32_t(offset >> 32), status);
+}
+
+size_t kuiops_sample_workspace_bytes(uint32_t m, uint32_t top_k) { return size_t(m) * top_k * 12 + 256; }
+
+int kuiops_sample_topk_topp_f32(uint32_t m, uint32_t n, const void* logits, float temperature, uint32_t top_k, float top_p,
+                                uint64_t seed, uint64_t offset, int64_t* out, float* out_prob, void* workspace,
+                                size_t workspace_bytes, kuiops_stream_t s) {
+  if (m == 0 || n == 0 || !logits || !out) return KUIOPS_EINVAL;
+  if (!(temperature > 0.f) || !(top_p > 0.f) || top_p > 1.f || top_k == 0) return KUIOPS_EINVAL;
+  const uint32_t k = top_k < n ? top_k : n;
+  if (k > 4u * kPickThreads) return KUIOPS_ELIMIT;
+  if (!workspace || workspace_bytes < kuiops_sample_workspace_bytes(m, k) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
+    return KUIOPS_EWORKSPACE;
+  // [m, k] int64 indices first (8-byte aligned), then the [m, k] values
+  int64_t* idx = static_cast<int64_t*>(workspace);
+  float* vals = reinterpret_cast<float*>(idx + size_t(m) * k);
+  const int rc = kuiops_topk_f32(m, n, k, logits, vals, idx, s);
+  if (rc != KUIOPS_OK) return rc;
+  return launch_pdl(sample_pick_kernel, dim3(m), dim3(kPickThreads), 0, as_stream(s), k, static_cast<const float*>(vals),
+                    static_cast<const int64_t*>(idx), 1.f / temperature, top_p, out, out_prob, uint32_t(seed), uint32_t(seed >> 32),
+                    uint32_t(offset), uint32_t(offset >> 32));
 }
 
 }  // extern "C"

@@ -293,6 +293,13 @@ class Decoder:
         best = _ffi.argmax_lastdim(vals.t().contiguous())                # [B]: the rank that holds the row's maximum
         return _ffi.gather(idxs.t().contiguous(), 1, best.reshape(B, 1)).reshape(B)
 
+    def sample_token(self, local, temperature=0.7, top_k=50, top_p=0.8, seed=0, offset=0):
+        """One sampled token per row: temperature, top-k and top-p filters and the draw in one fused call
+        (kuiops_sample_topk_topp_f32) over the full fp32 logits.  Every rank of a tensor-parallel group
+        draws from the same stream position and so picks the same token."""
+        logits = _ffi.cast(self._full_logits(local), torch.float32)
+        return _ffi.sample_topk_topp(logits, temperature, top_k, top_p, seed=seed, offset=offset)
+
     def _forward_tp_overlap(self, ids, positions, seq):
         """Prefill of a tensor-parallel group with the sums over ranks hidden behind compute.  The batch
         is cut into two halves of sequences that walk the layers in lockstep: while one half's partial
@@ -418,8 +425,16 @@ class Decoder:
             self.length += 1
         return out
 
-    def generate(self, ids, new_tokens, use_graph=False):
-        """Greedy decoding; returns the [B, new_tokens] generated ids."""
+    def generate(self, ids, new_tokens, use_graph=False, sampling=None):
+        """Greedy decoding, or sampled decoding when `sampling` is a dict of sample_token's arguments
+        (temperature, top_k, top_p, seed; token t of the generation draws at stream offset 4 t);
+        returns the [B, new_tokens] generated ids."""
+        if sampling is not None:
+            kw = dict(sampling)
+            out = [self.sample_token(self.prefill(ids, local_logits=True), offset=0, **kw)]
+            for t in range(1, new_tokens):
+                out.append(self.sample_token(self.decode_step(out[-1], local_logits=True), offset=4 * t, **kw))
+            return torch.stack(out, 1)
         tok = self.next_token(self.prefill(ids, local_logits=True))
         if use_graph and new_tokens > 1:
             if getattr(self, "_graph", None) is None or self._tok.shape[0] != ids.shape[0]:

@@ -120,6 +120,9 @@ SIGNATURES = {
     "kuiops_sort_f32": (c_int, [c_u32, c_u32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "kuiops_multinomial_f32": (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_u64, c_u64, c_void_p, c_void_p]),
     "kuiops_argmax": (c_int, [c_int, c_u64, c_u64, c_void_p, c_void_p, c_void_p]),
+    "kuiops_sample_workspace_bytes": (c_size_t, [c_u32, c_u32]),
+    "kuiops_sample_topk_topp_f32": (c_int, [c_u32, c_u32, c_void_p, c_float, c_u32, c_float, c_u64, c_u64, c_void_p, c_void_p,
+                                            c_void_p, c_size_t, c_void_p]),
 }
 for _sfx in ("f32", "bf16", "f16"):
     SIGNATURES[f"kuiops_mm_{_sfx}"] = (c_int, [c_u32, c_u32, c_u32, c_void_p, c_void_p, c_void_p,
@@ -622,6 +625,27 @@ def multinomial(P, num_samples=1, seed=0, offset=0):
     _check(lib().kuiops_multinomial_f32(m, n, num_samples, Pc.data_ptr(), out.data_ptr(), int(seed) & (2 ** 64 - 1),
                                         int(offset) & (2 ** 64 - 1), _status(Pc.device).data_ptr(), _stream()), "multinomial")
     return out
+
+
+def sample_topk_topp(logits, temperature=1.0, top_k=50, top_p=1.0, seed=0, offset=0, out=None, want_prob=False):
+    """One token id per row of the fp32 logits ([m, n] or [n]): temperature, top-k, top-p and the draw from the
+    documented Philox stream (seed, offset); see kuiops_sample_topk_topp_f32.  With want_prob also the picked
+    token's probability under the filtered distribution."""
+    if logits.dtype != torch.float32:
+        raise KuiopsError(EUNSUPPORTED, f"sample over {logits.dtype}")
+    Lc = logits.contiguous()
+    n = Lc.shape[-1]
+    m = Lc.numel() // n
+    k = min(int(top_k), n)
+    if out is None:
+        out = torch.empty(tuple(Lc.shape[:-1]), dtype=torch.int64, device=Lc.device)
+    prob = torch.empty(tuple(Lc.shape[:-1]), dtype=torch.float32, device=Lc.device) if want_prob else None
+    nbytes = lib().kuiops_sample_workspace_bytes(m, max(k, 1))
+    ws = workspace("sample", Lc.device, nbytes)
+    _check(lib().kuiops_sample_topk_topp_f32(m, n, Lc.data_ptr(), float(temperature), int(top_k), float(top_p),
+                                             int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1), out.data_ptr(), _ptr(prob),
+                                             ws.data_ptr(), nbytes, _stream()), "sample_topk_topp")
+    return (out, prob) if want_prob else out
 
 
 def sort_lastdim(X, descending=False):

@@ -118,7 +118,7 @@ class Table:
 def bench_stream(T, iters):
     dev = "cuda"
     m, n = 64, 128256
-    if any(wanted(o, f"{m}x{n}") for o in ("softmax_f32", "topk_f32_k50", "argmax_f32", "cumsum_f32", "sort_f32", "multinomial_f32")):
+    if any(wanted(o, f"{m}x{n}") for o in ("softmax_f32", "topk_f32_k50", "argmax_f32", "cumsum_f32", "sort_f32", "multinomial_f32", "sample_topk50_topp_f32")):
         nv = variants_for(m * n * 4)
         xs = [torch.randn(m, n, device=dev) * 3 for _ in range(nv)]
         y = torch.empty_like(xs[0])
@@ -133,6 +133,11 @@ def bench_stream(T, iters):
             T.add("multinomial_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.multinomial(pm[i], 1, seed=1, offset=4 * i), nv, iters)), bytes_=m * n * 4,
                   note="one draw per row; one CTA per row")
             del pm
+        if wanted("sample_topk50_topp_f32", f"{m}x{n}"):
+            ids = torch.empty(m, dtype=torch.int64, device=dev)
+            T.add("sample_topk50_topp_f32", f"{m}x{n}",
+                  (lambda: time_us(lambda i: _ffi.sample_topk_topp(xs[i], 0.7, 50, 0.8, seed=1, offset=4 * i, out=ids), nv, iters)), bytes_=m * n * 4,
+                  note="temperature + top-k + top-p + draw: two launches, the logits read once")
         T.add("sort_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.sort_lastdim(xs[i]), nv, max(2, iters // 4))), bytes_=m * n * 16,
               note="values + int64 permutation; a cluster of 4 CTAs per row")
         T.add("cumsum_f32", f"{m}x{n}", (lambda: time_us(lambda i: _ffi.cumsum_lastdim(xs[i], out=y), nv, iters)), bytes_=2 * m * n * 4)

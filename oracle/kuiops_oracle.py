@@ -423,3 +423,71 @@ def max_rel_err(out: np.ndarray, ref: np.ndarray) -> float:
     o, r = out.astype(np.float64), ref.astype(np.float64)
     scale = np.abs(r).max()
     return float(np.abs(o - r).max() / (scale if scale > 0 else 1.0))
+
+
+def sample_topk_topp(logits: np.ndarray, temperature: float, top_k: int, top_p: float, seed: int, offset: int):
+    """The specification kuiops_sample_topk_topp_f32 states for itself (the reference has no sampler; its driver
+    samples through HuggingFace's temperature / top-k / top-p warpers, infer.py:139-143).  Returns (token ids,
+    probability of the token under the filtered distribution, margin): margin[row] is the relative distance of
+    the draw's threshold to the nearest running sum, or 0 when ranks that carry weight sit within rounding of
+    the nucleus cut; a restatement whose exp differs in the last bit can only disagree where the margin is of
+    that order."""
+    f32 = np.float32
+    rows = logits.reshape(-1, logits.shape[-1]).astype(f32)
+    m, n = rows.shape
+    k = min(int(top_k), n)
+    ids = np.zeros(m, dtype=np.int64)
+    prob = np.zeros(m, dtype=f32)
+    margin = np.zeros(m, dtype=np.float64)
+    inv_t = f32(1.0) / f32(temperature)
+    for r in range(m):
+        v, idx = topk(rows[r:r + 1], k)
+        v, idx = v[0].astype(f32), idx[0]
+        with np.errstate(all="ignore"):
+            e = np.exp(((v - v[0]) * inv_t).astype(f32)).astype(f32)
+        e[0] = 1
+        e[~(e >= 0) | np.isinf(e)] = 0
+        a = np.zeros(1024, dtype=f32)
+        a[:k] = e
+        a = a.reshape(8, 32, 4)
+        run = np.empty_like(a)
+        run[..., 0] = a[..., 0]
+        for j in range(1, 4):
+            run[..., j] = (run[..., j - 1] + a[..., j]).astype(f32)
+        incl = run[..., 3].copy()
+        for o in (1, 2, 4, 8, 16):
+            nxt = incl.copy()
+            nxt[:, o:] = (incl[:, o:] + incl[:, :-o]).astype(f32)
+            incl = nxt
+        lane_excl = np.zeros_like(incl)
+        lane_excl[:, 1:] = incl[:, :-1]
+        base = np.zeros(9, dtype=f32)
+        for g in range(8):
+            base[g + 1] = f32(base[g] + incl[g, 31])
+        total = base[8]
+        before = (base[:8, None] + lane_excl).astype(f32)                  # [8, 32]
+        excl = np.empty_like(a)
+        excl[..., 0] = before
+        for j in range(1, 4):
+            excl[..., j] = (before + run[..., j - 1]).astype(f32)
+        incl_r = (before[..., None] + run).astype(f32).reshape(-1)
+        excl, a_flat = excl.reshape(-1), a.reshape(-1)
+        cut = f32(f32(top_p) * total)
+        keep = (np.arange(1024) < k) & ((np.arange(1024) == 0) | (excl < cut))
+        R = int(keep.sum())
+        K = incl_r[R - 1]
+        x = philox4x32_10((offset & 0xFFFFFFFF, (offset >> 32) & 0xFFFFFFFF, r, 0), (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+        u = f32(x[0] >> 8) * f32(2.0 ** -24)
+        t = f32(u * K)
+        cand = np.nonzero((np.arange(1024) < R) & (a_flat > 0))[0]
+        over = cand[incl_r[cand] > t]
+        pick = int(over[0]) if len(over) else int(cand[-1])
+        ids[r] = idx[pick]
+        prob[r] = a_flat[pick] / K if K > 0 else 1.0
+        scale = max(float(total), 1e-30)
+        # ranks whose membership a last-bit difference could flip only matter by the weight they carry
+        near_cut = np.abs(excl[1:k].astype(np.float64) - float(cut)) <= 1e-6 * scale
+        d_cut = 1.0 if float(a_flat[1:k][near_cut].astype(np.float64).sum()) <= 4e-6 * scale else 0.0
+        d_pick = np.abs(incl_r[:R].astype(np.float64) - float(t)).min() / scale
+        margin[r] = min(d_cut, d_pick)
+    return ids.reshape(logits.shape[:-1]), prob.reshape(logits.shape[:-1]), margin.reshape(logits.shape[:-1])

@@ -91,6 +91,32 @@ def test_generate_is_deterministic_and_cache_consistent(cuda):
     assert O.rel_frobenius(to_np(l_step), to_np(l_full)) < 3e-2
 
 
+def test_sampled_generation_repeats_and_respects_its_filters(cuda):
+    """Sampled decoding through the fused sampler: the same seed repeats the generation, another seed
+    does not, top_k = 1 is greedy, and every sampled token lies in the top-k of the logits it was drawn from."""
+    from kuipy import _ffi
+    from kuillm_b200.decoder import Decoder, DecoderConfig
+    dec = Decoder(DecoderConfig.tiny(), device="cuda", seed=1, init_std=0.05)
+    ids = torch.randint(0, 1000, (3, 10), generator=torch.Generator().manual_seed(2)).cuda()
+    dec.alloc_cache(3, 32)
+    samp = dict(temperature=0.9, top_k=20, top_p=0.9, seed=123)
+    a = dec.generate(ids, 8, sampling=samp)
+    dec.length = 0
+    assert torch.equal(a, dec.generate(ids, 8, sampling=samp))
+    dec.length = 0
+    assert not torch.equal(a, dec.generate(ids, 8, sampling=dict(samp, seed=124)))
+    dec.length = 0
+    greedy = dec.generate(ids, 8)
+    dec.length = 0
+    assert torch.equal(greedy, dec.generate(ids, 8, sampling=dict(temperature=0.7, top_k=1, top_p=1.0, seed=5)))
+    dec.length = 0
+    logits = dec.prefill(ids).float()
+    tok = dec.sample_token(logits.to(dec.cfg.dtype), **samp)
+    top = logits.topk(20, dim=-1).indices
+    assert all(int(tok[r]) in set(top[r].tolist()) for r in range(3))
+    assert _ffi.tc_error() == 0
+
+
 def test_rope_prefill_sized_call_equals_row_chunks(cuda):
     """A prefill-sized call shares each row's sines and cosines over eight heads; small calls compute
     them per head.  Same arithmetic, so the packed rows and both caches must agree bit for bit."""

@@ -100,3 +100,91 @@ def test_torch_multinomial_is_offloaded_and_follows_the_generator(cuda, gates):
     seed = torch.cuda.default_generators[0].initial_seed()
     assert seed == 1234
     assert np.array_equal(a.cpu().numpy(), O.multinomial(P.cpu().numpy(), 1, seed=1234, offset=0))
+
+
+# ---- fused sampler: temperature, top-k, top-p, draw (kuiops_sample_topk_topp_f32) ---------------------------
+def _filtered_distribution(row, temperature, top_k, top_p):
+    """The distribution HuggingFace's temperature -> top-k -> top-p warpers leave (fp64), token id -> probability."""
+    z = row.astype(np.float64) / temperature
+    order = np.lexsort((np.arange(z.size), -z))[:top_k]
+    p = np.exp(z[order] - z[order].max())
+    p /= p.sum()
+    before = np.concatenate(([0.0], np.cumsum(p)[:-1]))
+    keep = before < top_p
+    keep[0] = True
+    q = np.where(keep, p, 0.0)
+    return order, q / q.sum()
+
+
+def test_sampler_oracle_keeps_the_nucleus_and_follows_the_distribution():
+    rng = np.random.default_rng(3)
+    logits = (rng.standard_normal((1, 900)) * 2).astype(np.float32)
+    order, q = _filtered_distribution(logits[0], 0.7, 40, 0.8)
+    allowed = set(order[q > 0].tolist())
+    rows = np.tile(logits, (4000, 1))
+    ids, prob, _ = O.sample_topk_topp(rows, 0.7, 40, 0.8, seed=11, offset=4)
+    assert set(ids.tolist()) <= allowed
+    counts = np.array([(ids == t).sum() for t in order[q > 0]])
+    exp = q[q > 0] * ids.size
+    big = exp >= 5
+    chi2 = ((counts[big] - exp[big]) ** 2 / exp[big]).sum()
+    assert chi2 < 2.5 * big.sum() + 20, (chi2, big.sum())
+    # the reported probability is the filtered distribution's
+    lookup = dict(zip(order.tolist(), q.tolist()))
+    assert np.allclose(prob, [lookup[t] for t in ids.tolist()], rtol=1e-4)
+    # top_k = 1 and a tiny nucleus are greedy
+    g1, _, _ = O.sample_topk_topp(logits, 1.0, 1, 1.0, seed=1, offset=0)
+    g2, _, _ = O.sample_topk_topp(logits, 1.0, 50, 1e-6, seed=1, offset=0)
+    assert g1[0] == g2[0] == logits[0].argmax()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,top_k,top_p,temp", [(5, 100, 50, 0.9, 0.7), (64, 128256, 50, 0.8, 0.7), (33, 4099, 1024, 0.95, 1.3),
+                                                  (7, 300, 500, 1.0, 1.0), (4, 2000, 1, 0.5, 0.1), (9, 50000, 20, 1e-6, 2.0)])
+def test_sampler_matches_the_oracle(cuda, m, n, top_k, top_p, temp):
+    from kuipy import _ffi
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    logits = torch.randn(m, n, generator=g) * 3
+    ids, prob = _ffi.sample_topk_topp(logits.cuda(), temp, top_k, top_p, seed=0xABCDEF0123, offset=12, want_prob=True)
+    want, wprob, margin = O.sample_topk_topp(logits.numpy(), temp, top_k, top_p, seed=0xABCDEF0123, offset=12)
+    ids, prob = ids.cpu().numpy(), prob.cpu().numpy()
+    sure = margin > 1e-5              # elsewhere one bit of an exp may move a threshold across a running sum
+    assert (~sure).sum() <= max(1, m // 10)
+    assert np.array_equal(ids[sure], want[sure])
+    assert np.allclose(prob[sure], wprob[sure], rtol=1e-4, atol=1e-7)
+    # every pick, sure or not, lies inside the set the filters keep
+    for r in range(m):
+        order, q = _filtered_distribution(logits.numpy()[r], temp, min(top_k, n), top_p)
+        assert ids[r] in set(order[q > 1e-12].tolist()) or not sure[r]
+    # another position of the stream gives other draws, the same position the same
+    again = _ffi.sample_topk_topp(logits.cuda(), temp, top_k, top_p, seed=0xABCDEF0123, offset=12).cpu().numpy()
+    assert np.array_equal(again, ids)
+
+
+@pytest.mark.gpu
+def test_sampler_distribution_and_edge_rows(cuda):
+    from kuipy import _ffi
+    rng = np.random.default_rng(5)
+    row = (rng.standard_normal(5000) * 2.5).astype(np.float32)
+    order, q = _filtered_distribution(row, 0.7, 50, 0.8)
+    logits = torch.from_numpy(np.tile(row, (8192, 1))).cuda()
+    ids = _ffi.sample_topk_topp(logits, 0.7, 50, 0.8, seed=21, offset=0).cpu().numpy()
+    kept = order[q > 0]
+    assert set(ids.tolist()) <= set(kept.tolist())
+    counts = np.array([(ids == t).sum() for t in kept])
+    exp = q[q > 0] * ids.size
+    big = exp >= 5
+    chi2 = ((counts[big] - exp[big]) ** 2 / exp[big]).sum()
+    assert chi2 < 2.5 * big.sum() + 20, (chi2, big.sum())
+    # rows with infinities and NaN: the largest entry (NaN above +inf) is the only candidate left
+    bad = torch.randn(3, 1000)
+    bad[0, 17] = float("inf")
+    bad[1, 400] = float("nan")
+    bad[2, :] = float("-inf")
+    got = _ffi.sample_topk_topp(bad.cuda(), 1.0, 50, 0.9, seed=1, offset=0).cpu().numpy()
+    assert got[0] == 17 and got[1] == 400 and got[2] == 0
+    # contract
+    with pytest.raises(_ffi.KuiopsError):
+        _ffi.sample_topk_topp(bad.cuda(), 0.0, 50, 0.9)
+    with pytest.raises(_ffi.KuiopsError):
+        _ffi.sample_topk_topp(torch.randn(2, 3000).cuda(), 1.0, 2000, 0.9)      # more than 1024 candidates

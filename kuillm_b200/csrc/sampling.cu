@@ -39,23 +39,28 @@ __host__ __device__ inline void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
 
 struct GroupScan { float incl, excl, own; float a[4]; };
 
-// The 128-element group starting at g0: this lane's four weights (zero beyond n or where the
-// weight is not a positive finite number), their left-to-right sum, and the inclusive / exclusive
-// scans of the lanes' sums.  `bad` collects whether a weight was negative, infinite or NaN.
-__device__ __forceinline__ GroupScan scan_group(const float* __restrict__ p, uint32_t n, uint32_t g0, int lane, bool vec, bool& bad) {
-  GroupScan r;
+// This lane's four weights of the 128-element group starting at g0 (zero beyond n).
+__device__ __forceinline__ float4 load_group(const float* __restrict__ p, uint32_t n, uint32_t g0, int lane, bool vec) {
   const uint32_t i0 = g0 + uint32_t(lane) * 4;
-  if (vec && i0 + 4 <= n) {
-    const float4 v = *reinterpret_cast<const float4*>(p + i0);
-    r.a[0] = v.x; r.a[1] = v.y; r.a[2] = v.z; r.a[3] = v.w;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) r.a[j] = (i0 + j < n) ? p[i0 + j] : 0.f;
-  }
+  if (vec && i0 + 4 <= n) return *reinterpret_cast<const float4*>(p + i0);
+  float4 v;
+  v.x = (i0 < n) ? p[i0] : 0.f;
+  v.y = (i0 + 1 < n) ? p[i0 + 1] : 0.f;
+  v.z = (i0 + 2 < n) ? p[i0 + 2] : 0.f;
+  v.w = (i0 + 3 < n) ? p[i0 + 3] : 0.f;
+  return v;
+}
+
+// A 128-element group from its loaded weights: the lane's four weights (zero where the weight is not a
+// non-negative finite number), their left-to-right sum, and the inclusive / exclusive scans of the lanes'
+// sums.  `bad` collects whether a weight was negative, infinite or NaN.
+__device__ __forceinline__ GroupScan scan_loaded(float4 w4, int lane, bool& bad) {
+  GroupScan r;
+  r.a[0] = w4.x; r.a[1] = w4.y; r.a[2] = w4.z; r.a[3] = w4.w;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float v = r.a[j];
-    if (!(v >= 0.f) || v > 3.402823466e38f) { bad = true; r.a[j] = 0.f; }
+    const float w = r.a[j];
+    if (!(w >= 0.f) || w > 3.402823466e38f) { bad = true; r.a[j] = 0.f; }
   }
   r.own = ((r.a[0] + r.a[1]) + r.a[2]) + r.a[3];
   float incl = r.own;
@@ -68,6 +73,10 @@ __device__ __forceinline__ GroupScan scan_group(const float* __restrict__ p, uin
   const float prev = __shfl_up_sync(0xffffffffu, incl, 1);
   r.excl = lane == 0 ? 0.f : prev;
   return r;
+}
+
+__device__ __forceinline__ GroupScan scan_group(const float* __restrict__ p, uint32_t n, uint32_t g0, int lane, bool vec, bool& bad) {
+  return scan_loaded(load_group(p, n, g0, lane, vec), lane, bad);
 }
 
 __global__ void __launch_bounds__(kSampThreads)
@@ -90,9 +99,18 @@ multinomial_rows_kernel(uint32_t n, uint32_t num_samples, const float* __restric
   // ---- phase A: the sum of every segment -----------------------------------------------------
   bool bad = false;
   float s = 0.f;
-  for (uint32_t k = gk0; k < gk1; ++k) {
-    const GroupScan g = scan_group(p, n, k * kSampGroup, lane, vec, bad);
-    s += __shfl_sync(0xffffffffu, g.incl, 31);
+  for (uint32_t k = gk0; k < gk1; k += 4) {
+    // four groups' loads in flight before the first scan (the order of the additions is unchanged)
+    float4 v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = (k + q < gk1) ? load_group(p, n, (k + q) * kSampGroup, lane, vec) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (k + q < gk1) {
+        const GroupScan g = scan_loaded(v[q], lane, bad);
+        s += __shfl_sync(0xffffffffu, g.incl, 31);
+      }
+    }
   }
   if (lane == 0) seg_sum[warp] = s;
   if (__any_sync(0xffffffffu, bad) && lane == 0 && status) atomicExch(status, 2);

@@ -137,6 +137,12 @@ KUIOPS_API int kuiops_gemm_tune_set(int dtype, int epilogue, int trans_b, uint32
 KUIOPS_API int kuiops_gemm_tune_clear(void);
 KUIOPS_API int kuiops_gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K,
                                       int* splits, int* bn, int* swapped);
+/* Number of SMs (0..64, default 0) the persistent GEMM (M > 128: one CTA per SM) leaves free from now on, process
+ * wide; returns the previous value.  For hosts that run a communication kernel on another stream beside the GEMMs
+ * (the tensor-parallel prefill sums one half-batch's partial products while the other half computes): a persistent
+ * grid that fills every SM makes such a kernel wait for the GEMM to end.  Results do not depend on it.  No
+ * counterpart in the reference (single GPU, kuipy/kuiops.py:397-469). */
+KUIOPS_API int kuiops_gemm_set_sm_reserve(int sms);
 KUIOPS_API int kuiops_gemm(int dtype, int out_dtype, uint32_t batch,
                 uint32_t M, uint32_t N, uint32_t K,
                 const void* A, int64_t lda, int64_t stride_a,

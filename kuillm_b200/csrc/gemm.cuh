@@ -46,6 +46,8 @@ bool gemm_tc_eligible(const GemmArgs& a);
 size_t gemm_tc_workspace_bytes(uint32_t batch, uint32_t M, uint32_t N, uint32_t K);
 int gemm_tc(const GemmArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t st);
 extern std::atomic<unsigned long long*> g_gemm_trace;
+// SMs the persistent (normal-placement) GEMM leaves free, for kernels that must run beside it (see kuiops_gemm_set_sm_reserve).
+extern std::atomic<int> g_gemm_sm_reserve;
 // Tuned-plan table of the tcgen05 kernel (see kuiops_gemm_tune_set).
 int gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int splits, int bn);
 void gemm_tune_clear();

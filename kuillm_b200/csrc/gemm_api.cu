@@ -92,6 +92,11 @@ int kuiops_gemm_tune_set(int dtype, int epilogue, int trans_b, uint32_t M, uint3
   return gemm_tune_set(dtype, epilogue, trans_b, M, N, K, splits, bn);
 }
 int kuiops_gemm_tune_clear(void) { gemm_tune_clear(); return KUIOPS_OK; }
+int kuiops_gemm_set_sm_reserve(int sms) {
+  if (sms < 0) sms = 0;
+  if (sms > 64) sms = 64;
+  return g_gemm_sm_reserve.exchange(sms);
+}
 int kuiops_gemm_tune_query(int dtype, int epilogue, int trans_b, uint32_t M, uint32_t N, uint32_t K, int* splits, int* bn,
                            int* swapped) {
   return gemm_tune_query(dtype, epilogue, trans_b, M, N, K, splits, bn, swapped);

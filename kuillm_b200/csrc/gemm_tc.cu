@@ -73,6 +73,7 @@ struct TcParams {
 __device__ unsigned int g_tc_error = 0;
 // Debug: device buffer of >= 16 uint64 that CTA 0 of every later tcgen05 GEMM stamps with %globaltimer.
 std::atomic<unsigned long long*> g_gemm_trace{nullptr};
+std::atomic<int> g_gemm_sm_reserve{0};
 
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
@@ -958,7 +959,10 @@ static int gemm_tc_typed(const GemmArgs& a, void* workspace, size_t workspace_by
 #undef KUIOPS_SW
     return KUIOPS_EUNSUPPORTED;
   }
-  const unsigned grid = unsigned(units < uint64_t(num_sms()) ? units : uint64_t(num_sms()));
+  // persistent CTAs, one per SM, minus the SMs the caller asked to keep free for a kernel of another stream
+  const int reserve = g_gemm_sm_reserve.load(std::memory_order_relaxed);
+  const uint64_t sms = uint64_t(num_sms() - reserve > 1 ? num_sms() - reserve : 1);
+  const unsigned grid = unsigned(units < sms ? units : sms);
   if (pl.bn == 256)
     return b_mn ? launch_tc<TIN, 256, 4, 2, false, true>(mapA, mapB, p, grid, st)
                 : launch_tc<TIN, 256, 4, 2, false, false>(mapA, mapB, p, grid, st);

@@ -130,6 +130,11 @@ class Decoder:
         # tensor-parallel prefills of at least this many rows hide their all-reduces behind compute (two halves
         # of the batch walk the layers in lockstep)
         self.overlap_min_rows = 4096
+        # SMs the GEMMs of such a prefill leave to the summing kernel.  Measured at 4 ranks (prefill of 32 x 2048):
+        # the overlap only pays when at least as many SMs stay free as the library's kernel has CTAs (32 by
+        # default: 294 ms against 308 ms without overlap and 309 - 322 ms with fewer SMs free); at 2 ranks the
+        # sums are too short to pay for the SMs
+        self.overlap_sm_reserve = 32 if tp_size >= 4 else 0
 
     def fold_norm_weights(self):
         """Multiply each layer's norm weights into the columns of the projection that consumes the
@@ -306,6 +311,15 @@ class Decoder:
         products are being summed (NCCL, asynchronously, on the library's own stream) the other half
         computes its attention or MLP block.  Same kernels and the same two all-reduces per layer and
         half as the plain form; only the order of launches differs."""
+        # the GEMMs are persistent grids over every SM: without free SMs the summing kernel would only run
+        # between them, and nothing would overlap
+        old_reserve = _ffi.gemm_set_sm_reserve(self.overlap_sm_reserve)
+        try:
+            return self._forward_tp_overlap_body(ids, positions, seq)
+        finally:
+            _ffi.gemm_set_sm_reserve(old_reserve)
+
+    def _forward_tp_overlap_body(self, ids, positions, seq):
         import torch.distributed as dist
         cfg = self.cfg
         B = ids.shape[0]

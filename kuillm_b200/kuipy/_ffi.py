@@ -58,6 +58,7 @@ SIGNATURES = {
     "kuiops_gemm_workspace_bytes": (c_size_t, [c_int, c_u32, c_u32, c_u32, c_u32]),
     "kuiops_gemm_tune_set": (c_int, [c_int, c_int, c_int, c_u32, c_u32, c_u32, c_int, c_int]),
     "kuiops_gemm_tune_clear": (c_int, []),
+    "kuiops_gemm_set_sm_reserve": (c_int, [c_int]),
     "kuiops_gemm_tune_query": (c_int, [c_int, c_int, c_int, c_u32, c_u32, c_u32, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
                                        ctypes.POINTER(c_int)]),
     "kuiops_gemm": (c_int, [c_int, c_int, c_u32, c_u32, c_u32, c_u32,
@@ -186,6 +187,11 @@ def gemm_plan(dtype, M, N, K, trans_b=True, epilogue=0):
     _check(lib().kuiops_gemm_tune_query(dtype_code(dtype), epilogue, 1 if trans_b else 0, M, N, K, ctypes.byref(s), ctypes.byref(b),
                                         ctypes.byref(w)), "gemm_tune_query")
     return s.value, b.value, bool(w.value)
+
+
+def gemm_set_sm_reserve(sms: int) -> int:
+    """SMs the persistent GEMM leaves free for kernels of other streams (0 = none); returns the old setting."""
+    return int(lib().kuiops_gemm_set_sm_reserve(int(sms)))
 
 
 def set_pdl(enabled: bool) -> bool:

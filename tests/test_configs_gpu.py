@@ -203,6 +203,23 @@ def test_sdpa_decode_batch64(cuda, S, hkv):
     assert (o1.float() - out[5:6].float()).abs().max() <= 2e-2 * out[5:6].float().abs().max()
 
 
+def test_persistent_gemm_with_sms_kept_free(cuda):
+    """kuiops_gemm_set_sm_reserve shrinks the persistent grid; the product does not change by a bit."""
+    g = gen(12)
+    A = torch.randn(4096, 1024, device="cuda", generator=g).bfloat16()
+    W = torch.randn(2048, 1024, device="cuda", generator=g).bfloat16()
+    want = _ffi.gemm(A, W, trans_b=True)
+    old = _ffi.gemm_set_sm_reserve(32)
+    try:
+        got = _ffi.gemm(A, W, trans_b=True)
+        assert _ffi.gemm_set_sm_reserve(1000) == 32          # clamped to 64, returns the previous value
+        got2 = _ffi.gemm(A, W, trans_b=True)
+    finally:
+        assert _ffi.gemm_set_sm_reserve(old) == 64
+    assert torch.equal(got, want) and torch.equal(got2, want)
+    assert _ffi.tc_error() == 0
+
+
 def test_sdpa_decode_many_launches_never_time_out(cuda):
     """The decode step's own attention shape (4 query heads per KV head, two P buffers), launched as
     often as a few generations do: no pipeline wait may run out (an issuer that falls two phases behind

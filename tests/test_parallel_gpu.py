@@ -18,6 +18,17 @@ def _free_port():
 
 
 def _tp_worker(rank, size, port, q):
+    """Child process of one rank; any exception ends the process with a non-zero code at once (the
+    parent then stops the others) instead of leaving it to the collectives' time limit."""
+    try:
+        _tp_worker_body(rank, size, port, q)
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        os._exit(3)
+
+
+def _tp_worker_body(rank, size, port, q):
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parent.parent
@@ -27,13 +38,17 @@ def _tp_worker(rank, size, port, q):
     from kuillm_b200.decoder import Decoder, DecoderConfig, dp_slice
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=size, device_id=torch.device("cuda", rank))
+    import datetime
+    # a rank that fails leaves the others in a collective: a short limit ends them instead of the default ten minutes
+    dist.init_process_group("nccl", rank=rank, world_size=size, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=180))
     cfg = DecoderConfig.tiny(n_heads=2 * size, n_kv_heads=size)
     g = torch.Generator().manual_seed(0)
-    ids = torch.randint(0, cfg.vocab, (4, 16), generator=g).cuda()
+    B = max(4, size)                                 # every data-parallel rank gets at least one sequence
+    ids = torch.randint(0, cfg.vocab, (B, 16), generator=g).cuda()
     # reference: the whole model on this rank's GPU
     full = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05)
-    full.alloc_cache(4, 24)
+    full.alloc_cache(B, 24)
     ref = full.prefill(ids)
     ref_tok = ref.argmax(-1)
     ref2 = full.decode_step(ref_tok)
@@ -46,7 +61,7 @@ def _tp_worker(rank, size, port, q):
         return real(t, *a, **k)
     dist.all_reduce = counted
     tp = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
-    tp.alloc_cache(4, 24)
+    tp.alloc_cache(B, 24)
     out = tp.prefill(ids)
     n_calls = calls[0]
     out2 = tp.decode_step(ref_tok)
@@ -61,7 +76,7 @@ def _tp_worker(rank, size, port, q):
     # the same prefill with its all-reduces hidden behind the other half of the batch: same logits (the sums are
     # element-wise, whatever the message size), same caches (the next decode step agrees), twice the calls
     tpo = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
-    tpo.alloc_cache(4, 24)
+    tpo.alloc_cache(B, 24)
     tpo.overlap_min_rows = 1
     calls[0] = 0
     dist.all_reduce = counted
@@ -74,11 +89,11 @@ def _tp_worker(rank, size, port, q):
     # them; no NCCL call on that path, and with two ranks the sum rounds exactly as NCCL's does
     from kuipy import _ffi
     tpf = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05, tp_rank=rank, tp_size=size)
-    tpf.alloc_cache(4, 24)
+    tpf.alloc_cache(B, 24)
     tpf.enable_fused_allreduce(128)
     calls[0] = 0
     dist.all_reduce = counted
-    f1 = tpf.prefill(ids)                     # 64 rows: small enough for the fused path
+    f1 = tpf.prefill(ids)                     # 64 rows (128 with eight ranks): small enough for the fused path
     tok = ref_tok
     # two ranks: fp32 sum of two rounded partials, rounded once, is what NCCL computes too; with more
     # ranks NCCL's order of additions is its own, so the forms agree only within rounding
@@ -96,7 +111,7 @@ def _tp_worker(rank, size, port, q):
     ok_fused = same and worst < 3e-2 and fused_calls == 0 and _ffi.tc_error() == 0 and int(tpf.exchange.epoch.item()) == 6 * 2 * cfg.n_layers
     ok_tp = ok_tp and ok_fused
     # data parallel: this rank's slice of the batch, no collective
-    lo, hi = dp_slice(4, rank, size)
+    lo, hi = dp_slice(B, rank, size)
     dp = Decoder(cfg, device=f"cuda:{rank}", seed=0, init_std=0.05)
     dp.alloc_cache(hi - lo, 24)
     ok_dp = torch.equal(dp.prefill(ids[lo:hi]), ref[lo:hi])
@@ -118,8 +133,15 @@ def test_tp_and_dp_match_single_gpu(size):
     procs = [ctx.Process(target=_tp_worker, args=(r, size, port, q)) for r in range(size)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
+    import time
+    deadline = time.time() + 300
+    while time.time() < deadline and any(p.exitcode is None for p in procs) and not any(p.exitcode not in (None, 0) for p in procs):
+        time.sleep(0.5)
+    codes = [p.exitcode for p in procs]
+    for p in procs:                                   # a failed or late rank: stop exactly the children started here
+        if p.exitcode is None:
+            p.kill()
+        p.join(10)
+    assert codes == [0] * size, codes
     ok, r1, r2, n, ok_fused, same, fused_calls = q.get(timeout=10)
     assert ok == 1, (r1, r2, n, ok_fused, same, fused_calls)

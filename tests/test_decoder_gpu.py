@@ -193,7 +193,7 @@ def test_folded_norms_match_the_unfused_layer_sequence(cuda):
         dec.alloc_cache(4, 48)
         decs.append(dec)
     ids = torch.randint(0, cfg.vocab, (4, 20), generator=g).cuda()
-    # The judge of both forms is the same model in fp32 (PyTorch eager, the unfolded weights): the folded form
+    # The yardstick for both forms is the same model in fp32 (PyTorch eager, the unfolded weights): the folded form
     # may not be further from it than the plain sequence is (it skips one rounding; its folded weights round
     # differently), and both stay within the bf16 bar of a whole model.
     twin32 = _hf_twin(decs[1]).float()

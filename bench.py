@@ -616,6 +616,22 @@ def run_ours(args):
             g = torch.Generator().manual_seed(1000)
             ids_host = torch.randint(0, cfg.vocab, (batch, prompt), generator=g).pin_memory()
             ids_dev = ids_host.to(dev)
+            if fused:
+                # one trial decode step before anything is timed: an exchange that does not work on this group
+                # shows here within about a minute (its waits are bounded, 1 s each for the trial) instead of
+                # stretching every step of the measurement; the step then keeps NCCL, and the line says so
+                old_wait = _ffi.set_peer_wait_ns(1_000_000_000)
+                dec.length = 0
+                tok = dec.next_token(dec.prefill(ids_dev[:, :8].contiguous(), local_logits=True))
+                dec.next_token(dec.decode_step(tok, local_logits=True))
+                torch.cuda.synchronize()
+                bad = torch.tensor([1.0 if _ffi.tc_error() != 0 else 0.0], device=dev)
+                dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+                _ffi.set_peer_wait_ns(old_wait)
+                dec.length = 0
+                if bad.item() != 0:
+                    dec.exchange, fused = None, False
+                    fused_note = "a bounded wait of the fused exchange ran out in the trial step"
             t = time_decoder(dec, cfg, batch, prompt, new, ids_dev, ids_host, dev, tp_steps, tp_warm, use_graph, barrier)
             total_ms, e2e_ms, prefill_ms, decode_ms = max_over_ranks([t["total_ms"], t["e2e_ms"], t["prefill_ms"], t["decode_ms"]])
             tp_res = {"parallelism": f"tp{world}", "scaling": "strong", "global_batch": batch, "steps": tp_steps, "warmup": tp_warm,
